@@ -1,0 +1,58 @@
+// One-hop / NVLS collectives, point-to-point copy, one-shot all-reduce: instantiations and launchers.
+#include "launch.h"
+#include "direct_engine.cuh"
+#include "p2p_engine.cuh"
+
+namespace mt {
+template <class T>
+static cudaError_t go_direct(const MtDevComm* comms, const DirectArgs& a, int nctas, int nlocal, cudaStream_t s) {
+  DirectArgs args = a;
+  void* p[] = {(void*)&comms, (void*)&args};
+  return launch_any((const void*)direct_kernel<T, kDirectThreads>, dim3(nctas, nlocal), dim3(kDirectThreads), p, s,
+                    nlocal > 1);
+}
+cudaError_t launch_direct(int dtype, const MtDevComm* comms, const DirectArgs& a, int nctas, int nlocal, cudaStream_t s) {
+  switch (dtype) {
+    case DT_F32: return go_direct<F32>(comms, a, nctas, nlocal, s);
+    case DT_F16: return go_direct<F16>(comms, a, nctas, nlocal, s);
+    case DT_BF16: return go_direct<BF16>(comms, a, nctas, nlocal, s);
+    default: return go_direct<U8>(comms, a, nctas, nlocal, s);
+  }
+}
+cudaError_t launch_p2p(const MtDevComm* comms, const P2pArgs& a, int nctas, int nlocal, cudaStream_t s) {
+  P2pArgs args = a;
+  void* p[] = {(void*)&comms, (void*)&args};
+  return launch_any((const void*)p2p_kernel<kP2pThreads>, dim3(nctas, nlocal), dim3(kP2pThreads), p, s, nlocal > 1);
+}
+template <class T>
+static cudaError_t go_ll(const MtDevComm* comms, const LLArgs& a, int nctas, int nlocal, cudaStream_t s) {
+  LLArgs args = a;
+  void* p[] = {(void*)&comms, (void*)&args};
+  return launch_any((const void*)ll_allreduce_kernel<T, kLLThreads>, dim3(nctas, nlocal), dim3(kLLThreads), p, s,
+                    nlocal > 1);
+}
+cudaError_t launch_ll_allreduce(int dtype, const MtDevComm* comms, const LLArgs& a, int nctas, int nlocal, cudaStream_t s) {
+  switch (dtype) {
+    case DT_F32: return go_ll<F32>(comms, a, nctas, nlocal, s);
+    case DT_F16: return go_ll<F16>(comms, a, nctas, nlocal, s);
+    case DT_BF16: return go_ll<BF16>(comms, a, nctas, nlocal, s);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+// A wait on a word that nothing ever writes: must give up after the communicator's budget, record
+// MT_ERR_TIMEOUT_SIGNAL and return, leaving the context usable.
+__global__ void wait_timeout_test_kernel(const MtDevComm* comms) {
+  const MtDevComm& c = comms[blockIdx.y];
+  if (threadIdx.x == 0) {
+    const uint64_t* w = (const uint64_t*)(c.heap[c.rank] + c.L.ll_epoch_off + 4088);  // never written
+    bounded_wait(
+        c, [&] { return load64_acquire_sys(w) == 0x5eedull; }, MT_ERR_TIMEOUT_SIGNAL, 0, MT_WHERE_TEST, 0x5eedull, 0,
+        (const volatile uint64_t*)w);
+  }
+}
+cudaError_t launch_wait_timeout_test(const MtDevComm* comms, int nlocal, cudaStream_t s) {
+  void* p[] = {(void*)&comms};
+  return launch_any((const void*)wait_timeout_test_kernel, dim3(1, nlocal), dim3(32), p, s, false);
+}
+}  // namespace mt

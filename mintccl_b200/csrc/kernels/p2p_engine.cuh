@@ -1,0 +1,156 @@
+// Direct point-to-point copy over a peer-mapped pointer, and the one-shot low-latency all-reduce.
+//
+// p2p: the reference's first script lets the receiver pull straight from the sender's buffer
+// (1_sendrecv_direct.py:31-54) and relies on host-side MPI ordering alone; nothing tells the sender
+// when its buffer may be reused.  Here both sides launch: the passive side announces "ready" and
+// waits for "done", the copying side waits for "ready", moves the data with many 16-byte accesses in
+// flight, and counts its CTAs into "done" with a release so the data is visible before the count.
+//
+// one-shot all-reduce: for messages of a few KiB the cost is latency, not bandwidth.  Every rank
+// writes its contribution as LL128 lines (flag = call epoch) into a per-sender area of every peer and
+// then sums what arrived; one kernel, no barrier, no host round trip, any input/output pointers.
+#pragma once
+#include "../device/proto_ll128.cuh"
+#include "direct_engine.cuh"
+
+namespace mt {
+
+struct P2pArgs {
+  const void* src[MT_MAX_RANKS];   // per local rank: the pointer the copying side reads
+  void* dst[MT_MAX_RANKS];         // per local rank: the pointer the copying side writes
+  uint64_t nbytes;
+  int32_t role[MT_MAX_RANKS];      // per local rank: 0 none, 1 copier, 2 passive
+  int32_t peer[MT_MAX_RANKS];      // per local rank: the other side
+  uint64_t seq[MT_MAX_RANKS];      // ready sequence number of this transfer (per ordered pair)
+  uint64_t done_target[MT_MAX_RANKS];  // cumulative CTA count the passive side waits for
+  int32_t copier_reads_remote;     // pull (1): src is in the peer's memory; push (0): dst is
+};
+
+__device__ __forceinline__ void red_release_sys_add_u64(uint64_t* p, uint64_t v) {
+  asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+
+template <int NTHREADS>
+__global__ void __launch_bounds__(NTHREADS, 1) p2p_kernel(const MtDevComm* comms, P2pArgs a) {
+  __shared__ int s_fail;
+  const int lr = blockIdx.y;
+  const MtDevComm& c = comms[lr];
+  const int role = a.role[lr], peer = a.peer[lr];
+  if (role == 0) return;
+  MtSigSlot* mine = (MtSigSlot*)(c.heap[c.rank] + c.L.sig_off) + peer;       // words the peer writes
+  MtSigSlot* theirs = (MtSigSlot*)(c.heap[peer] + c.L.sig_off) + c.rank;     // words I write
+  if (threadIdx.x == 0) s_fail = 0;
+  __syncthreads();
+  if (role == 2) {
+    if (blockIdx.x != 0) return;
+    if (threadIdx.x == 0) {
+      fence_acq_rel_sys();
+      store64_release_sys(&theirs->ready, a.seq[lr]);
+      const uint64_t want = a.done_target[lr];
+      const uint64_t* w = &mine->done;
+      bounded_wait(
+          c, [&] { return load64_acquire_sys(w) >= want; }, MT_ERR_TIMEOUT_SIGNAL, 0, MT_WHERE_P2P_DONE, want, a.seq[lr],
+          (const volatile uint64_t*)w);
+    }
+    return;
+  }
+  // copier
+  if (threadIdx.x == 0) {
+    const uint64_t want = a.seq[lr];
+    const uint64_t* w = &mine->ready;
+    if (!bounded_wait(
+            c, [&] { return load64_acquire_sys(w) >= want; }, MT_ERR_TIMEOUT_SIGNAL, blockIdx.x, MT_WHERE_P2P_READY, want,
+            a.seq[lr], (const volatile uint64_t*)w))
+      s_fail = 1;
+  }
+  __syncthreads();
+  if (s_fail) return;
+  const MtRange r = mt_split(a.nbytes, gridDim.x, blockIdx.x, kSplitAlignDirect);
+  const uint8_t* src = (const uint8_t*)a.src[lr];
+  uint8_t* dst = (uint8_t*)a.dst[lr];
+  if (r.hi > r.lo) {
+    if (a.copier_reads_remote) copy_range<NTHREADS, true, false>(src + r.lo, dst + r.lo, r.hi - r.lo);
+    else copy_range<NTHREADS, false, true>(src + r.lo, dst + r.lo, r.hi - r.lo);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    fence_acq_rel_sys();
+    red_release_sys_add_u64(&theirs->done, 1);
+  }
+}
+
+// ---- one-shot LL128 all-reduce ---------------------------------------------------------------------
+struct LLArgs {
+  const void* in[MT_MAX_RANKS];
+  void* out[MT_MAX_RANKS];
+  uint64_t nbytes;   // <= payload capacity of the one-shot area
+};
+
+// grid.x CTAs split the warp chunks of the message; epoch (one per CTA) grows by one per call.
+template <class T, int NTHREADS>
+__global__ void __launch_bounds__(NTHREADS, 1) ll_allreduce_kernel(const MtDevComm* comms, LLArgs a) {
+  __shared__ int s_fail;
+  const int lr = blockIdx.y;
+  const MtDevComm& c = comms[lr];
+  const int n = c.nranks, me = c.rank;
+  if (threadIdx.x == 0) s_fail = 0;
+  uint64_t* epoch_ptr = (uint64_t*)(c.heap[me] + c.L.ll_epoch_off) + blockIdx.x;
+  const uint64_t epoch = load64(epoch_ptr) + 1;
+  __syncthreads();
+  const uint64_t parity = epoch & 1;
+  const uint8_t* in = (const uint8_t*)a.in[lr];
+  uint8_t* out = (uint8_t*)a.out[lr];
+  const bool in_al = ((uintptr_t)in & 15) == 0, out_al = ((uintptr_t)out & 15) == 0;
+  const uint32_t nchunks = (uint32_t)mt_div_up(a.nbytes, MT_LL128_WARP_PAYLOAD);
+  const uint32_t warps_total = gridDim.x * (NTHREADS / 32);
+  bool ok = true;
+  for (uint32_t wc = blockIdx.x * (NTHREADS / 32) + (threadIdx.x >> 5); ok && wc < nchunks; wc += warps_total) {
+    const uint64_t po = (uint64_t)wc * MT_LL128_WARP_PAYLOAD, wo = (uint64_t)wc * MT_LL128_WARP_WIRE;
+    const uint64_t left = a.nbytes - po;
+    const int nb = left < MT_LL128_WARP_PAYLOAD ? (int)left : MT_LL128_WARP_PAYLOAD;
+    const LL128Lane L(nb);
+    uint64_t mineb[8];
+    ll128_load_raw(L, in + po, nb, in_al, mineb);
+    // push my lines to every peer's area for me
+    for (int d = 1; d < n; ++d) {
+      const int p = (me + d) % n;
+      uint8_t* wire = c.heap[p] + c.L.ll_off + (parity * n + me) * c.L.ll_bytes + wo;
+      ll128_store_wire(L, wire, mineb, epoch);
+    }
+    // sum in rank order so that every rank computes bit-identical results
+    float acc[8][T::kPer64];
+#pragma unroll
+    for (int w = 0; w < 8; ++w)
+#pragma unroll
+      for (int e = 0; e < T::kPer64; ++e) acc[w][e] = 0.f;
+    for (int p = 0; p < n && ok; ++p) {
+      uint64_t v[8];
+      if (p == me) {
+#pragma unroll
+        for (int w = 0; w < 8; ++w) v[w] = mineb[w];
+      } else {
+        const uint8_t* wire = c.heap[me] + c.L.ll_off + (parity * n + p) * c.L.ll_bytes + wo;
+        ok = ll128_poll_wire(c, L, wire, epoch, v, &s_fail, blockIdx.x, MT_WHERE_LL_ONESHOT, epoch);
+        if (!ok) break;
+      }
+#pragma unroll
+      for (int w = 0; w < 8; ++w) {
+        if (L.flag_lane && (w & 1)) continue;  // flag words carry no payload
+        float f[T::kPer64];
+        T::unpack(v[w], f);
+#pragma unroll
+        for (int e = 0; e < T::kPer64; ++e) acc[w][e] += f[e];
+      }
+    }
+    if (ok) {
+      uint64_t r[8];
+#pragma unroll
+      for (int w = 0; w < 8; ++w) r[w] = T::pack(acc[w]);
+      ll128_store_raw(L, out + po, nb, out_al, r);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && s_fail == 0) store64(epoch_ptr, epoch);
+}
+
+}  // namespace mt

@@ -1,0 +1,102 @@
+// C interface of the native library (loaded from Python with ctypes).
+//
+// The communicator owns the symmetric heap, the peer mappings, the optional NVLS multicast mapping
+// and the device-side descriptor; every collective is one kernel launch on the caller's stream.
+// This layer takes the place of the reference's `common.py` (set_gpu / send_ptr / recv_ptr,
+// common.py:10-38), which re-allocates staging memory and re-opens CUDA IPC handles on every call.
+#pragma once
+#include <stddef.h>
+#include <stdint.h>
+#include "device/layout.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct MtComm MtComm;
+
+typedef struct {
+  uint32_t nchannels;          // channels the FIFOs are sized for (<= MT_MAX_CHANNELS)
+  uint64_t simple_slot_bytes;  // Simple protocol: bytes per FIFO slot
+  uint32_t simple_slots;
+  uint64_t ll128_slot_bytes;   // LL128: wire bytes per FIFO slot (multiple of 2048)
+  uint32_t ll128_slots;
+  uint64_t ll_bytes;           // one-shot area: wire bytes per (parity, sender)
+  uint64_t scratch_bytes;
+  uint64_t heap_bytes;         // whole heap (control + user part)
+  uint64_t timeout_ms;         // budget of device-side waits
+  int32_t heap_kind;           // 0 = cuMem VMM (fd export, NVLS capable), 1 = cudaMalloc + cudaIpc
+} MtConfig;
+
+const char* mt_last_error(void);
+int mt_version(void);
+uint64_t mt_launch_count(void);          // kernels launched by this library in this process
+void mt_reset_launch_count(void);
+
+// ---- communicator life cycle ------------------------------------------------------------------------
+// Real communicator: one rank per process.  Steps: create -> export -> (exchange) -> import peers ->
+// [multicast create/import/bind] -> finalize.
+MtComm* mt_comm_create(int rank, int nranks, int device, const MtConfig* cfg);
+// Emulated world: `nranks` ranks on one GPU in one process; kernels are launched once for all of them
+// (cooperative launch, gridDim.y = nranks).  Used by single-GPU tests and benchmarks.
+MtComm* mt_comm_create_emulated(int nranks, int device, const MtConfig* cfg);
+void mt_comm_destroy(MtComm* c);
+int mt_comm_heap_kind(MtComm* c);                              // 0 VMM, 1 IPC
+int mt_comm_export_fd(MtComm* c);                              // VMM: POSIX fd of the local heap (caller closes)
+int mt_comm_export_ipc(MtComm* c, unsigned char handle[64]);   // IPC: cudaIpcMemHandle_t of the local heap
+int mt_comm_import_fd(MtComm* c, int peer, int fd);
+int mt_comm_import_ipc(MtComm* c, int peer, const unsigned char handle[64]);
+int mt_comm_mc_supported(MtComm* c);
+int mt_comm_mc_create(MtComm* c);                              // rank 0: returns fd of the multicast object
+int mt_comm_mc_import(MtComm* c, int fd);                      // other ranks
+int mt_comm_mc_add_device(MtComm* c);                          // all ranks, before any bind
+int mt_comm_mc_bind(MtComm* c);                                // all ranks, after every rank added its device
+int mt_comm_finalize(MtComm* c, const int* ring);              // ring: nranks entries; uploads descriptors
+int mt_comm_set_ring(MtComm* c, const int* ring);
+int mt_comm_set_timeout_ms(MtComm* c, uint64_t ms);
+void* mt_comm_heap_ptr(MtComm* c, int local_rank, int peer);   // heap base of `peer` as mapped by local rank
+void* mt_comm_mc_ptr(MtComm* c);
+int mt_comm_layout(MtComm* c, MtHeapLayout* out);
+int mt_comm_status(MtComm* c, int local_rank, MtStatus* out);  // synchronises the device
+int mt_comm_clear_status(MtComm* c);
+int mt_comm_nlocal(MtComm* c);
+
+// ---- registration of ordinary device allocations (cudaIpc with base + offset) ---------------------
+int mt_ipc_export(const void* ptr, unsigned char handle[64], uint64_t* offset, uint64_t* alloc_bytes);
+void* mt_ipc_open(const unsigned char handle[64]);             // returns the mapped allocation base (cached)
+int mt_ipc_close_all(void);
+
+// ---- file-descriptor passing over abstract unix sockets --------------------------------------------
+int mt_fd_listen(const char* name);                            // returns a listening socket
+int mt_fd_accept(int sock, int* tag, int timeout_ms);          // returns the received fd, tag = sender's tag
+int mt_fd_send(const char* name, int tag, int fd, int timeout_ms);
+void mt_fd_close(int fd);
+
+// ---- collectives ------------------------------------------------------------------------------------
+// `in` / `out` are arrays with one pointer per local rank (one entry outside emulation).
+// dtype: 0 f32, 1 f16, 2 bf16, 3 bytes (copy-only ops).  proto: 0 Simple, 1 LL128.
+// op (ring): 0 sendrecv(chain) 1 broadcast 2 reduce 3 allgather 4 reducescatter 5 allreduce.
+int mt_ring(MtComm* c, void* stream, int proto, int dtype, int op, const void* const* in, void* const* out,
+            uint64_t nbytes, int root, int spatial, const int* chain, int chain_len, int nchannels);
+// op (direct): 0 allgather 1 reducescatter 2 allreduce 3 alltoall 4 broadcast 5 reduce.
+int mt_direct(MtComm* c, void* stream, int dtype, int op, const void* const* in, void* const* out, uint64_t in_off,
+              uint64_t out_off, uint64_t nbytes, int root, int variant, int nvls, int nctas);
+int mt_ll_allreduce(MtComm* c, void* stream, int dtype, const void* const* in, void* const* out, uint64_t nbytes);
+uint64_t mt_ll_capacity(MtComm* c);
+// Direct copy between two ranks.  Real mode: `local_rank_role` 1 = this rank copies, 2 = passive.
+// pull != 0: the receiver copies (reads the sender's memory); else the sender copies.
+int mt_p2p(MtComm* c, void* stream, int src_rank, int dst_rank, const void* src_ptr, void* dst_ptr, uint64_t nbytes,
+           int pull, int nctas);
+
+// ---- device-wait self test: a wait nothing satisfies must time out and report, not hang -----------
+int mt_test_wait_timeout(MtComm* c, void* stream);
+
+// ---- topology ---------------------------------------------------------------------------------------
+// bw: n*n row-major matrix of link bandwidth (0 = no link).  Results are written to `out`.
+int mt_find_ring(const double* bw, int n, int* out);                          // returns length (n+1) or 0
+int mt_find_route(const double* bw, int n, int src, int dst, int* out);       // returns length or 0
+int mt_topo_probe(int ndev, double* bw, int measure, uint64_t probe_bytes);   // fills n*n matrix (GB/s or 1.0)
+
+#ifdef __cplusplus
+}
+#endif

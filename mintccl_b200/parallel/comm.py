@@ -1,0 +1,727 @@
+"""Communicator: symmetric heap, peer mappings, algorithm choice and kernel launches.
+
+One ``Communicator`` per process and GPU.  Creating it is the only expensive step: it allocates the
+symmetric heap, exchanges the heap handles through the control plane (POSIX fds of a cuMem allocation
+over unix sockets, or cudaIpc handles), maps every peer, optionally binds the NVLS multicast object and
+uploads the device descriptor.  After that every collective is exactly one kernel launch on the current
+CUDA stream, with no host communication and no allocation.
+
+The reference has no such object (every call of e.g. ``allgather`` re-allocates its staging buffer and
+re-exchanges IPC handles over MPI, 6_allgather.py:141-158); its module-level functions are provided by
+``mintccl_b200.ops.collectives`` on top of a default communicator.
+
+``Communicator.emulated(n)`` creates a world of ``n`` ranks on ONE GPU in one process: the same kernels
+run with ``gridDim.y = n`` (cooperative launch), which is how the single-GPU tests exercise every
+multi-rank protocol path.  In that mode every tensor argument is a list with one tensor per rank.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import uuid
+from typing import List, Optional, Sequence, Union
+
+import torch
+
+from .. import _native as N
+from ..config import Config
+from ..topology import find_ring, find_route, uniform_topology
+from .rendezvous import ControlPlane, SingleControl, connect, local_rank_default
+
+TensorOrList = Union[torch.Tensor, Sequence[torch.Tensor]]
+
+_DT = {torch.float32: N.DT_F32, torch.float16: N.DT_F16, torch.bfloat16: N.DT_BF16}
+
+
+class CollectiveError(RuntimeError):
+    """A device-side wait gave up (timeout or abort).  The communicator must be re-created."""
+
+    def __init__(self, status):
+        self.code, self.rank, self.channel, self.where = status.code, status.rank, status.channel, status.where
+        self.expected, self.seen, self.step = status.expected, status.seen, status.step
+        super().__init__(f"{N.ERR_NAMES.get(status.code, status.code)} on rank {status.rank} channel "
+                         f"{status.channel} (where={status.where}, expected={status.expected}, seen={status.seen}, "
+                         f"step={status.step})")
+
+
+CollectiveTimeout = CollectiveError
+
+
+class _RawCuda:
+    """Wraps a raw device pointer so that torch can build a tensor over it (CUDA array interface)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+def _dtype_code(t: torch.Tensor, reduce: bool) -> int:
+    if t.dtype in _DT:
+        return _DT[t.dtype]
+    if reduce:
+        raise TypeError(f"reductions support float32/float16/bfloat16, got {t.dtype}")
+    return N.DT_U8
+
+
+class Communicator:
+    def __init__(self, control: Optional[ControlPlane] = None, device: Optional[int] = None,
+                 config: Optional[Config] = None, group=None, _emulate: int = 0):
+        self.cfg = config or Config.from_env()
+        self.lib = N.lib()
+        self._handle = None
+        self._pending: list = []
+        self._allocs: dict[int, int] = {}
+        self._free: list[tuple[int, int]] = []
+        self._registered: dict = {}
+        self.emulated = _emulate > 0
+        if self.emulated:
+            self.control = SingleControl()
+            self.rank, self.world_size, self.nlocal = 0, _emulate, _emulate
+            self.device = 0 if device is None else device
+        else:
+            self.control = control or connect(group)
+            self.rank, self.world_size, self.nlocal = self.control.rank, self.control.world_size, 1
+            self.device = local_rank_default(self.rank) if device is None else device
+        if not torch.cuda.is_available():
+            raise RuntimeError("mintccl_b200.Communicator needs a CUDA device; use the CPU backend "
+                               "(mintccl_b200.parallel.cpu_backend) on machines without one")
+        if self.world_size > N.MT_MAX_RANKS:
+            raise ValueError(f"at most {N.MT_MAX_RANKS} ranks per node")
+        torch.cuda.set_device(self.device)
+        torch.cuda.init()
+        torch.zeros(1, device=f"cuda:{self.device}")  # make sure the primary context exists
+        self._create()
+
+    # ------------------------------------------------------------------------------------------ set-up
+    @classmethod
+    def emulated(cls, nranks: int, device: int = 0, config: Optional[Config] = None) -> "Communicator":
+        return cls(device=device, config=config, _emulate=nranks)
+
+    def _mtconfig(self, heap_kind: int) -> N.MtConfig:
+        c = self.cfg
+        return N.MtConfig(nchannels=c.max_channels, simple_slot_bytes=c.simple_slot_bytes, simple_slots=c.simple_slots,
+                          ll128_slot_bytes=c.ll128_slot_bytes, ll128_slots=c.ll128_slots, ll_bytes=c.ll_bytes,
+                          scratch_bytes=c.scratch_bytes, heap_bytes=c.heap_bytes, timeout_ms=c.wait_timeout_ms,
+                          heap_kind=heap_kind)
+
+    def _create(self) -> None:
+        L, n = self.lib, self.world_size
+        self.nvls = False
+        if self.emulated:
+            mc = self._mtconfig(1)
+            self._handle = L.mt_comm_create_emulated(n, self.device, C.byref(mc))
+            if not self._handle:
+                raise RuntimeError(f"mt_comm_create_emulated: {N.last_error()}")
+            self.heap_kind = "emulated"
+        else:
+            kinds = {"vmm": [0], "ipc": [1], "auto": [0, 1]}[self.cfg.heap_kind]
+            last = ""
+            for kind in kinds:
+                ok, err = self._try_create(kind)
+                oks = self.control.allgather(ok)
+                if all(oks):
+                    break
+                last = err or "a peer failed"
+                if self._handle:
+                    L.mt_comm_destroy(self._handle)
+                    self._handle = None
+            else:
+                raise RuntimeError(f"could not create and exchange the symmetric heap: {last}")
+            if self.heap_kind == "vmm" and n > 1 and self.cfg.nvls != "off":
+                self._try_nvls()
+                if self.cfg.nvls == "on" and not self.nvls:
+                    raise RuntimeError("MINTCCL_NVLS=on but the multicast object could not be set up")
+        ring = self._choose_ring()
+        arr = (C.c_int * N.MT_MAX_RANKS)(*ring)
+        N.check(L.mt_comm_finalize(self._handle, arr), "mt_comm_finalize")
+        self.ring = ring
+        lay = N.MtHeapLayout()
+        L.mt_comm_layout(self._handle, C.byref(lay))
+        self.layout = lay
+        self.heap_bytes = lay.heap_bytes
+        self.user_off = lay.user_off
+        self._free = [(lay.user_off, lay.heap_bytes - lay.user_off)]
+        self.heap_base = [L.mt_comm_heap_ptr(self._handle, lr, lr if self.emulated else self.rank)
+                          for lr in range(self.nlocal)]
+        self.ll_capacity = L.mt_ll_capacity(self._handle)
+        self.control.barrier()
+
+    def _try_create(self, kind: int):
+        L, n = self.lib, self.world_size
+        mc = self._mtconfig(kind)
+        self._handle = L.mt_comm_create(self.rank, n, self.device, C.byref(mc))
+        if not self._handle:
+            return False, N.last_error()
+        self.heap_kind = "vmm" if kind == 0 else "ipc"
+        if n == 1:
+            return True, ""
+        try:
+            if kind == 1:
+                buf = C.create_string_buffer(64)
+                N.check(L.mt_comm_export_ipc(self._handle, buf), "export_ipc")
+                handles = self.control.allgather(buf.raw)
+                for p, h in enumerate(handles):
+                    if p != self.rank:
+                        N.check(L.mt_comm_import_ipc(self._handle, p, h), f"import_ipc({p})")
+            else:
+                token = self.control.bcast(uuid.uuid4().hex[:12], 0)
+                self._sock_token = token
+                sock = L.mt_fd_listen(f"mintccl-{token}-{self.rank}".encode())
+                if sock < 0:
+                    raise RuntimeError("cannot listen on the fd-passing socket")
+                self._sock = sock
+                self.control.barrier()
+                fd = N.check(L.mt_comm_export_fd(self._handle), "export_fd")
+                try:
+                    for p in range(n):
+                        if p != self.rank:
+                            N.check(L.mt_fd_send(f"mintccl-{token}-{p}".encode(), self.rank, fd, 20000), f"fd_send({p})")
+                    for _ in range(n - 1):
+                        tag = C.c_int(-1)
+                        rfd = L.mt_fd_accept(sock, C.byref(tag), 20000)
+                        if rfd < 0:
+                            raise RuntimeError("did not receive a peer's heap descriptor")
+                        try:
+                            N.check(L.mt_comm_import_fd(self._handle, tag.value, rfd), f"import_fd({tag.value})")
+                        finally:
+                            L.mt_fd_close(rfd)
+                finally:
+                    L.mt_fd_close(fd)
+            return True, ""
+        except RuntimeError as e:  # reported to all ranks by the caller's allgather
+            return False, str(e)
+
+    def _try_nvls(self) -> None:
+        L, n = self.lib, self.world_size
+        sup = self.control.allgather(bool(L.mt_comm_mc_supported(self._handle)))
+        if not all(sup):
+            return
+        ok = True
+        try:
+            if self.rank == 0:
+                fd = N.check(L.mt_comm_mc_create(self._handle), "mc_create")
+                for p in range(1, n):
+                    N.check(L.mt_fd_send(f"mintccl-{self._sock_token}-{p}".encode(), 1000, fd, 20000), "mc fd_send")
+                L.mt_fd_close(fd)
+            else:
+                tag = C.c_int(-1)
+                rfd = L.mt_fd_accept(self._sock, C.byref(tag), 20000)
+                if rfd < 0 or tag.value != 1000:
+                    raise RuntimeError("did not receive the multicast descriptor")
+                N.check(L.mt_comm_mc_import(self._handle, rfd), "mc_import")
+                L.mt_fd_close(rfd)
+        except RuntimeError:
+            ok = False
+        if not all(self.control.allgather(ok)):
+            return
+        ok = L.mt_comm_mc_add_device(self._handle) == 0
+        if not all(self.control.allgather(ok)):
+            return
+        ok = L.mt_comm_mc_bind(self._handle) == 0
+        if not all(self.control.allgather(ok)):
+            raise RuntimeError(f"multicast bind failed on some rank ({N.last_error()}); cannot continue safely")
+        self.nvls = True
+
+    def _choose_ring(self) -> List[int]:
+        n = self.world_size
+        env = os.environ.get("MINTCCL_RING")
+        if env:
+            ring = [int(x) for x in env.split(",")]
+            if sorted(ring) != list(range(n)):
+                raise ValueError("MINTCCL_RING must be a permutation of the ranks")
+            return ring
+        seed = os.environ.get("MINTCCL_RING_SEED")
+        if seed is not None:
+            g = torch.Generator().manual_seed(int(seed))
+            return torch.randperm(n, generator=g).tolist()
+        ring = find_ring(uniform_topology(n))
+        return ring[:n] if ring else list(range(n))
+
+    def set_ring(self, ring: Sequence[int]) -> None:
+        arr = (C.c_int * N.MT_MAX_RANKS)(*ring)
+        N.check(self.lib.mt_comm_set_ring(self._handle, arr), "set_ring")
+        self.ring = list(ring)
+
+    def set_timeout_ms(self, ms: int) -> None:
+        N.check(self.lib.mt_comm_set_timeout_ms(self._handle, ms), "set_timeout")
+
+    def close(self) -> None:
+        if self._handle:
+            torch.cuda.synchronize(self.device)
+            self.control.barrier()
+            self.lib.mt_comm_destroy(self._handle)
+            self._handle = None
+            if getattr(self, "_sock", None) is not None:
+                self.lib.mt_fd_close(self._sock)
+                self._sock = None
+
+    def __del__(self):
+        try:
+            if self._handle:
+                self.lib.mt_comm_destroy(self._handle)
+                self._handle = None
+        except Exception:
+            pass
+
+    # ------------------------------------------------------------------------------------- status
+    def status(self, local_rank: int = 0) -> N.MtStatus:
+        st = N.MtStatus()
+        N.check(self.lib.mt_comm_status(self._handle, local_rank, C.byref(st)), "status")
+        return st
+
+    def check(self) -> None:
+        """Synchronise and raise :class:`CollectiveError` if any device-side wait gave up."""
+        for lr in range(self.nlocal):
+            st = self.status(lr)
+            if st.code != 0 or st.abort != 0:
+                raise CollectiveError(st)
+
+    # ------------------------------------------------------------------------------ symmetric memory
+    def _alloc_off(self, nbytes: int, align: int = 256) -> int:
+        nbytes = max(align, (nbytes + align - 1) // align * align)
+        for i, (off, size) in enumerate(self._free):
+            if size >= nbytes:
+                if size == nbytes:
+                    self._free.pop(i)
+                else:
+                    self._free[i] = (off + nbytes, size - nbytes)
+                self._allocs[off] = nbytes
+                return off
+        raise MemoryError(f"symmetric heap exhausted ({nbytes} bytes requested); raise MINTCCL_HEAP_BYTES")
+
+    def symm_free(self, t: TensorOrList) -> None:
+        t0 = t[0] if isinstance(t, (list, tuple)) else t
+        off = t0.data_ptr() - self.heap_base[0]
+        size = self._allocs.pop(off)
+        self._free.append((off, size))
+        self._free.sort()
+        merged: list[tuple[int, int]] = []
+        for o, s in self._free:
+            if merged and merged[-1][0] + merged[-1][1] == o:
+                merged[-1] = (merged[-1][0], merged[-1][1] + s)
+            else:
+                merged.append((o, s))
+        self._free = merged
+
+    def symm_empty(self, shape, dtype=torch.float32) -> TensorOrList:
+        """Allocate a tensor in the symmetric heap.  Collective in spirit: every rank must allocate the
+        same sizes in the same order so that the tensor has the same heap offset everywhere."""
+        shape = (shape,) if isinstance(shape, int) else tuple(shape)
+        numel = 1
+        for s in shape:
+            numel *= s
+        nbytes = numel * torch.empty((), dtype=dtype).element_size()
+        off = self._alloc_off(nbytes)
+        outs = []
+        for lr in range(self.nlocal):
+            raw = torch.as_tensor(_RawCuda(self.heap_base[lr] + off, max(nbytes, 1)), device=f"cuda:{self.device}")
+            outs.append(raw[:nbytes].view(dtype).view(shape))
+        return outs if self.emulated else outs[0]
+
+    def symm_zeros(self, shape, dtype=torch.float32) -> TensorOrList:
+        t = self.symm_empty(shape, dtype)
+        for x in (t if self.emulated else [t]):
+            x.zero_()
+        return t
+
+    def symm_offset(self, t: torch.Tensor, lr: int = 0) -> Optional[int]:
+        """Heap offset of ``t`` if it lies inside the symmetric heap of local rank ``lr``, else None."""
+        off = t.data_ptr() - self.heap_base[lr]
+        nbytes = t.numel() * t.element_size()
+        if off >= self.user_off and off + nbytes <= self.heap_bytes:
+            return off
+        return None
+
+    # ------------------------------------------------------------------------------ helpers
+    def _lists(self, t: Optional[TensorOrList]) -> Optional[List[torch.Tensor]]:
+        if t is None:
+            return None
+        if isinstance(t, torch.Tensor):
+            if self.emulated:
+                raise TypeError("emulated communicator: pass one tensor per rank")
+            ts = [t]
+        else:
+            ts = list(t)
+            if len(ts) != self.nlocal:
+                raise ValueError(f"expected {self.nlocal} tensors")
+        for x in ts:
+            if not x.is_cuda or not x.is_contiguous():
+                raise ValueError("tensors must be contiguous CUDA tensors")
+        return ts
+
+    def _stream(self) -> int:
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def _symm_off_all(self, ts: List[torch.Tensor]) -> Optional[int]:
+        offs = [self.symm_offset(t, lr) for lr, t in enumerate(ts)]
+        if offs[0] is None or any(o != offs[0] for o in offs):
+            return None
+        return offs[0]
+
+    def _ring_channels(self, nbytes: int, proto: int, nch: Optional[int]) -> int:
+        cap = self.cfg.num_blocks
+        if self.emulated:
+            cap = min(cap, 148 // self.nlocal)
+        if nch is not None:
+            return max(1, min(nch, cap))
+        per = 64 << 10 if proto == N.PROTO_LL128 else 256 << 10
+        return max(1, min(cap, (nbytes + per - 1) // per))
+
+    def _direct_ctas(self, nbytes: int, nctas: Optional[int]) -> int:
+        cap = self.cfg.direct_ctas or 64
+        if self.emulated:
+            cap = min(cap, 148 // self.nlocal)
+        if nctas is not None:
+            return max(1, min(nctas, 148 // self.nlocal if self.emulated else 148))
+        return max(1, min(cap, (nbytes + (64 << 10) - 1) // (64 << 10)))
+
+    def _pick_proto(self, nbytes: int, proto: Optional[str]) -> int:
+        p = proto or self.cfg.proto
+        if p == "simple":
+            return N.PROTO_SIMPLE
+        if p == "ll128":
+            return N.PROTO_LL128
+        return N.PROTO_LL128 if nbytes <= self.cfg.ll128_max_bytes else N.PROTO_SIMPLE
+
+    def _launch_ring(self, op, ins, outs, nbytes, dtype, proto, root=0, spatial=False, chain=None, nch=None):
+        nch = self._ring_channels(nbytes, proto, nch)
+        if spatial:
+            n = self.world_size
+            nch = max(n, nch // n * n)
+            if nch > self.cfg.max_channels or (self.emulated and nch * n > 148):
+                spatial = False
+                nch = self._ring_channels(nbytes, proto, None)
+        inp = N.ptr_array([t.data_ptr() if t is not None else 0 for t in ins]) if ins else None
+        outp = N.ptr_array([t.data_ptr() if t is not None else 0 for t in outs]) if outs else None
+        ch_arr = (C.c_int * (N.MT_MAX_RANKS + 1))(*(chain or []))
+        N.check(self.lib.mt_ring(self._handle, self._stream(), proto, dtype, op, inp, outp, nbytes, root,
+                                 1 if spatial else 0, ch_arr, len(chain or []), nch), "mt_ring")
+
+    def _launch_direct(self, dop, ins, outs, in_off, out_off, nbytes, dtype, root=0, variant=0, nvls=False, nctas=None):
+        nctas = self._direct_ctas(nbytes, nctas)
+        inp = N.ptr_array([t.data_ptr() if t is not None else 0 for t in ins])
+        outp = N.ptr_array([t.data_ptr() if t is not None else 0 for t in outs])
+        N.check(self.lib.mt_direct(self._handle, self._stream(), dtype, dop, inp, outp, in_off or 0, out_off or 0,
+                                   nbytes, root, variant, 1 if nvls else 0, nctas), "mt_direct")
+
+    def _algo(self, algo: Optional[str]) -> str:
+        return algo or self.cfg.algo
+
+    # ------------------------------------------------------------------------------ collectives
+    def allreduce(self, x: TensorOrList, out: Optional[TensorOrList] = None, algo: Optional[str] = None,
+                  proto: Optional[str] = None, nch: Optional[int] = None) -> None:
+        """Sum over all ranks; in place unless ``out`` is given."""
+        ins = self._lists(x)
+        outs = self._lists(out) or ins
+        nbytes = ins[0].numel() * ins[0].element_size()
+        dt = _dtype_code(ins[0], True)
+        algo = self._algo(algo)
+        in_off, out_off = self._symm_off_all(ins), self._symm_off_all(outs)
+        if self.world_size == 1:
+            algo = "ring"  # a single rank: the ring kernel degenerates to a local copy
+        if algo == "auto":
+            if nbytes <= min(self.cfg.ll_max_bytes, self.ll_capacity):
+                algo = "ll"
+            elif in_off is not None and out_off is not None:
+                algo = "nvls" if (self.nvls and nbytes >= self.cfg.nvls_min_bytes and nbytes % 16 == 0) else "direct"
+            else:
+                algo = "ring"
+        if algo == "ll":
+            if nbytes > self.ll_capacity:
+                raise ValueError("message too large for the one-shot path")
+            N.check(self.lib.mt_ll_allreduce(self._handle, self._stream(), dt,
+                                             N.ptr_array([t.data_ptr() for t in ins]),
+                                             N.ptr_array([t.data_ptr() for t in outs]), nbytes), "mt_ll_allreduce")
+        elif algo in ("direct", "nvls", "oneshot"):
+            if in_off is None or (out_off is None and algo != "oneshot"):
+                raise ValueError(f"algo={algo} needs tensors from the symmetric heap (Communicator.symm_empty)")
+            if algo == "nvls" and not self.nvls:
+                raise ValueError("NVLS is not available on this communicator")
+            variant = 1 if algo == "oneshot" else 0
+            if variant == 1 and in_off == out_off:
+                raise ValueError("one-shot all-reduce cannot run in place")
+            self._launch_direct(N.DOP_ALLREDUCE, ins, outs, in_off, out_off, nbytes, dt, variant=variant,
+                                nvls=algo == "nvls", nctas=nch)
+        elif algo == "ring":
+            self._launch_ring(N.OP_ALLREDUCE, ins, outs, nbytes, dt, self._pick_proto(nbytes, proto), nch=nch)
+        else:
+            raise ValueError(f"unknown algo {algo}")
+
+    def allgather(self, buff: TensorOrList, inp: Optional[TensorOrList] = None, mode: str = "temporal",
+                  algo: Optional[str] = None, proto: Optional[str] = None, nch: Optional[int] = None) -> None:
+        """``buff`` is ``[world, ...]``; row ``rank`` (or ``inp``) is the contribution, all rows the result
+        (same in-place convention as the reference, 6_allgather.py:14-16)."""
+        outs = self._lists(buff)
+        n = self.world_size
+        if outs[0].shape[0] != n:
+            raise ValueError("first dimension must equal the world size")
+        ranks = range(n) if self.emulated else [self.rank]
+        ins = self._lists(inp) or [o[r] for o, r in zip(outs, ranks)]
+        B = ins[0].numel() * ins[0].element_size()
+        if B * n != outs[0].numel() * outs[0].element_size():
+            raise ValueError("contribution and buffer sizes do not match")
+        dt = _dtype_code(outs[0], False)
+        algo = self._algo(algo)
+        out_off = self._symm_off_all(outs)
+        if n == 1:
+            algo = "ring"
+        if algo == "auto":
+            algo = "direct" if out_off is not None else "ring"
+            if algo == "direct" and self.nvls and B >= self.cfg.nvls_min_bytes and B % 16 == 0:
+                algo = "nvls"
+        if algo in ("direct", "nvls", "pull"):
+            in_off = self._symm_off_all(ins)
+            if algo == "pull":
+                if in_off is None:
+                    raise ValueError("pull all-gather needs a symmetric input")
+            elif out_off is None:
+                raise ValueError(f"algo={algo} needs a symmetric output buffer")
+            self._launch_direct(N.DOP_ALLGATHER, ins, outs, in_off, out_off, B, dt, variant=1 if algo == "pull" else 0,
+                                nvls=algo == "nvls", nctas=nch)
+        else:
+            self._launch_ring(N.OP_ALLGATHER, ins, outs, B, dt, self._pick_proto(B * (n - 1), proto),
+                              spatial=mode == "spatial", nch=nch)
+
+    def reducescatter(self, buff: TensorOrList, out: Optional[TensorOrList] = None, mode: str = "temporal",
+                      algo: Optional[str] = None, proto: Optional[str] = None, nch: Optional[int] = None) -> None:
+        """``buff`` is ``[world, ...]``; the sum over ranks of row ``rank`` lands in row ``rank`` of the
+        local ``buff`` (or in ``out``), as in the reference (7_reducescatter.py:105-117)."""
+        ins = self._lists(buff)
+        n = self.world_size
+        if ins[0].shape[0] != n:
+            raise ValueError("first dimension must equal the world size")
+        ranks = range(n) if self.emulated else [self.rank]
+        outs = self._lists(out) or [i[r] for i, r in zip(ins, ranks)]
+        B = outs[0].numel() * outs[0].element_size()
+        dt = _dtype_code(ins[0], True)
+        algo = self._algo(algo)
+        in_off = self._symm_off_all(ins)
+        if n == 1:
+            algo = "ring"
+        if algo == "auto":
+            algo = "direct" if in_off is not None else "ring"
+            if algo == "direct" and self.nvls and B >= self.cfg.nvls_min_bytes and B % 16 == 0:
+                algo = "nvls"
+        if algo in ("direct", "nvls"):
+            if in_off is None:
+                raise ValueError(f"algo={algo} needs a symmetric input buffer")
+            self._launch_direct(N.DOP_REDUCESCATTER, ins, outs, in_off, 0, B, dt, nvls=algo == "nvls", nctas=nch)
+        else:
+            self._launch_ring(N.OP_REDUCESCATTER, ins, outs, B, dt, self._pick_proto(B * (n - 1), proto),
+                              spatial=mode == "spatial", nch=nch)
+
+    def broadcast(self, buff: TensorOrList, root: int = 0, algo: Optional[str] = None, proto: Optional[str] = None,
+                  nch: Optional[int] = None) -> None:
+        """Copy ``buff`` of ``root`` into ``buff`` of every rank (4_broadcast.py:79-101)."""
+        ts = self._lists(buff)
+        nbytes = ts[0].numel() * ts[0].element_size()
+        dt = _dtype_code(ts[0], False)
+        if self.world_size == 1:
+            return
+        algo = self._algo(algo)
+        off = self._symm_off_all(ts)
+        if algo == "auto":
+            if off is not None and self.nvls and nbytes >= self.cfg.nvls_min_bytes and nbytes % 16 == 0:
+                algo = "nvls"
+            elif off is not None and nbytes <= (256 << 10):
+                algo = "direct"
+            else:
+                algo = "ring"
+        if algo in ("direct", "nvls", "pull"):
+            if off is None:
+                raise ValueError(f"algo={algo} needs a symmetric buffer")
+            self._launch_direct(N.DOP_BROADCAST, ts, ts, off, off, nbytes, dt, root=root,
+                                variant=1 if algo == "pull" else 0, nvls=algo == "nvls", nctas=nch)
+        else:
+            self._launch_ring(N.OP_BROADCAST, ts, ts, nbytes, dt, self._pick_proto(nbytes, proto), root=root, nch=nch)
+
+    def reduce(self, buff: TensorOrList, root: int = 0, out: Optional[TensorOrList] = None, algo: Optional[str] = None,
+               proto: Optional[str] = None, nch: Optional[int] = None) -> None:
+        """Sum of ``buff`` over all ranks, stored in ``buff`` (or ``out``) of ``root`` (5_reduce.py:99-121)."""
+        ins = self._lists(buff)
+        outs = self._lists(out) or ins
+        nbytes = ins[0].numel() * ins[0].element_size()
+        dt = _dtype_code(ins[0], True)
+        algo = self._algo(algo)
+        if self.world_size == 1:
+            algo = "ring"
+        off = self._symm_off_all(ins)
+        if algo == "auto":
+            if off is not None and self.nvls and nbytes >= self.cfg.nvls_min_bytes and nbytes % 16 == 0:
+                algo = "nvls"
+            elif off is not None and nbytes <= (256 << 10):
+                algo = "direct"
+            else:
+                algo = "ring"
+        if algo in ("direct", "nvls"):
+            if off is None:
+                raise ValueError(f"algo={algo} needs a symmetric buffer")
+            # the root reads every peer's buffer and writes its own: not safe in place
+            if any(o.data_ptr() == i.data_ptr() for i, o in zip(ins, outs)):
+                raise ValueError("direct/NVLS reduce needs a separate output on the root (pass out=)")
+            self._launch_direct(N.DOP_REDUCE, ins, outs, off, 0, nbytes, dt, root=root, nvls=algo == "nvls", nctas=nch)
+        else:
+            self._launch_ring(N.OP_REDUCE, ins, outs, nbytes, dt, self._pick_proto(nbytes, proto), root=root, nch=nch)
+
+    def alltoall(self, inp: TensorOrList, out: TensorOrList, algo: Optional[str] = None,
+                 nch: Optional[int] = None) -> None:
+        """Row ``p`` of ``inp`` goes to rank ``p``; row ``p`` of ``out`` comes from rank ``p``.  ``out`` must be
+        symmetric for the default push variant, ``inp`` for ``algo="pull"``."""
+        ins, outs = self._lists(inp), self._lists(out)
+        n = self.world_size
+        if ins[0].shape[0] != n or outs[0].shape[0] != n:
+            raise ValueError("first dimension must equal the world size")
+        B = ins[0].numel() * ins[0].element_size() // n
+        dt = _dtype_code(ins[0], False)
+        if n == 1:
+            outs[0].copy_(ins[0])
+            return
+        in_off, out_off = self._symm_off_all(ins), self._symm_off_all(outs)
+        pull = (algo == "pull") or (algo in (None, "auto") and out_off is None and in_off is not None)
+        if pull and in_off is None or (not pull and out_off is None):
+            raise ValueError("alltoall needs a symmetric output (push) or a symmetric input (pull)")
+        self._launch_direct(N.DOP_ALLTOALL, ins, outs, in_off, out_off, B, dt, variant=1 if pull else 0, nctas=nch)
+
+    # ------------------------------------------------------------------------------ point to point
+    def sendrecv_route(self, route: Sequence[int], src: Optional[TensorOrList], dst: Optional[TensorOrList],
+                       nbytes: Optional[int] = None, proto: Optional[str] = None, nch: Optional[int] = None) -> None:
+        """Move ``src`` on ``route[0]`` to ``dst`` on ``route[-1]`` through the jump hosts in between
+        (store-and-forward through their FIFOs, never through their user memory).  Every rank on the route
+        calls this with the same ``route``; ranks off the route may call it too (no-op).  Real mode: pass
+        ``src`` on the first rank, ``dst`` on the last, ``nbytes`` on jump hosts."""
+        route = list(route)
+        if len(set(route)) != len(route) or len(route) < 2:
+            raise ValueError("route must list at least two distinct ranks")
+        if self.emulated:
+            ins = [None] * self.nlocal
+            outs = [None] * self.nlocal
+            s, d = self._lists(src), self._lists(dst)
+            ins[route[0]] = s[route[0]]
+            outs[route[-1]] = d[route[-1]]
+            ref = s[route[0]]
+        else:
+            if self.rank not in route:
+                return
+            ins = [src if self.rank == route[0] else None]
+            outs = [dst if self.rank == route[-1] else None]
+            ref = ins[0] if ins[0] is not None else outs[0]
+        if nbytes is None:
+            if ref is None:
+                raise ValueError("jump hosts must pass nbytes")
+            nbytes = ref.numel() * ref.element_size()
+        self._launch_ring(N.OP_SENDRECV, ins, outs, nbytes, N.DT_U8, self._pick_proto(nbytes, proto), chain=route,
+                          nch=nch)
+
+    def p2p_copy(self, src_rank: int, dst_rank: int, src_ptr: int, dst_ptr: int, nbytes: int, pull: bool = True,
+                 nctas: Optional[int] = None) -> None:
+        """One direct copy over a peer-mapped pointer (both ranks call this with the same arguments; the
+        pointer of the remote side must be valid in the copier's address space)."""
+        if self.emulated or self.rank in (src_rank, dst_rank):
+            nctas = self._direct_ctas(nbytes, nctas)
+            N.check(self.lib.mt_p2p(self._handle, self._stream(), src_rank, dst_rank, src_ptr, dst_ptr, nbytes,
+                                    1 if pull else 0, nctas), "mt_p2p")
+
+    def sendrecv_direct(self, src_rank: int, dst_rank: int, buff: TensorOrList, pull: bool = True,
+                        nctas: Optional[int] = None) -> None:
+        """Direct send/recv of a symmetric tensor: ``buff`` of ``src_rank`` is copied into ``buff`` of
+        ``dst_rank`` by a single kernel on the copying side (the receiver when ``pull``), which waits for the
+        other side's ready signal and answers with a done signal (1_sendrecv_direct.py:60-79 has no such
+        handshake).  Both ranks call this."""
+        ts = self._lists(buff)
+        off = self._symm_off_all(ts)
+        if off is None:
+            raise ValueError("sendrecv_direct needs a symmetric tensor; use register() for ordinary tensors")
+        nbytes = ts[0].numel() * ts[0].element_size()
+        L = self.lib
+        if self.emulated:
+            sp = L.mt_comm_heap_ptr(self._handle, dst_rank, src_rank) + off
+            dp = L.mt_comm_heap_ptr(self._handle, src_rank, dst_rank) + off
+        else:
+            sp = L.mt_comm_heap_ptr(self._handle, 0, src_rank) + off
+            dp = L.mt_comm_heap_ptr(self._handle, 0, dst_rank) + off
+        self.p2p_copy(src_rank, dst_rank, sp, dp, nbytes, pull, nctas)
+
+    def register(self, t: torch.Tensor) -> List[int]:
+        """Make an ordinary CUDA tensor readable and writable by every peer: returns, for every rank, the
+        address of that rank's tensor in THIS process.  Collective (uses the control plane once); the
+        mapping is cached by allocation.  Uses cudaIpc on the allocation that contains the tensor plus the
+        tensor's offset inside it (the reference sends the handle only, common.py:24-26)."""
+        if self.emulated or self.world_size == 1:
+            return [t.data_ptr()] * max(1, self.world_size)
+        buf = C.create_string_buffer(64)
+        off, size = C.c_uint64(0), C.c_uint64(0)
+        N.check(self.lib.mt_ipc_export(t.data_ptr(), buf, C.byref(off), C.byref(size)), "ipc_export")
+        infos = self.control.allgather((buf.raw, off.value))
+        ptrs = []
+        for p, (h, o) in enumerate(infos):
+            if p == self.rank:
+                ptrs.append(t.data_ptr())
+            else:
+                base = self.lib.mt_ipc_open(h)
+                if not base:
+                    raise RuntimeError(f"cannot open the IPC handle of rank {p}: {N.last_error()}")
+                ptrs.append(base + o)
+        return ptrs
+
+    # deferred send / recv / sync, as in 2_sendrecv_indirect.py:96-167 and 3_sendrecv_buffer.py:78-151
+    def send(self, buff: torch.Tensor, peer: int, rank: Optional[int] = None) -> None:
+        self._pending.append(("send", self.rank if rank is None else rank, peer, buff))
+
+    def recv(self, buff: torch.Tensor, peer: int, rank: Optional[int] = None) -> None:
+        self._pending.append(("recv", self.rank if rank is None else rank, peer, buff))
+
+    def route(self, src: int, dst: int) -> List[int]:
+        """Route of a deferred transfer: the direct link on a switch; with MINTCCL_ROUTE=ring the ring
+        order from ``src`` to ``dst`` (forces multi-hop forwarding through the neighbours)."""
+        if os.environ.get("MINTCCL_ROUTE", "direct").lower() == "ring":
+            pos = self.ring.index(src)
+            out = [src]
+            while out[-1] != dst:
+                pos = (pos + 1) % self.world_size
+                out.append(self.ring[pos])
+            return out
+        r = find_route(src, dst, uniform_topology(self.world_size))
+        return r or [src, dst]
+
+    def sync(self, proto: Optional[str] = None) -> None:
+        """Execute all posted send/recv pairs.  Every rank calls it (jump hosts included).  Unlike the
+        reference there is no master rank: the posted metadata is all-gathered and every rank derives the
+        same matching and the same routes."""
+        mine = [(k, r, p, b.numel() * b.element_size()) for (k, r, p, b) in self._pending]
+        everyone = self.control.allgather(mine)
+        sends, recvs = {}, {}
+        for lst in everyone:
+            for (k, r, p, nb) in lst:
+                (sends if k == "send" else recvs).setdefault((r, p) if k == "send" else (p, r), []).append(nb)
+        for key in sorted(set(sends) | set(recvs)):
+            s, r = sends.get(key, []), recvs.get(key, [])
+            if len(s) != len(r) or any(a != b for a, b in zip(s, r)):
+                self._pending.clear()
+                raise ValueError(f"unmatched or size-mismatched send/recv between ranks {key}: sends {s}, recvs {r}")
+        cursor: dict = {}
+        for (src, dst) in sorted(sends):
+            for nb in sends[(src, dst)]:
+                i = cursor.get((src, dst), 0)
+                cursor[(src, dst)] = i + 1
+                route = self.route(src, dst)
+                sb = [b for (k, r, p, b) in self._pending if k == "send" and r == src and p == dst]
+                rb = [b for (k, r, p, b) in self._pending if k == "recv" and r == dst and p == src]
+                if self.emulated:
+                    ins = [None] * self.nlocal
+                    outs = [None] * self.nlocal
+                    ins[src], outs[dst] = sb[i], rb[i]
+                    self._launch_ring(N.OP_SENDRECV, ins, outs, nb, N.DT_U8, self._pick_proto(nb, proto), chain=route)
+                elif self.rank in route:
+                    self._launch_ring(N.OP_SENDRECV, [sb[i] if self.rank == src else None],
+                                      [rb[i] if self.rank == dst else None], nb, N.DT_U8,
+                                      self._pick_proto(nb, proto), chain=route)
+        self._pending.clear()
+
+    # ------------------------------------------------------------------------------ self tests
+    def test_wait_timeout(self) -> N.MtStatus:
+        """Launch a wait that nothing satisfies; it must give up after the communicator's budget and
+        leave an error record instead of hanging.  Returns the status of local rank 0."""
+        N.check(self.lib.mt_test_wait_timeout(self._handle, self._stream()), "test_wait_timeout")
+        return self.status(0)
+
+    def clear_status(self) -> None:
+        N.check(self.lib.mt_comm_clear_status(self._handle), "clear_status")

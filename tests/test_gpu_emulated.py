@@ -1,0 +1,275 @@
+"""Every collective on an emulated world (n ranks on one GPU, one cooperative kernel per call) against a
+plain PyTorch fp32 reference.  Copies must be bit-exact; sums are compared with the fp32-accumulated
+oracle at rtol 1e-2 (the reference compares reductions bit-exactly with NCCL, 5_reduce.py:145, which
+cannot hold for more than two ranks)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.float16, torch.bfloat16]
+_worlds = {}
+
+
+def world(n):
+    from mintccl_b200 import Config, emulated
+    if n not in _worlds:
+        cfg = Config.from_env(max_channels=16, num_blocks=16, buff_size=1 << 20, heap_bytes=768 << 20,
+                              scratch_bytes=1 << 20, wait_timeout_ms=3000)
+        _worlds[n] = emulated(n, 0, cfg)
+    return _worlds[n]
+
+
+def rand(n, numel, dtype, seed0=0):
+    out = []
+    for r in range(n):
+        g = torch.Generator(device="cuda").manual_seed(seed0 + r)
+        out.append(torch.randn(numel, generator=g, device="cuda", dtype=torch.float32).to(dtype))
+    return out
+
+
+def oracle_sum(ts):
+    acc = torch.zeros_like(ts[0], dtype=torch.float32)
+    for t in ts:
+        acc += t.float()
+    return acc
+
+
+def assert_sum_close(got, ref32, dtype):
+    torch.testing.assert_close(got.float(), ref32.to(dtype).float(), rtol=1e-2, atol=1e-2)
+
+
+SIZES = [1, 7, 120, 1000, 4099, 65536 + 3, 1_500_000]
+
+
+@pytest.mark.parametrize("n", [2, 4, 8])
+@pytest.mark.parametrize("proto", ["simple", "ll128"])
+@pytest.mark.parametrize("numel", SIZES)
+def test_ring_allreduce(n, proto, numel):
+    w = world(n)
+    for dtype in DTYPES:
+        xs = rand(n, numel, dtype)
+        ref = oracle_sum(xs)
+        w.allreduce(xs, algo="ring", proto=proto)
+        w.check()
+        for x in xs:
+            assert_sum_close(x, ref, dtype)
+        for x in xs[1:]:
+            assert torch.equal(x, xs[0])  # every rank holds the same bits
+
+
+@pytest.mark.parametrize("n", [2, 4, 8])
+@pytest.mark.parametrize("proto", ["simple", "ll128"])
+@pytest.mark.parametrize("mode", ["temporal", "spatial"])
+@pytest.mark.parametrize("numel", [1, 33, 5000, 300_001])
+def test_ring_allgather(n, proto, mode, numel):
+    w = world(n)
+    for dtype in (torch.float32, torch.bfloat16):
+        src = rand(n, numel, dtype)
+        bufs = [torch.zeros(n, numel, device="cuda", dtype=dtype) for _ in range(n)]
+        for r in range(n):
+            bufs[r][r].copy_(src[r])
+        w.allgather(bufs, mode=mode, algo="ring", proto=proto)
+        w.check()
+        ref = torch.stack(src)
+        for b in bufs:
+            assert torch.equal(b, ref)
+
+
+@pytest.mark.parametrize("n", [2, 4, 8])
+@pytest.mark.parametrize("proto", ["simple", "ll128"])
+@pytest.mark.parametrize("mode", ["temporal", "spatial"])
+@pytest.mark.parametrize("numel", [1, 33, 5000, 300_001])
+def test_ring_reducescatter(n, proto, mode, numel):
+    w = world(n)
+    for dtype in DTYPES:
+        bufs = [t.view(n, numel) for t in rand(n, n * numel, dtype, seed0=11)]
+        ref = oracle_sum(bufs)
+        w.reducescatter(bufs, mode=mode, algo="ring", proto=proto)
+        w.check()
+        for r in range(n):
+            assert_sum_close(bufs[r][r], ref[r], dtype)
+
+
+@pytest.mark.parametrize("n", [2, 4, 8])
+@pytest.mark.parametrize("proto", ["simple", "ll128"])
+@pytest.mark.parametrize("numel", [1, 1000, 1_000_003])
+def test_ring_broadcast_and_reduce(n, proto, numel):
+    w = world(n)
+    for root in (0, n - 1):
+        xs = rand(n, numel, torch.float16, seed0=3)
+        want = xs[root].clone()
+        w.broadcast(xs, root=root, algo="ring", proto=proto)
+        w.check()
+        for x in xs:
+            assert torch.equal(x, want)
+        for dtype in DTYPES:
+            ys = rand(n, numel, dtype, seed0=5)
+            ref = oracle_sum(ys)
+            w.reduce(ys, root=root, algo="ring", proto=proto)
+            w.check()
+            assert_sum_close(ys[root], ref, dtype)
+
+
+@pytest.mark.parametrize("proto", ["simple", "ll128"])
+@pytest.mark.parametrize("nbytes", [8, 4096, 1 << 20, (4 << 20) + 24])
+def test_multihop_sendrecv(proto, nbytes):
+    """rank 0 -> rank 4 through the jump hosts 1, 2, 3 (the reference hard-codes route [0, 1])."""
+    w = world(8)
+    src = [torch.randint(0, 255, (nbytes,), device="cuda", dtype=torch.uint8) for _ in range(8)]
+    dst = [torch.zeros(nbytes, device="cuda", dtype=torch.uint8) for _ in range(8)]
+    w.sendrecv_route([0, 1, 2, 3, 4], src, dst, proto=proto)
+    w.check()
+    assert torch.equal(dst[4], src[0])
+    for r in (0, 1, 2, 3, 5, 6, 7):
+        assert int(dst[r].sum()) == 0  # jump hosts never touch their user memory
+
+
+def test_deferred_send_recv_sync():
+    w = world(4)
+    a = torch.randn(100_000, device="cuda")
+    b = torch.zeros_like(a)
+    c = torch.randn(77, device="cuda", dtype=torch.float16)
+    d = torch.zeros_like(c)
+    w.send(a, 2, rank=1)
+    w.recv(b, 1, rank=2)
+    w.send(c, 0, rank=3)
+    w.recv(d, 3, rank=0)
+    w.sync()
+    w.check()
+    assert torch.equal(a, b) and torch.equal(c, d)
+
+
+def test_back_to_back_thousand_multihop():
+    """1,000 consecutive multi-hop transfers on the same FIFOs: flags never repeat, nothing is cleared."""
+    w = world(8)
+    nbytes = 4096
+    src = [torch.randint(0, 255, (nbytes,), device="cuda", dtype=torch.uint8) for _ in range(8)]
+    dst = [torch.zeros(nbytes, device="cuda", dtype=torch.uint8) for _ in range(8)]
+    for i in range(1000):
+        w.sendrecv_route([0, 1, 2, 3, 4], src, dst, proto="ll128")
+    w.check()
+    assert torch.equal(dst[4], src[0])
+
+
+@pytest.mark.parametrize("n", [2, 4, 8])
+@pytest.mark.parametrize("numel", [2, 5, 1000, 16 * 1024])
+def test_ll_oneshot_allreduce(n, numel):
+    w = world(n)
+    for dtype in DTYPES:
+        for it in range(3):  # both parities of the staging area, back to back
+            xs = rand(n, numel, dtype, seed0=it)
+            ref = oracle_sum(xs)
+            outs = [torch.empty_like(x) for x in xs]
+            w.allreduce(xs, out=outs, algo="ll")
+            w.check()
+            for o in outs:
+                assert_sum_close(o, ref, dtype)
+            for o in outs[1:]:
+                assert torch.equal(o, outs[0])
+
+
+@pytest.mark.parametrize("n", [2, 4, 8])
+@pytest.mark.parametrize("numel", [4, 1001, 262144 + 8, 3_000_000])
+def test_direct_collectives(n, numel):
+    w = world(n)
+    for dtype in DTYPES:
+        # all-reduce, two-shot (in place) and one-shot (out of place)
+        xs = w.symm_empty(numel, dtype)
+        src = rand(n, numel, dtype, seed0=21)
+        for x, s in zip(xs, src):
+            x.copy_(s)
+        ref = oracle_sum(src)
+        w.allreduce(xs, algo="direct")
+        w.check()
+        for x in xs:
+            assert_sum_close(x, ref, dtype)
+        for x in xs[1:]:
+            assert torch.equal(x, xs[0])
+        for x, s in zip(xs, src):
+            x.copy_(s)
+        outs = [torch.empty_like(s) for s in src]
+        w.allreduce(xs, out=outs, algo="oneshot")
+        w.check()
+        for o in outs:
+            assert_sum_close(o, ref, dtype)
+        for o in outs[1:]:
+            assert torch.equal(o, outs[0])
+        w.symm_free(xs)
+        # all-gather (push and pull)
+        gb = w.symm_empty((n, numel), dtype)
+        for algo in ("direct", "pull"):
+            for r in range(n):
+                gb[r].zero_()
+                gb[r][r].copy_(src[r])
+            w.allgather(gb, algo=algo)
+            w.check()
+            want = torch.stack(src)
+            for b in gb:
+                assert torch.equal(b, want)
+        # reduce-scatter
+        full = rand(n, n * numel, dtype, seed0=31)
+        for r in range(n):
+            gb[r].view(-1).copy_(full[r])
+        ref2 = oracle_sum(full).view(n, numel)
+        outs = [torch.empty(numel, device="cuda", dtype=dtype) for _ in range(n)]
+        w.reducescatter(gb, out=outs, algo="direct")
+        w.check()
+        for r in range(n):
+            assert_sum_close(outs[r], ref2[r], dtype)
+        # all-to-all
+        ob = w.symm_empty((n, numel), dtype)
+        for r in range(n):
+            gb[r].view(-1).copy_(full[r])
+        w.alltoall(gb, ob)
+        w.check()
+        for r in range(n):
+            for p in range(n):
+                assert torch.equal(ob[r][p], full[p].view(n, numel)[r])
+        # broadcast and reduce
+        for r in range(n):
+            gb[r].view(-1).copy_(full[r])
+        w.broadcast(gb, root=n - 1, algo="direct")
+        w.check()
+        for r in range(n):
+            assert torch.equal(gb[r].view(-1), full[n - 1])
+        for r in range(n):
+            gb[r].view(-1).copy_(full[r])
+        routs = [torch.zeros(n, numel, device="cuda", dtype=dtype) for _ in range(n)]
+        w.reduce(gb, root=1, out=routs, algo="direct")
+        w.check()
+        assert_sum_close(routs[1].view(-1), oracle_sum(full), dtype)
+        w.symm_free(gb)
+        w.symm_free(ob)
+
+
+def test_direct_sendrecv_symmetric():
+    w = world(4)
+    bufs = w.symm_empty(1_000_000, torch.float32)
+    for r, b in enumerate(bufs):
+        b.fill_(float(r))
+    bufs[1].copy_(torch.randn(1_000_000, device="cuda"))
+    want = bufs[1].clone()
+    for pull in (True, False):
+        bufs[3].zero_()
+        w.sendrecv_direct(1, 3, bufs, pull=pull)
+        w.check()
+        assert torch.equal(bufs[3], want)
+    w.symm_free(bufs)
+
+
+def test_bounded_wait_reports_instead_of_hanging():
+    """A wait that nothing satisfies returns after the budget with an error record; the context stays
+    usable and the communicator reports the failure on the host."""
+    from mintccl_b200 import Config, emulated
+    from mintccl_b200.parallel.comm import CollectiveError
+    cfg = Config.from_env(max_channels=2, num_blocks=2, buff_size=1 << 20, heap_bytes=64 << 20, scratch_bytes=1 << 20,
+                          wait_timeout_ms=300)
+    w = emulated(2, 0, cfg)
+    st = w.test_wait_timeout()
+    assert st.code == 5 and st.where == 10 and st.abort == 1
+    with pytest.raises(CollectiveError):
+        w.check()
+    x = torch.ones(8, device="cuda")
+    assert float((x + 1).sum()) == 16.0  # the CUDA context still works
+    w.close()
