@@ -1,0 +1,165 @@
+"""Bus-bandwidth sweep: collective x size x algorithm, this library against NCCL (torch.distributed).
+
+Run with one process per GPU::
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        -m mintccl_b200.benchmarks.sweep --min 8 --max 1G --out sweep.json
+
+Sizes follow the nccl-tests convention (all-gather: total output bytes; reduce-scatter: total input
+bytes).  Every number is the device time (CUDA events, warm-up first, one event pair around `iters`
+back-to-back calls) as the maximum over ranks; buffers are rotated through a pool larger than the L2
+so that large-message numbers are not served from cache.  The reference publishes no numbers
+(README.md has none), so NCCL on the same box is the yardstick.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+
+def parse_size(s: str) -> int:
+    s = s.strip().upper()
+    for suf, m in (("K", 1 << 10), ("M", 1 << 20), ("G", 1 << 30)):
+        if s.endswith(suf):
+            return int(float(s[:-1]) * m)
+    return int(s)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--min", default="8")
+    ap.add_argument("--max", default="256M")
+    ap.add_argument("--dtype", default="fp16", choices=["fp16", "bf16", "fp32"])
+    ap.add_argument("--collectives", default="allreduce,allgather,reducescatter,broadcast,reduce,alltoall")
+    ap.add_argument("--impls", default="mintccl,nccl")
+    ap.add_argument("--algos", default="auto", help="comma list for mintccl: auto,ring,direct,nvls,ll,oneshot")
+    ap.add_argument("--iters", type=int, default=0, help="0 = by size")
+    ap.add_argument("--out", default="")
+    a = ap.parse_args()
+
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local))
+    gloo = dist.new_group(backend="gloo")
+
+    import mintccl_b200
+    from mintccl_b200 import Config
+    from mintccl_b200.utils.busbw import busbw_factor
+
+    dtype = {"fp16": torch.float16, "bf16": torch.bfloat16, "fp32": torch.float32}[a.dtype]
+    esz = torch.empty((), dtype=dtype).element_size()
+    lo, hi = parse_size(a.min), parse_size(a.max)
+    pool_bytes = max(4 * hi, 512 << 20)
+    comm = mintccl_b200.Communicator(group=gloo, config=Config.from_env(heap_bytes=2 * pool_bytes + (3 << 30)))
+    n = world
+
+    sizes = []
+    s = lo
+    while s <= hi:
+        sizes.append(s)
+        s *= 2
+
+    def maxr(x: float) -> float:
+        t = torch.tensor([x], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=gloo)
+        return float(t[0])
+
+    def timed(fn, iters):
+        for _ in range(max(3, iters // 10)):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier(group=gloo)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return maxr(e0.elapsed_time(e1) / iters)
+
+    # rotating pools: inputs and outputs of successive calls do not sit in L2
+    sym_in = comm.symm_empty(pool_bytes // esz, dtype)
+    sym_out = comm.symm_empty(pool_bytes // esz, dtype)
+    sym_in.normal_()
+    plain_in = torch.randn(pool_bytes // esz, device="cuda", dtype=torch.float32).to(dtype) if False else sym_in
+    results = []
+    state = {"k": 0}
+
+    def views(nbytes):
+        """Next pair of (input, output) views of nbytes from the pools."""
+        per = max(nbytes, 256)
+        cnt = max(1, pool_bytes // per)
+        k = state["k"] % cnt
+        state["k"] += 1
+        ne = per // esz
+        return sym_in[k * ne: k * ne + max(1, nbytes // esz)], sym_out[k * ne: k * ne + max(1, nbytes // esz)]
+
+    for coll in a.collectives.split(","):
+        for size in sizes:
+            numel = max(1, size // esz)
+            if coll in ("allgather", "reducescatter", "alltoall"):
+                numel = max(n, numel // n * n)
+            nbytes = numel * esz
+            iters = a.iters or (200 if nbytes <= (1 << 20) else 50 if nbytes <= (64 << 20) else 10)
+            for impl in a.impls.split(","):
+                algos = a.algos.split(",") if impl == "mintccl" else ["nccl"]
+                for algo in algos:
+                    def call():
+                        i, o = views(nbytes)
+                        if impl == "mintccl":
+                            kw = {} if algo == "auto" else {"algo": algo}
+                            if coll == "allreduce":
+                                comm.allreduce(i, out=o, **kw)
+                            elif coll == "allgather":
+                                comm.allgather(o.view(n, -1), inp=i[: numel // n], **kw)
+                            elif coll == "reducescatter":
+                                comm.reducescatter(i.view(n, -1), out=o[: numel // n], **kw)
+                            elif coll == "broadcast":
+                                comm.broadcast(o, root=0, **kw)
+                            elif coll == "reduce":
+                                comm.reduce(i, root=0, out=o, **kw)
+                            elif coll == "alltoall":
+                                comm.alltoall(i.view(n, -1), o.view(n, -1))
+                        else:
+                            if coll == "allreduce":
+                                dist.all_reduce(o)
+                            elif coll == "allgather":
+                                dist.all_gather_into_tensor(o, i[: numel // n])
+                            elif coll == "reducescatter":
+                                dist.reduce_scatter_tensor(o[: numel // n], i)
+                            elif coll == "broadcast":
+                                dist.broadcast(o, src=0)
+                            elif coll == "reduce":
+                                dist.reduce(o, dst=0)
+                            elif coll == "alltoall":
+                                dist.all_to_all_single(o, i)
+                    try:
+                        ms = timed(call, iters)
+                        if impl == "mintccl":
+                            comm.check()
+                    except (ValueError, RuntimeError) as e:
+                        if rank == 0:
+                            print(f"# skip {coll} {size} {impl}:{algo}: {e}", file=sys.stderr)
+                        continue
+                    bus = busbw_factor(coll, n) * nbytes / (ms * 1e-3) / 1e9
+                    row = {"collective": coll, "bytes": nbytes, "impl": impl, "algo": algo, "us": round(ms * 1e3, 2),
+                           "algbw_GBps": round(nbytes / (ms * 1e-3) / 1e9, 3), "busbw_GBps": round(bus, 3), "n": n,
+                           "dtype": a.dtype}
+                    results.append(row)
+                    if rank == 0:
+                        print(json.dumps(row), flush=True)
+    if rank == 0 and a.out:
+        with open(a.out, "w") as f:
+            json.dump({"nvls": bool(comm.nvls), "heap": comm.heap_kind, "rows": results}, f, indent=0)
+    comm.close()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

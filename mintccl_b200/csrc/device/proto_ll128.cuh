@@ -78,7 +78,8 @@ struct LL128Lane {
     for (int k = 0; k < 4; ++k) {
       const int pair = (k >> 1) * 4 + g, half = k & 1;
       const int line_off = MT_LL128_PAIR_PAYLOAD * pair + 128 * half;
-      need[k] = line_off < nbytes;
+      // the second line of a pair also carries payload bytes [120,128) of the pair (in its flag lane)
+      need[k] = (MT_LL128_PAIR_PAYLOAD * pair + MT_LL128_LINE_PAYLOAD * half) < nbytes;
       poff[k] = flag_lane ? MT_LL128_PAIR_PAYLOAD * pair + 112 + 8 * half : line_off + 16 * l;
     }
   }

@@ -18,7 +18,7 @@ namespace mt {
 template <class T, int NTHREADS>
 struct SimplePrims {
   static constexpr int kProto = MT_PROTO_SIMPLE;
-  static constexpr int kUnroll = 4;
+  static constexpr int kUnroll = 8;
   const MtDevComm& c;
   const int ch;
   int* s_fail;  // shared-memory word, 0 while healthy

@@ -61,7 +61,7 @@ MT_HD uint64_t mt_slot_payload(int proto, uint64_t slot_wire_bytes) {
 MT_HD uint64_t mt_ll128_wire_lines(uint64_t payload) {
   uint64_t pairs = payload / MT_LL128_PAIR_PAYLOAD;
   uint64_t rest = payload % MT_LL128_PAIR_PAYLOAD;
-  return pairs * 2 + (rest == 0 ? 0 : (rest <= 128 ? 1 : 2));
+  return pairs * 2 + (rest == 0 ? 0 : (rest <= MT_LL128_LINE_PAYLOAD ? 1 : 2));
 }
 
 // Line index, inside a warp chunk, of pair p / half h (h = 0 or 1).  Access k of the warp touches

@@ -502,7 +502,9 @@ static int check_ready(MtComm* c) {
 int mt_ring(MtComm* c, void* stream, int proto, int dtype, int op, const void* const* in, void* const* out,
             uint64_t nbytes, int root, int spatial, const int* chain, int chain_len, int nchannels) {
   if (check_ready(c)) return -1;
-  if (nchannels < 1 || nchannels > (int)c->L.nchannels) return fail("nchannels out of range");
+  // a single rank uses no FIFO, so its local-copy kernels may use as many CTAs as they like
+  const int max_ch = c->nranks == 1 ? 1024 : (int)c->L.nchannels;
+  if (nchannels < 1 || nchannels > max_ch) return fail("nchannels out of range");
   if (chain_len > MT_MAX_RANKS + 1) return fail("route too long");
   if (c->emulated && nchannels * c->nlocal > 148) return fail("emulated world: channels * ranks must be <= 148");
   mt::RingArgs a;

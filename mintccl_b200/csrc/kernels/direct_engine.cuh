@@ -180,7 +180,9 @@ __device__ void direct_body(const MtDevComm& c, const DirectArgs& a, int lr, int
             if (p == me) {
               if (in != out + (uint64_t)me * B) copy_range<NTHREADS, false, false>(in + r.lo, out + (uint64_t)me * B + r.lo, r.hi - r.lo);
             } else {
-              copy_range<NTHREADS, true, false>(c.heap[p] + a.in_off + r.lo, out + (uint64_t)p * B + r.lo, r.hi - r.lo);
+              // in_off == ~0: every rank's contribution is row `rank` of its own (symmetric) output buffer
+              const uint64_t src_off = a.in_off == ~0ull ? a.out_off + (uint64_t)p * B : a.in_off;
+              copy_range<NTHREADS, true, false>(c.heap[p] + src_off + r.lo, out + (uint64_t)p * B + r.lo, r.hi - r.lo);
             }
           }
         }

@@ -359,6 +359,8 @@ class Communicator:
 
     def _ring_channels(self, nbytes: int, proto: int, nch: Optional[int]) -> int:
         cap = self.cfg.num_blocks
+        if self.world_size == 1:
+            cap = 296  # local copies only: no FIFO limits the channel count, fill the 148 SMs twice
         if self.emulated:
             cap = min(cap, 148 // self.nlocal)
         if nch is not None:
@@ -471,6 +473,8 @@ class Communicator:
         if algo in ("direct", "nvls", "pull"):
             in_off = self._symm_off_all(ins)
             if algo == "pull":
+                if in_off is None and inp is None and out_off is not None:
+                    in_off = (1 << 64) - 1  # contributions are the rows of the symmetric buffer itself
                 if in_off is None:
                     raise ValueError("pull all-gather needs a symmetric input")
             elif out_off is None:

@@ -1,0 +1,162 @@
+"""Worker of the multi-GPU tests: run under ``python -m torch.distributed.run`` with one rank per GPU.
+
+Every rank can regenerate every other rank's input from the seed, so each rank checks its own result
+against a locally computed fp32 oracle and no second library is needed as a reference."""
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def gen(rank, numel, dtype, seed0=0):
+    g = torch.Generator(device="cuda").manual_seed(seed0 + rank)
+    return torch.randn(numel, generator=g, device="cuda", dtype=torch.float32).to(dtype)
+
+
+def close(got, ref32, dtype, hops=1):
+    tol = 1e-2 if dtype != torch.bfloat16 else max(1e-2, 4e-3 * hops)
+    if dtype == torch.float32:
+        tol = 1e-5 * max(1, hops)
+    torch.testing.assert_close(got.float(), ref32.to(dtype).float(), rtol=tol, atol=4 * tol)
+
+
+def main():
+    import mintccl_b200
+    from mintccl_b200 import Config
+    rank, n = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    cfg = Config.from_env(heap_bytes=1 << 30, wait_timeout_ms=5000)
+    c = mintccl_b200.Communicator(config=cfg)
+    print(f"[r{rank}] heap={c.heap_kind} nvls={c.nvls} ring={c.ring}", flush=True)
+    dtypes = [torch.float32, torch.float16, torch.bfloat16]
+    sizes = [1, 120, 4099, 300_001, 2_000_000]
+    algos_ar = ["ring:simple", "ring:ll128", "direct", "oneshot", "ll"] + (["nvls"] if c.nvls else [])
+    for dtype in dtypes:
+        for numel in sizes:
+            srcs = [gen(r, numel, dtype) for r in range(n)]
+            ref = sum(s.float() for s in srcs)
+            for a in algos_ar:
+                if a == "ll" and numel * srcs[0].element_size() > c.ll_capacity:
+                    continue
+                if a == "nvls" and (numel * srcs[0].element_size()) % 16:
+                    continue
+                x = c.symm_empty(numel, dtype)
+                x.copy_(srcs[rank])
+                y = c.symm_empty(numel, dtype)
+                if a.startswith("ring"):
+                    c.allreduce(x, algo="ring", proto=a.split(":")[1])
+                    got, hops = x, n
+                elif a in ("oneshot", "ll"):
+                    c.allreduce(x, out=y, algo=a)
+                    got, hops = y, 1
+                else:
+                    c.allreduce(x, algo=a)
+                    got, hops = x, 1
+                c.check()
+                close(got, ref, dtype, hops)
+                c.symm_free(x)
+                c.symm_free(y)
+            # all-gather / reduce-scatter / all-to-all / broadcast / reduce
+            for mode, algo, proto in [("temporal", "ring", "simple"), ("spatial", "ring", "ll128"), ("temporal", "direct", None),
+                                      ("temporal", "pull", None)] + ([("temporal", "nvls", None)] if c.nvls and (numel * srcs[0].element_size()) % 16 == 0 else []):
+                gb = c.symm_zeros((n, numel), dtype)
+                gb[rank].copy_(srcs[rank])
+                torch.cuda.synchronize()
+                c.control.barrier()
+                c.allgather(gb, mode=mode, algo=algo, proto=proto)
+                c.check()
+                assert torch.equal(gb, torch.stack(srcs)), f"allgather {algo} {mode} {dtype} {numel}"
+                c.symm_free(gb)
+            full = [gen(r, n * numel, dtype, seed0=100).view(n, numel) for r in range(n)]
+            ref2 = sum(f.float() for f in full)
+            for mode, algo, proto in [("temporal", "ring", "simple"), ("spatial", "ring", "ll128"), ("temporal", "direct", None)] + \
+                    ([("temporal", "nvls", None)] if c.nvls and (numel * srcs[0].element_size()) % 16 == 0 else []):
+                gb = c.symm_empty((n, numel), dtype)
+                gb.copy_(full[rank])
+                out = torch.empty(numel, device="cuda", dtype=dtype)
+                torch.cuda.synchronize()
+                c.control.barrier()
+                c.reducescatter(gb, out=out, mode=mode, algo=algo, proto=proto)
+                c.check()
+                close(out, ref2[rank], dtype, n if algo == "ring" else 1)
+                c.symm_free(gb)
+            gi = c.symm_empty((n, numel), dtype)
+            go = c.symm_empty((n, numel), dtype)
+            gi.copy_(full[rank])
+            torch.cuda.synchronize()
+            c.control.barrier()
+            c.alltoall(gi, go)
+            c.check()
+            for p in range(n):
+                assert torch.equal(go[p], full[p][rank]), "alltoall"
+            c.symm_free(gi)
+            c.symm_free(go)
+            for algo in ["ring", "direct", "pull"] + (["nvls"] if c.nvls and (numel * srcs[0].element_size()) % 16 == 0 else []):
+                b = c.symm_empty(numel, dtype)
+                b.copy_(srcs[rank])
+                torch.cuda.synchronize()
+                c.control.barrier()
+                c.broadcast(b, root=n - 1, algo=algo)
+                c.check()
+                assert torch.equal(b, srcs[n - 1]), f"broadcast {algo}"
+                b.copy_(srcs[rank])
+                o = torch.zeros(numel, device="cuda", dtype=dtype)
+                torch.cuda.synchronize()
+                c.control.barrier()
+                if algo == "pull":
+                    c.symm_free(b)
+                    continue
+                c.reduce(b, root=0, out=o, algo=algo)
+                c.check()
+                if rank == 0:
+                    close(o, ref, dtype, n if algo == "ring" else 1)
+                c.symm_free(b)
+    # point to point: deferred API over a multi-hop ring route, direct pull and push, registered tensor
+    os.environ["MINTCCL_ROUTE"] = "ring"
+    a = gen(0, 1_000_003, torch.float16)
+    dst = n - 1
+    buf = a.clone() if rank == 0 else torch.zeros_like(a)
+    if rank == 0:
+        c.send(buf, dst)
+    elif rank == dst:
+        c.recv(buf, 0)
+    c.sync()
+    c.check()
+    if rank == dst:
+        assert torch.equal(buf, a), "multi-hop send/recv"
+    s = c.symm_empty(500_000, torch.float32)
+    s.copy_(gen(rank, 500_000, torch.float32, seed0=7))
+    torch.cuda.synchronize()
+    c.control.barrier()
+    for pull in (True, False):
+        c.sendrecv_direct(0, n - 1, s, pull=pull)
+        c.check()
+        if rank == n - 1:
+            assert torch.equal(s, gen(0, 500_000, torch.float32, seed0=7)), f"direct pull={pull}"
+        c.control.barrier()
+    t = gen(rank, 250_000, torch.float32, seed0=9)
+    ptrs = c.register(t)
+    out = torch.zeros_like(t)
+    c.p2p_copy(0, n - 1, ptrs[0], out.data_ptr() if rank == n - 1 else 0, t.numel() * 4, pull=True)
+    c.check()
+    if rank == n - 1:
+        assert torch.equal(out, gen(0, 250_000, torch.float32, seed0=9)), "registered pull"
+    # 1000 back-to-back multi-hop transfers (all ranks on the route)
+    route = c.ring[:]
+    small = torch.full((1024,), float(rank), device="cuda")
+    got = torch.zeros(1024, device="cuda")
+    for _ in range(1000):
+        c.sendrecv_route(route, small if rank == route[0] else None, got if rank == route[-1] else None,
+                         nbytes=4096, proto="ll128")
+    c.check()
+    if rank == route[-1]:
+        assert float(got[0]) == float(route[0])
+    c.control.barrier()
+    c.close()
+    print(f"[r{rank}] MULTI OK", flush=True)
+
+
+if __name__ == "__main__":
+    main()

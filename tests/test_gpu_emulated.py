@@ -35,8 +35,14 @@ def oracle_sum(ts):
     return acc
 
 
-def assert_sum_close(got, ref32, dtype):
-    torch.testing.assert_close(got.float(), ref32.to(dtype).float(), rtol=1e-2, atol=1e-2)
+def assert_sum_close(got, ref32, dtype, hops=1):
+    """Direct / NVLS / one-shot paths accumulate in fp32 and round once (hops=1): rtol 1e-2 holds for every
+    dtype.  A ring rounds the partial sum to the storage type at every hop, so for bf16 (8-bit mantissa,
+    half an ulp = 0.2 %) the bound grows with the number of hops."""
+    tol = 1e-2 if dtype != torch.bfloat16 else max(1e-2, 4e-3 * hops)
+    if dtype == torch.float32:
+        tol = 1e-5 * max(1, hops)
+    torch.testing.assert_close(got.float(), ref32.to(dtype).float(), rtol=tol, atol=tol * 4)
 
 
 SIZES = [1, 7, 120, 1000, 4099, 65536 + 3, 1_500_000]
@@ -53,7 +59,7 @@ def test_ring_allreduce(n, proto, numel):
         w.allreduce(xs, algo="ring", proto=proto)
         w.check()
         for x in xs:
-            assert_sum_close(x, ref, dtype)
+            assert_sum_close(x, ref, dtype, hops=n)
         for x in xs[1:]:
             assert torch.equal(x, xs[0])  # every rank holds the same bits
 
@@ -88,7 +94,7 @@ def test_ring_reducescatter(n, proto, mode, numel):
         w.reducescatter(bufs, mode=mode, algo="ring", proto=proto)
         w.check()
         for r in range(n):
-            assert_sum_close(bufs[r][r], ref[r], dtype)
+            assert_sum_close(bufs[r][r], ref[r], dtype, hops=n)
 
 
 @pytest.mark.parametrize("n", [2, 4, 8])
@@ -108,7 +114,7 @@ def test_ring_broadcast_and_reduce(n, proto, numel):
             ref = oracle_sum(ys)
             w.reduce(ys, root=root, algo="ring", proto=proto)
             w.check()
-            assert_sum_close(ys[root], ref, dtype)
+            assert_sum_close(ys[root], ref, dtype, hops=n)
 
 
 @pytest.mark.parametrize("proto", ["simple", "ll128"])
