@@ -3,7 +3,7 @@
 Run with one process per GPU::
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
-        -m mintccl_b200.benchmarks.sweep --min 8 --max 1G --out sweep.json
+        mintccl_b200/benchmarks/sweep.py --size-lo 8 --size-hi 1G --out sweep.json
 
 Sizes follow the nccl-tests convention (all-gather: total output bytes; reduce-scatter: total input
 bytes).  Every number is the device time (CUDA events, warm-up first, one event pair around `iters`
@@ -21,6 +21,8 @@ import sys
 import torch
 import torch.distributed as dist
 
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
 
 def parse_size(s: str) -> int:
     s = s.strip().upper()
@@ -32,13 +34,14 @@ def parse_size(s: str) -> int:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--min", default="8")
-    ap.add_argument("--max", default="256M")
+    ap.add_argument("--size-lo", default="8")
+    ap.add_argument("--size-hi", default="256M")
     ap.add_argument("--dtype", default="fp16", choices=["fp16", "bf16", "fp32"])
     ap.add_argument("--collectives", default="allreduce,allgather,reducescatter,broadcast,reduce,alltoall")
     ap.add_argument("--impls", default="mintccl,nccl")
     ap.add_argument("--algos", default="auto", help="comma list for mintccl: auto,ring,direct,nvls,ll,oneshot")
     ap.add_argument("--iters", type=int, default=0, help="0 = by size")
+    ap.add_argument("--ctas", default="", help="comma list of CTA / channel counts to try for mintccl (default: automatic)")
     ap.add_argument("--out", default="")
     a = ap.parse_args()
 
@@ -54,7 +57,7 @@ def main() -> None:
 
     dtype = {"fp16": torch.float16, "bf16": torch.bfloat16, "fp32": torch.float32}[a.dtype]
     esz = torch.empty((), dtype=dtype).element_size()
-    lo, hi = parse_size(a.min), parse_size(a.max)
+    lo, hi = parse_size(a.size_lo), parse_size(a.size_hi)
     pool_bytes = max(4 * hi, 512 << 20)
     comm = mintccl_b200.Communicator(group=gloo, config=Config.from_env(heap_bytes=2 * pool_bytes + (3 << 30)))
     n = world
@@ -91,14 +94,14 @@ def main() -> None:
     results = []
     state = {"k": 0}
 
-    def views(nbytes):
-        """Next pair of (input, output) views of nbytes from the pools."""
+    def make_views(nbytes):
+        """Pre-sliced (input, output) pairs rotating through the pools, so that slicing costs nothing
+        inside the timed loop and the launch plans of the communicator are reused."""
         per = max(nbytes, 256)
-        cnt = max(1, pool_bytes // per)
-        k = state["k"] % cnt
-        state["k"] += 1
+        cnt = max(1, min(64, pool_bytes // per))
         ne = per // esz
-        return sym_in[k * ne: k * ne + max(1, nbytes // esz)], sym_out[k * ne: k * ne + max(1, nbytes // esz)]
+        k = max(1, nbytes // esz)
+        return [(sym_in[j * ne: j * ne + k], sym_out[j * ne: j * ne + k]) for j in range(cnt)]
 
     for coll in a.collectives.split(","):
         for size in sizes:
@@ -109,11 +112,16 @@ def main() -> None:
             iters = a.iters or (200 if nbytes <= (1 << 20) else 50 if nbytes <= (64 << 20) else 10)
             for impl in a.impls.split(","):
                 algos = a.algos.split(",") if impl == "mintccl" else ["nccl"]
-                for algo in algos:
+                ctas_list = [int(x) for x in a.ctas.split(",")] if (a.ctas and impl == "mintccl") else [0]
+                vlist = make_views(nbytes)
+                for algo, ctas in [(x, y) for x in algos for y in ctas_list]:
                     def call():
-                        i, o = views(nbytes)
+                        i, o = vlist[state["k"] % len(vlist)]
+                        state["k"] += 1
                         if impl == "mintccl":
                             kw = {} if algo == "auto" else {"algo": algo}
+                            if ctas:
+                                kw["nch"] = ctas
                             if coll == "allreduce":
                                 comm.allreduce(i, out=o, **kw)
                             elif coll == "allgather":
@@ -125,7 +133,7 @@ def main() -> None:
                             elif coll == "reduce":
                                 comm.reduce(i, root=0, out=o, **kw)
                             elif coll == "alltoall":
-                                comm.alltoall(i.view(n, -1), o.view(n, -1))
+                                comm.alltoall(i.view(n, -1), o.view(n, -1), nch=kw.get("nch"))
                         else:
                             if coll == "allreduce":
                                 dist.all_reduce(o)
@@ -148,7 +156,7 @@ def main() -> None:
                             print(f"# skip {coll} {size} {impl}:{algo}: {e}", file=sys.stderr)
                         continue
                     bus = busbw_factor(coll, n) * nbytes / (ms * 1e-3) / 1e9
-                    row = {"collective": coll, "bytes": nbytes, "impl": impl, "algo": algo, "us": round(ms * 1e3, 2),
+                    row = {"collective": coll, "bytes": nbytes, "impl": impl, "algo": algo, "ctas": ctas, "us": round(ms * 1e3, 2),
                            "algbw_GBps": round(nbytes / (ms * 1e-3) / 1e9, 3), "busbw_GBps": round(bus, 3), "n": n,
                            "dtype": a.dtype}
                     results.append(row)

@@ -125,6 +125,27 @@ __device__ __forceinline__ __nv_bfloat16 sum_elem<BF16>(__nv_bfloat16 a, __nv_bf
 template <>
 __device__ __forceinline__ uint8_t sum_elem<U8>(uint8_t a, uint8_t) { return a; }
 
+template <class T>
+__device__ __forceinline__ float elem_to_float(typename T::elem v);
+template <>
+__device__ __forceinline__ float elem_to_float<F32>(float v) { return v; }
+template <>
+__device__ __forceinline__ float elem_to_float<F16>(__half v) { return __half2float(v); }
+template <>
+__device__ __forceinline__ float elem_to_float<BF16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <>
+__device__ __forceinline__ float elem_to_float<U8>(uint8_t v) { return (float)v; }
+template <class T>
+__device__ __forceinline__ typename T::elem float_to_elem(float v);
+template <>
+__device__ __forceinline__ float float_to_elem<F32>(float v) { return v; }
+template <>
+__device__ __forceinline__ __half float_to_elem<F16>(float v) { return __float2half_rn(v); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 float_to_elem<BF16>(float v) { return __float2bfloat16_rn(v); }
+template <>
+__device__ __forceinline__ uint8_t float_to_elem<U8>(float v) { return (uint8_t)v; }
+
 // ---- MXFP8 (e4m3 payload, ue8m0 scale per 32 elements) ----------------------------------------------
 __device__ __forceinline__ float e4m3_to_float(uint8_t v) {
   __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)v, __NV_E4M3);

@@ -46,32 +46,61 @@ static constexpr uint64_t kSplitAlignDirect = 128;
 // message lands at local_out + (o - local_base).  FIXED_ORDER sums ranks 0..n-1 in that order on every
 // rank (bitwise identical results everywhere, needed when several ranks reduce the same element);
 // otherwise each rank starts at itself so that the n readers spread over the n memories.
-template <class T, int NTHREADS, bool PUSH, bool FIXED_ORDER>
-__device__ __forceinline__ void pull_reduce_range(const MtDevComm& c, uint64_t in_off, uint64_t out_off,
-                                                  uint8_t* local_out, uint64_t byte_lo, uint64_t byte_hi,
-                                                  uint64_t local_base) {
-  const int n = c.nranks;
-  const uint64_t nvec = (byte_hi - byte_lo) >> 4;
-  for (uint64_t base = 0; base < nvec; base += (uint64_t)NTHREADS * kDirectUnroll) {
-    Acc128<T> acc[kDirectUnroll];
-    u128 v[kDirectUnroll];
-    for (int d = 0; d < n; ++d) {
-      const int p = FIXED_ORDER ? d : (c.rank + d) % n;
+template <class T, int NTHREADS, bool PUSH, bool FIXED_ORDER, int NR>
+__device__ __forceinline__ void pull_reduce_range_n(const MtDevComm& c, uint64_t in_off, uint64_t out_off,
+                                                    uint8_t* local_out, uint64_t byte_lo, uint64_t byte_hi,
+                                                    uint64_t local_base) {
+  // NR > 0: the rank count is a compile-time constant, so the loop over peers unrolls and all
+  // NR x kU remote loads of a thread are in flight together
+  const int n = NR > 0 ? NR : c.nranks;
+  // vectors per thread and pass: bounded so that NR x kU 16-byte registers fit without spilling
+  constexpr int kU = NR >= 8 ? 2 : kDirectUnroll;
+  // 16-byte vectors need every address involved to be 16-byte aligned; heaps are, so only the offsets
+  // count (a shard offset rank * B is unaligned when B is not a multiple of 16).
+  const bool vec_ok = (((in_off + byte_lo) | (PUSH ? out_off + byte_lo : 0) |
+                        (uint64_t)(uintptr_t)(local_out + (byte_lo - local_base))) & 15) == 0;
+  const uint64_t nvec = vec_ok ? (byte_hi - byte_lo) >> 4 : 0;
+  for (uint64_t base = 0; base < nvec; base += (uint64_t)NTHREADS * kU) {
+    Acc128<T> acc[kU];
+    if (NR > 0) {
+      u128 v[NR > 0 ? NR : 1][kU];
 #pragma unroll
-      for (int u = 0; u < kDirectUnroll; ++u) {
-        const uint64_t i = base + (uint64_t)u * NTHREADS + threadIdx.x;
-        if (i < nvec) v[u] = load128_relaxed_sys(c.heap[p] + in_off + byte_lo + (i << 4));
+      for (int d = 0; d < NR; ++d) {
+        const int p = FIXED_ORDER ? d : (c.rank + d) % NR;
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+          const uint64_t i = base + (uint64_t)u * NTHREADS + threadIdx.x;
+          if (i < nvec) v[d][u] = load128_relaxed_sys(c.heap[p] + in_off + byte_lo + (i << 4));
+        }
       }
-      if (d == 0) {
 #pragma unroll
-        for (int u = 0; u < kDirectUnroll; ++u) acc[u].set(v[u]);
-      } else {
+      for (int d = 0; d < NR; ++d) {
 #pragma unroll
-        for (int u = 0; u < kDirectUnroll; ++u) acc[u].add(v[u]);
+        for (int u = 0; u < kU; ++u) {
+          if (d == 0) acc[u].set(v[d][u]);
+          else acc[u].add(v[d][u]);
+        }
+      }
+    } else {
+      u128 v[kU];
+      for (int d = 0; d < n; ++d) {
+        const int p = FIXED_ORDER ? d : (c.rank + d) % n;
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+          const uint64_t i = base + (uint64_t)u * NTHREADS + threadIdx.x;
+          if (i < nvec) v[u] = load128_relaxed_sys(c.heap[p] + in_off + byte_lo + (i << 4));
+        }
+        if (d == 0) {
+#pragma unroll
+          for (int u = 0; u < kU; ++u) acc[u].set(v[u]);
+        } else {
+#pragma unroll
+          for (int u = 0; u < kU; ++u) acc[u].add(v[u]);
+        }
       }
     }
 #pragma unroll
-    for (int u = 0; u < kDirectUnroll; ++u) {
+    for (int u = 0; u < kU; ++u) {
       const uint64_t i = base + (uint64_t)u * NTHREADS + threadIdx.x;
       if (i < nvec) {
         const u128 r = acc[u].get();
@@ -86,21 +115,34 @@ __device__ __forceinline__ void pull_reduce_range(const MtDevComm& c, uint64_t i
       }
     }
   }
-  // tail (< 16 bytes), element-wise; only the last slice of a message can have one
+  // what the vectors did not cover (a tail of < 16 bytes, or everything when unaligned), element-wise
   using E = typename T::elem;
   const uint64_t done = byte_lo + (nvec << 4);
   const uint64_t nel = (byte_hi - done) / sizeof(E);
-  if (threadIdx.x < nel) {
-    const uint64_t o = done + threadIdx.x * sizeof(E);
-    E e = *reinterpret_cast<const volatile E*>(c.heap[FIXED_ORDER ? 0 : c.rank] + in_off + o);
-    for (int d = 1; d < n; ++d) {
+  for (uint64_t e_i = threadIdx.x; e_i < nel; e_i += NTHREADS) {
+    const uint64_t o = done + e_i * sizeof(E);
+    float acc = 0.f;
+    for (int d = 0; d < n; ++d) {
       const int p = FIXED_ORDER ? d : (c.rank + d) % n;
       const E x = *reinterpret_cast<const volatile E*>(c.heap[p] + in_off + o);
-      e = sum_elem<T>(e, x);
+      acc += elem_to_float<T>(x);
     }
+    const E e = float_to_elem<T>(acc);
     *reinterpret_cast<E*>(local_out + (o - local_base)) = e;
     if (PUSH)
       for (int d = 1; d < n; ++d) *reinterpret_cast<volatile E*>(c.heap[(c.rank + d) % n] + out_off + o) = e;
+  }
+}
+
+template <class T, int NTHREADS, bool PUSH, bool FIXED_ORDER>
+__device__ __forceinline__ void pull_reduce_range(const MtDevComm& c, uint64_t in_off, uint64_t out_off,
+                                                  uint8_t* local_out, uint64_t byte_lo, uint64_t byte_hi,
+                                                  uint64_t local_base) {
+  switch (c.nranks) {
+    case 2: pull_reduce_range_n<T, NTHREADS, PUSH, FIXED_ORDER, 2>(c, in_off, out_off, local_out, byte_lo, byte_hi, local_base); break;
+    case 4: pull_reduce_range_n<T, NTHREADS, PUSH, FIXED_ORDER, 4>(c, in_off, out_off, local_out, byte_lo, byte_hi, local_base); break;
+    case 8: pull_reduce_range_n<T, NTHREADS, PUSH, FIXED_ORDER, 8>(c, in_off, out_off, local_out, byte_lo, byte_hi, local_base); break;
+    default: pull_reduce_range_n<T, NTHREADS, PUSH, FIXED_ORDER, 0>(c, in_off, out_off, local_out, byte_lo, byte_hi, local_base); break;
   }
 }
 
@@ -145,6 +187,45 @@ __device__ __forceinline__ u128 mc_ld_reduce<BF16>(const void* p) { return multi
 template <>
 __device__ __forceinline__ u128 mc_ld_reduce<U8>(const void* p) { return load128(p); }
 
+// NVLS loops with several multimem operations in flight per thread.
+// dst[i] = sum over all ranks of mc_src[i]; dst is local memory, or the multicast alias when TO_MC.
+template <class T, int NTHREADS, bool TO_MC>
+__device__ __forceinline__ void nvls_reduce_range(const uint8_t* mc_src, uint8_t* dst, uint64_t nvec) {
+  for (uint64_t base = 0; base < nvec; base += (uint64_t)NTHREADS * kDirectUnroll) {
+    u128 v[kDirectUnroll];
+#pragma unroll
+    for (int u = 0; u < kDirectUnroll; ++u) {
+      const uint64_t i = base + (uint64_t)u * NTHREADS + threadIdx.x;
+      if (i < nvec) v[u] = mc_ld_reduce<T>(mc_src + (i << 4));
+    }
+#pragma unroll
+    for (int u = 0; u < kDirectUnroll; ++u) {
+      const uint64_t i = base + (uint64_t)u * NTHREADS + threadIdx.x;
+      if (i < nvec) {
+        if (TO_MC) multimem_st_128(dst + (i << 4), v[u]);
+        else *reinterpret_cast<u128*>(dst + (i << 4)) = v[u];
+      }
+    }
+  }
+}
+// mc_dst[i] (every rank's copy) = src[i]
+template <int NTHREADS>
+__device__ __forceinline__ void nvls_bcast_range(const uint8_t* src, uint8_t* mc_dst, uint64_t nvec) {
+  for (uint64_t base = 0; base < nvec; base += (uint64_t)NTHREADS * kDirectUnroll) {
+    u128 v[kDirectUnroll];
+#pragma unroll
+    for (int u = 0; u < kDirectUnroll; ++u) {
+      const uint64_t i = base + (uint64_t)u * NTHREADS + threadIdx.x;
+      if (i < nvec) v[u] = load128_stream(src + (i << 4));
+    }
+#pragma unroll
+    for (int u = 0; u < kDirectUnroll; ++u) {
+      const uint64_t i = base + (uint64_t)u * NTHREADS + threadIdx.x;
+      if (i < nvec) multimem_st_128(mc_dst + (i << 4), v[u]);
+    }
+  }
+}
+
 template <class T, int NTHREADS>
 __device__ void direct_body(const MtDevComm& c, const DirectArgs& a, int lr, int cta, int ncta, int* s_fail) {
   const int n = c.nranks, me = c.rank;
@@ -162,8 +243,7 @@ __device__ void direct_body(const MtDevComm& c, const DirectArgs& a, int lr, int
           // one multimem store lands in every rank's output (mine included)
           uint8_t* mdst = c.mc + a.out_off + (uint64_t)me * B;
           const uint64_t nvec = (r.hi - r.lo) >> 4;
-          for (uint64_t i = threadIdx.x; i < nvec; i += NTHREADS)
-            multimem_st_128(mdst + r.lo + (i << 4), load128_stream(in + r.lo + (i << 4)));
+          nvls_bcast_range<NTHREADS>(in + r.lo, mdst + r.lo, nvec);
           // a tail cannot be sent with 16-byte multimem stores
           for (uint64_t o = r.lo + (nvec << 4) + threadIdx.x; o < r.hi; o += NTHREADS)
             for (int p = 0; p < n; ++p) *(volatile uint8_t*)(c.heap[p] + a.out_off + (uint64_t)me * B + o) = in[o];
@@ -212,8 +292,7 @@ __device__ void direct_body(const MtDevComm& c, const DirectArgs& a, int lr, int
         if (a.nvls) {
           const uint8_t* msrc = c.mc + a.in_off + so;
           const uint64_t nvec = (r.hi - r.lo) >> 4;
-          for (uint64_t i = threadIdx.x; i < nvec; i += NTHREADS)
-            *reinterpret_cast<u128*>(out + r.lo + (i << 4)) = mc_ld_reduce<T>(msrc + r.lo + (i << 4));
+          nvls_reduce_range<T, NTHREADS, false>(msrc + r.lo, out + r.lo, nvec);
           if (r.lo + (nvec << 4) < r.hi)
             pull_reduce_range<T, NTHREADS, false, false>(c, a.in_off, 0, out, so + r.lo + (nvec << 4), so + r.hi, so);
         } else {
@@ -234,8 +313,7 @@ __device__ void direct_body(const MtDevComm& c, const DirectArgs& a, int lr, int
           if (hi > lo) {
             if (a.nvls) {
               const uint64_t nvec = (hi - lo) >> 4;
-              for (uint64_t i = threadIdx.x; i < nvec; i += NTHREADS)
-                multimem_st_128(c.mc + a.out_off + lo + (i << 4), mc_ld_reduce<T>(c.mc + a.in_off + lo + (i << 4)));
+              nvls_reduce_range<T, NTHREADS, true>(c.mc + a.in_off + lo, c.mc + a.out_off + lo, nvec);
               if (lo + (nvec << 4) < hi)
                 pull_reduce_range<T, NTHREADS, true, false>(c, a.in_off, a.out_off, out, lo + (nvec << 4), hi, 0);
             } else {
@@ -252,8 +330,7 @@ __device__ void direct_body(const MtDevComm& c, const DirectArgs& a, int lr, int
         if (a.nvls) {
           if (me == a.root) {
             const uint64_t nvec = (r.hi - r.lo) >> 4;
-            for (uint64_t i = threadIdx.x; i < nvec; i += NTHREADS)
-              multimem_st_128(c.mc + a.out_off + r.lo + (i << 4), load128_stream(in + r.lo + (i << 4)));
+            nvls_bcast_range<NTHREADS>(in + r.lo, c.mc + a.out_off + r.lo, nvec);
             for (uint64_t o = r.lo + (nvec << 4) + threadIdx.x; o < r.hi; o += NTHREADS)
               for (int p = 0; p < n; ++p) *(volatile uint8_t*)(c.heap[p] + a.out_off + o) = in[o];
           }
@@ -278,8 +355,7 @@ __device__ void direct_body(const MtDevComm& c, const DirectArgs& a, int lr, int
       if (r.hi > r.lo && me == a.root) {
         if (a.nvls) {
           const uint64_t nvec = (r.hi - r.lo) >> 4;
-          for (uint64_t i = threadIdx.x; i < nvec; i += NTHREADS)
-            *reinterpret_cast<u128*>(out + r.lo + (i << 4)) = mc_ld_reduce<T>(c.mc + a.in_off + r.lo + (i << 4));
+          nvls_reduce_range<T, NTHREADS, false>(c.mc + a.in_off + r.lo, out + r.lo, nvec);
           if (r.lo + (nvec << 4) < r.hi)
             pull_reduce_range<T, NTHREADS, false, false>(c, a.in_off, 0, out, r.lo + (nvec << 4), r.hi, 0);
         } else {

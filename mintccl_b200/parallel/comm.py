@@ -72,6 +72,8 @@ class Communicator:
         self._allocs: dict[int, int] = {}
         self._free: list[tuple[int, int]] = []
         self._registered: dict = {}
+        self._plans: dict = {}
+        self._rec_key = None
         self.emulated = _emulate > 0
         if self.emulated:
             self.control = SingleControl()
@@ -395,23 +397,60 @@ class Communicator:
         inp = N.ptr_array([t.data_ptr() if t is not None else 0 for t in ins]) if ins else None
         outp = N.ptr_array([t.data_ptr() if t is not None else 0 for t in outs]) if outs else None
         ch_arr = (C.c_int * (N.MT_MAX_RANKS + 1))(*(chain or []))
-        N.check(self.lib.mt_ring(self._handle, self._stream(), proto, dtype, op, inp, outp, nbytes, root,
-                                 1 if spatial else 0, ch_arr, len(chain or []), nch), "mt_ring")
+        self._run(self.lib.mt_ring, (proto, dtype, op, inp, outp, nbytes, root, 1 if spatial else 0, ch_arr,
+                                     len(chain or []), nch))
 
     def _launch_direct(self, dop, ins, outs, in_off, out_off, nbytes, dtype, root=0, variant=0, nvls=False, nctas=None):
         nctas = self._direct_ctas(nbytes, nctas)
+        if nvls and (nbytes % 16 or (in_off or 0) % 16 or (out_off or 0) % 16
+                     or any(t is not None and t.data_ptr() % 16 for t in list(ins) + list(outs))):
+            raise ValueError("NVLS algorithms need 16-byte aligned buffers and a byte count that is a multiple of 16")
         inp = N.ptr_array([t.data_ptr() if t is not None else 0 for t in ins])
         outp = N.ptr_array([t.data_ptr() if t is not None else 0 for t in outs])
-        N.check(self.lib.mt_direct(self._handle, self._stream(), dtype, dop, inp, outp, in_off or 0, out_off or 0,
-                                   nbytes, root, variant, 1 if nvls else 0, nctas), "mt_direct")
+        self._run(self.lib.mt_direct, (dtype, dop, inp, outp, in_off or 0, out_off or 0, nbytes, root, variant,
+                                       1 if nvls else 0, nctas))
 
     def _algo(self, algo: Optional[str]) -> str:
         return algo or self.cfg.algo
+
+    # Launch plans: the first call of a collective on given buffers validates the arguments, picks the
+    # algorithm and records the native call; later calls with the same buffers replay it directly, which
+    # keeps the host cost of a collective at a few microseconds.
+    def _run(self, fn, args) -> None:
+        if fn(self._handle, torch.cuda.current_stream(self.device).cuda_stream, *args) < 0:
+            raise RuntimeError(f"{fn.__name__}: {N.last_error()}")
+        if self._rec_key is not None:
+            if len(self._plans) > 8192:
+                self._plans.clear()
+            self._plans[self._rec_key] = (fn, args)
+            self._rec_key = None
+
+    def _replay(self, key) -> bool:
+        p = self._plans.get(key)
+        if p is None:
+            self._rec_key = key
+            return False
+        if p[0](self._handle, torch.cuda.current_stream(self.device).cuda_stream, *p[1]) < 0:
+            raise RuntimeError(f"{p[0].__name__}: {N.last_error()}")
+        return True
+
+    @staticmethod
+    def _key(tag, a, b, *rest):
+        return (tag, a.data_ptr(), a.numel(), a.dtype, 0 if b is None else b.data_ptr(), *rest)
 
     # ------------------------------------------------------------------------------ collectives
     def allreduce(self, x: TensorOrList, out: Optional[TensorOrList] = None, algo: Optional[str] = None,
                   proto: Optional[str] = None, nch: Optional[int] = None) -> None:
         """Sum over all ranks; in place unless ``out`` is given."""
+        if not self.emulated and type(x) is torch.Tensor:
+            if self._replay(self._key("allreduce", x, out, algo, proto, nch)):
+                return
+        try:
+            return self._allreduce_slow(x, out, algo, proto, nch)
+        finally:
+            self._rec_key = None
+
+    def _allreduce_slow(self, x, out, algo, proto, nch):
         ins = self._lists(x)
         outs = self._lists(out) or ins
         nbytes = ins[0].numel() * ins[0].element_size()
@@ -430,9 +469,8 @@ class Communicator:
         if algo == "ll":
             if nbytes > self.ll_capacity:
                 raise ValueError("message too large for the one-shot path")
-            N.check(self.lib.mt_ll_allreduce(self._handle, self._stream(), dt,
-                                             N.ptr_array([t.data_ptr() for t in ins]),
-                                             N.ptr_array([t.data_ptr() for t in outs]), nbytes), "mt_ll_allreduce")
+            self._run(self.lib.mt_ll_allreduce, (dt, N.ptr_array([t.data_ptr() for t in ins]),
+                                                 N.ptr_array([t.data_ptr() for t in outs]), nbytes))
         elif algo in ("direct", "nvls", "oneshot"):
             if in_off is None or (out_off is None and algo != "oneshot"):
                 raise ValueError(f"algo={algo} needs tensors from the symmetric heap (Communicator.symm_empty)")
@@ -452,6 +490,15 @@ class Communicator:
                   algo: Optional[str] = None, proto: Optional[str] = None, nch: Optional[int] = None) -> None:
         """``buff`` is ``[world, ...]``; row ``rank`` (or ``inp``) is the contribution, all rows the result
         (same in-place convention as the reference, 6_allgather.py:14-16)."""
+        if not self.emulated and type(buff) is torch.Tensor:
+            if self._replay(self._key("allgather", buff, inp, mode, algo, proto, nch)):
+                return
+        try:
+            return self._allgather_slow(buff, inp, mode, algo, proto, nch)
+        finally:
+            self._rec_key = None
+
+    def _allgather_slow(self, buff, inp, mode, algo, proto, nch):
         outs = self._lists(buff)
         n = self.world_size
         if outs[0].shape[0] != n:
@@ -473,7 +520,7 @@ class Communicator:
         if algo in ("direct", "nvls", "pull"):
             in_off = self._symm_off_all(ins)
             if algo == "pull":
-                if in_off is None and inp is None and out_off is not None:
+                if inp is None and out_off is not None:
                     in_off = (1 << 64) - 1  # contributions are the rows of the symmetric buffer itself
                 if in_off is None:
                     raise ValueError("pull all-gather needs a symmetric input")
@@ -489,6 +536,15 @@ class Communicator:
                       algo: Optional[str] = None, proto: Optional[str] = None, nch: Optional[int] = None) -> None:
         """``buff`` is ``[world, ...]``; the sum over ranks of row ``rank`` lands in row ``rank`` of the
         local ``buff`` (or in ``out``), as in the reference (7_reducescatter.py:105-117)."""
+        if not self.emulated and type(buff) is torch.Tensor:
+            if self._replay(self._key("reducescatter", buff, out, mode, algo, proto, nch)):
+                return
+        try:
+            return self._reducescatter_slow(buff, out, mode, algo, proto, nch)
+        finally:
+            self._rec_key = None
+
+    def _reducescatter_slow(self, buff, out, mode, algo, proto, nch):
         ins = self._lists(buff)
         n = self.world_size
         if ins[0].shape[0] != n:
@@ -516,6 +572,15 @@ class Communicator:
     def broadcast(self, buff: TensorOrList, root: int = 0, algo: Optional[str] = None, proto: Optional[str] = None,
                   nch: Optional[int] = None) -> None:
         """Copy ``buff`` of ``root`` into ``buff`` of every rank (4_broadcast.py:79-101)."""
+        if not self.emulated and type(buff) is torch.Tensor:
+            if self._replay(self._key("broadcast", buff, None, root, algo, proto, nch)):
+                return
+        try:
+            return self._broadcast_slow(buff, root, algo, proto, nch)
+        finally:
+            self._rec_key = None
+
+    def _broadcast_slow(self, buff, root, algo, proto, nch):
         ts = self._lists(buff)
         nbytes = ts[0].numel() * ts[0].element_size()
         dt = _dtype_code(ts[0], False)
@@ -541,6 +606,15 @@ class Communicator:
     def reduce(self, buff: TensorOrList, root: int = 0, out: Optional[TensorOrList] = None, algo: Optional[str] = None,
                proto: Optional[str] = None, nch: Optional[int] = None) -> None:
         """Sum of ``buff`` over all ranks, stored in ``buff`` (or ``out``) of ``root`` (5_reduce.py:99-121)."""
+        if not self.emulated and type(buff) is torch.Tensor:
+            if self._replay(self._key("reduce", buff, out, root, algo, proto, nch)):
+                return
+        try:
+            return self._reduce_slow(buff, root, out, algo, proto, nch)
+        finally:
+            self._rec_key = None
+
+    def _reduce_slow(self, buff, root, out, algo, proto, nch):
         ins = self._lists(buff)
         outs = self._lists(out) or ins
         nbytes = ins[0].numel() * ins[0].element_size()
@@ -570,6 +644,15 @@ class Communicator:
                  nch: Optional[int] = None) -> None:
         """Row ``p`` of ``inp`` goes to rank ``p``; row ``p`` of ``out`` comes from rank ``p``.  ``out`` must be
         symmetric for the default push variant, ``inp`` for ``algo="pull"``."""
+        if not self.emulated and type(inp) is torch.Tensor:
+            if self._replay(self._key("alltoall", inp, out, algo, nch)):
+                return
+        try:
+            return self._alltoall_slow(inp, out, algo, nch)
+        finally:
+            self._rec_key = None
+
+    def _alltoall_slow(self, inp, out, algo, nch):
         ins, outs = self._lists(inp), self._lists(out)
         n = self.world_size
         if ins[0].shape[0] != n or outs[0].shape[0] != n:

@@ -272,8 +272,12 @@ def test_bounded_wait_reports_instead_of_hanging():
     cfg = Config.from_env(max_channels=2, num_blocks=2, buff_size=1 << 20, heap_bytes=64 << 20, scratch_bytes=1 << 20,
                           wait_timeout_ms=300)
     w = emulated(2, 0, cfg)
-    st = w.test_wait_timeout()
-    assert st.code == 5 and st.where == 10 and st.abort == 1
+    w.test_wait_timeout()
+    sts = [w.status(r) for r in range(2)]
+    # the rank whose budget ran out first reports the timeout (5) and raises the abort flag everywhere;
+    # the other one may notice that flag first and report "aborted by a peer" (6)
+    assert all(st.code in (5, 6) and st.where == 10 and st.abort == 1 for st in sts)
+    assert any(st.code == 5 for st in sts)
     with pytest.raises(CollectiveError):
         w.check()
     x = torch.ones(8, device="cuda")
