@@ -67,7 +67,7 @@ class Config:
     # algorithm / protocol selection
     algo: str = "auto"                    # ring | direct | nvls | ll | auto
     proto: str = "auto"                   # simple | ll128 | auto
-    max_channels: int = 32                # channels the FIFOs are sized for
+    max_channels: int = 16                # channels the FIFOs are sized for
     direct_ctas: int = 0                  # CTAs of direct/NVLS kernels (0 = by message size)
     simple_slots: int = 4
     ll128_slot_bytes: int = 128 << 10
@@ -82,7 +82,7 @@ class Config:
     # thresholds of the automatic choice (bytes)
     ll_max_bytes: int = 32 << 10
     ll128_max_bytes: int = 512 << 10
-    nvls_min_bytes: int = 256 << 10
+    nvls_min_bytes: int = 48 << 10
     spins_before_abort: int = 1000000     # common.py:106 (kept for parity; waits are time-bounded)
 
     @property
@@ -117,7 +117,7 @@ class Config:
             verbose=env_bool("MINTCCL_TEST_VERBOSE", False),
             algo=env_str("MINTCCL_ALGO", "auto", ("ring", "direct", "nvls", "ll", "auto")),
             proto=env_str("MINTCCL_PROTO", "auto", ("simple", "ll128", "auto")),
-            max_channels=env_int("MINTCCL_MAX_CHANNELS", 32),
+            max_channels=env_int("MINTCCL_MAX_CHANNELS", 16),
             direct_ctas=env_int("MINTCCL_DIRECT_CTAS", 0),
             simple_slots=env_int("MINTCCL_SIMPLE_SLOTS", 4),
             ll128_slot_bytes=env_int("MINTCCL_LL128_SLOT_BYTES", 128 << 10),
@@ -131,7 +131,7 @@ class Config:
             debug=env_str("MINTCCL_DEBUG", "warn", ("warn", "info", "trace")),
             ll_max_bytes=env_int("MINTCCL_LL_MAX_BYTES", 32 << 10),
             ll128_max_bytes=env_int("MINTCCL_LL128_MAX_BYTES", 512 << 10),
-            nvls_min_bytes=env_int("MINTCCL_NVLS_MIN_BYTES", 256 << 10),
+            nvls_min_bytes=env_int("MINTCCL_NVLS_MIN_BYTES", 48 << 10),
         )
         for k, v in overrides.items():
             if not hasattr(c, k):

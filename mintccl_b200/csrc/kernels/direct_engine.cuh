@@ -32,7 +32,9 @@ struct DirectArgs {
   uint64_t nbytes;               // AG/RS/A2A: bytes per shard; others: message bytes
   int32_t op;
   int32_t root;
-  int32_t variant;               // all-reduce: 0 two-shot, 1 one-shot; all-gather/all-to-all: 0 push, 1 pull
+  int32_t variant;               // all-reduce: 0 two-shot, 1 one-shot; all-gather/all-to-all: 0 push, 1 pull;
+                                 // broadcast: 0 root pushes, 1 peers pull, 2 scatter + all-gather;
+                                 // reduce: 0 root sums, 2 reduce-scatter + gather into the root
   int32_t nvls;                  // use multimem instructions
 };
 
@@ -187,19 +189,21 @@ __device__ __forceinline__ u128 mc_ld_reduce<BF16>(const void* p) { return multi
 template <>
 __device__ __forceinline__ u128 mc_ld_reduce<U8>(const void* p) { return load128(p); }
 
-// NVLS loops with several multimem operations in flight per thread.
+// NVLS loops with several multimem operations in flight per thread (a multimem round trip through the
+// switch is several microseconds, so the depth matters more than for plain peer loads).
+static constexpr int kNvlsUnroll = 8;
 // dst[i] = sum over all ranks of mc_src[i]; dst is local memory, or the multicast alias when TO_MC.
 template <class T, int NTHREADS, bool TO_MC>
 __device__ __forceinline__ void nvls_reduce_range(const uint8_t* mc_src, uint8_t* dst, uint64_t nvec) {
-  for (uint64_t base = 0; base < nvec; base += (uint64_t)NTHREADS * kDirectUnroll) {
-    u128 v[kDirectUnroll];
+  for (uint64_t base = 0; base < nvec; base += (uint64_t)NTHREADS * kNvlsUnroll) {
+    u128 v[kNvlsUnroll];
 #pragma unroll
-    for (int u = 0; u < kDirectUnroll; ++u) {
+    for (int u = 0; u < kNvlsUnroll; ++u) {
       const uint64_t i = base + (uint64_t)u * NTHREADS + threadIdx.x;
       if (i < nvec) v[u] = mc_ld_reduce<T>(mc_src + (i << 4));
     }
 #pragma unroll
-    for (int u = 0; u < kDirectUnroll; ++u) {
+    for (int u = 0; u < kNvlsUnroll; ++u) {
       const uint64_t i = base + (uint64_t)u * NTHREADS + threadIdx.x;
       if (i < nvec) {
         if (TO_MC) multimem_st_128(dst + (i << 4), v[u]);
@@ -209,17 +213,18 @@ __device__ __forceinline__ void nvls_reduce_range(const uint8_t* mc_src, uint8_t
   }
 }
 // mc_dst[i] (every rank's copy) = src[i]
-template <int NTHREADS>
+// COHERENT: src was written by a peer during this kernel, so it must not go through the read-only path.
+template <int NTHREADS, bool COHERENT = false>
 __device__ __forceinline__ void nvls_bcast_range(const uint8_t* src, uint8_t* mc_dst, uint64_t nvec) {
-  for (uint64_t base = 0; base < nvec; base += (uint64_t)NTHREADS * kDirectUnroll) {
-    u128 v[kDirectUnroll];
+  for (uint64_t base = 0; base < nvec; base += (uint64_t)NTHREADS * kNvlsUnroll) {
+    u128 v[kNvlsUnroll];
 #pragma unroll
-    for (int u = 0; u < kDirectUnroll; ++u) {
+    for (int u = 0; u < kNvlsUnroll; ++u) {
       const uint64_t i = base + (uint64_t)u * NTHREADS + threadIdx.x;
-      if (i < nvec) v[u] = load128_stream(src + (i << 4));
+      if (i < nvec) v[u] = COHERENT ? load128_relaxed_sys(src + (i << 4)) : load128_stream(src + (i << 4));
     }
 #pragma unroll
-    for (int u = 0; u < kDirectUnroll; ++u) {
+    for (int u = 0; u < kNvlsUnroll; ++u) {
       const uint64_t i = base + (uint64_t)u * NTHREADS + threadIdx.x;
       if (i < nvec) multimem_st_128(mc_dst + (i << 4), v[u]);
     }
@@ -326,6 +331,36 @@ __device__ void direct_body(const MtDevComm& c, const DirectArgs& a, int lr, int
     }
     case DOP_BROADCAST: {
       const MtRange r = mt_split(B, ncta, cta, kSplitAlignDirect);
+      if (a.variant == 2) {
+        // scatter + all-gather: the root hands sub-slice j to rank j, then every rank replicates its
+        // sub-slice (multimem.st, or plain stores to every peer).  One source can only inject so many
+        // multicast stores per second; spreading the replication over all ranks lifts that limit.
+        const uint64_t len = r.hi - r.lo;
+        if (me == a.root && len) {
+          for (int d = 1; d < n; ++d) {
+            const int j = (me + d) % n;
+            const MtRange sj = mt_split(len, n, j, 16);
+            if (sj.hi > sj.lo)
+              copy_range<NTHREADS, false, true>(in + r.lo + sj.lo, c.heap[j] + a.out_off + r.lo + sj.lo, sj.hi - sj.lo);
+          }
+        }
+        if (!rank_barrier(c, cta, s_fail)) return;
+        const MtRange sm = mt_split(len, n, me, 16);
+        if (sm.hi > sm.lo) {
+          const uint8_t* src = (me == a.root ? in : out) + r.lo + sm.lo;
+          const uint64_t nb = sm.hi - sm.lo;
+          if (a.nvls) {
+            nvls_bcast_range<NTHREADS, true>(src, c.mc + a.out_off + r.lo + sm.lo, nb >> 4);
+          } else {
+            for (int d = 1; d < n; ++d) {
+              const int p = (me + d) % n;
+              copy_range<NTHREADS, true, true>(src, c.heap[p] + a.out_off + r.lo + sm.lo, nb);
+            }
+            if (me == a.root && in != out) copy_range<NTHREADS, false, false>(src, out + r.lo + sm.lo, nb);
+          }
+        }
+        break;
+      }
       if (r.hi > r.lo) {
         if (a.nvls) {
           if (me == a.root) {
@@ -352,6 +387,22 @@ __device__ void direct_body(const MtDevComm& c, const DirectArgs& a, int lr, int
     }
     case DOP_REDUCE: {
       const MtRange r = mt_split(B, ncta, cta, kSplitAlignDirect);
+      if (a.variant == 2) {
+        // reduce-scatter + gather: rank j sums sub-slice j (in the switch, or by pulling from every peer)
+        // and stores the result straight into the root's output, so the summing is spread over all ranks
+        // and the root only receives.
+        const MtRange sm = mt_split(r.hi - r.lo, n, me, 16);
+        if (sm.hi > sm.lo) {
+          const uint64_t lo = r.lo + sm.lo, hi = r.lo + sm.hi;
+          uint8_t* dst = me == a.root ? out : c.heap[a.root] + a.out_off;
+          if (a.nvls) {
+            nvls_reduce_range<T, NTHREADS, false>(c.mc + a.in_off + lo, dst + lo, (hi - lo) >> 4);
+          } else {
+            pull_reduce_range<T, NTHREADS, false, false>(c, a.in_off, 0, dst, lo, hi, 0);
+          }
+        }
+        break;
+      }
       if (r.hi > r.lo && me == a.root) {
         if (a.nvls) {
           const uint64_t nvec = (r.hi - r.lo) >> 4;

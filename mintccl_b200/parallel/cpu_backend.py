@@ -36,15 +36,20 @@ class CpuCommunicator:
     def allreduce(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, **_) -> None:
         (out if out is not None else x).copy_(self._sum_fp32(x).to(x.dtype))
 
+    @staticmethod
+    def _raw(t: torch.Tensor) -> torch.Tensor:
+        """Byte view: gloo lacks some 16-bit types, and copies do not care about the element type."""
+        return t.view(torch.uint8) if t.is_contiguous() else t.contiguous().view(torch.uint8)
+
     def allgather(self, buff: torch.Tensor, inp: Optional[torch.Tensor] = None, mode: str = "temporal", **_) -> None:
-        mine = (inp if inp is not None else buff[self.rank]).contiguous()
+        mine = self._raw((inp if inp is not None else buff[self.rank]).contiguous()).reshape(-1)
         if self.world_size == 1:
-            buff[0].copy_(mine.view_as(buff[0]))
+            self._raw(buff[0]).reshape(-1).copy_(mine)
             return
         parts = [torch.empty_like(mine) for _ in range(self.world_size)]
         dist.all_gather(parts, mine, group=self.group)
         for r, p in enumerate(parts):
-            buff[r].copy_(p.view_as(buff[r]))
+            self._raw(buff[r]).reshape(-1).copy_(p)
 
     def reducescatter(self, buff: torch.Tensor, out: Optional[torch.Tensor] = None, mode: str = "temporal", **_) -> None:
         acc = self._sum_fp32(buff)
@@ -52,11 +57,7 @@ class CpuCommunicator:
 
     def broadcast(self, buff: torch.Tensor, root: int = 0, **_) -> None:
         if self.world_size > 1:
-            if buff.dtype in (torch.bfloat16, torch.float16):
-                raw = buff.view(torch.int16)
-                dist.broadcast(raw, src=root, group=self.group)
-            else:
-                dist.broadcast(buff, src=root, group=self.group)
+            dist.broadcast(self._raw(buff), src=root, group=self.group)
 
     def reduce(self, buff: torch.Tensor, root: int = 0, out: Optional[torch.Tensor] = None, **_) -> None:
         acc = self._sum_fp32(buff)
@@ -86,7 +87,7 @@ class CpuCommunicator:
         """Executes posted transfers.  Sends and receives are matched in posting order per pair."""
         reqs = []
         for kind, peer, buff in self._pending:
-            raw = buff.view(torch.uint8) if buff.dtype in (torch.bfloat16, torch.float16) else buff
+            raw = self._raw(buff)
             reqs.append(dist.isend(raw, peer, group=self.group) if kind == "send" else dist.irecv(raw, peer, group=self.group))
         for r in reqs:
             r.wait()
@@ -96,9 +97,9 @@ class CpuCommunicator:
     def sendrecv_route(self, route: Sequence[int], src, dst, nbytes=None, **_) -> None:
         route = list(route)
         if self.rank == route[0]:
-            dist.send(src.view(torch.uint8) if src.dtype in (torch.bfloat16, torch.float16) else src, route[-1], group=self.group)
+            dist.send(self._raw(src), route[-1], group=self.group)
         elif self.rank == route[-1]:
-            dist.recv(dst.view(torch.uint8) if dst.dtype in (torch.bfloat16, torch.float16) else dst, route[0], group=self.group)
+            dist.recv(self._raw(dst), route[0], group=self.group)
 
     def symm_empty(self, shape, dtype=torch.float32) -> torch.Tensor:
         return torch.empty(shape, dtype=dtype)

@@ -27,7 +27,7 @@ def main():
     from mintccl_b200 import Config
     rank, n = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
-    cfg = Config.from_env(heap_bytes=1 << 30, wait_timeout_ms=5000)
+    cfg = Config.from_env(heap_bytes=3 << 30, wait_timeout_ms=5000)
     c = mintccl_b200.Communicator(config=cfg)
     print(f"[r{rank}] heap={c.heap_kind} nvls={c.nvls} ring={c.ring}", flush=True)
     dtypes = [torch.float32, torch.float16, torch.bfloat16]
@@ -93,7 +93,7 @@ def main():
                 assert torch.equal(go[p], full[p][rank]), "alltoall"
             c.symm_free(gi)
             c.symm_free(go)
-            for algo in ["ring", "direct", "pull"] + (["nvls"] if c.nvls and (numel * srcs[0].element_size()) % 16 == 0 else []):
+            for algo in ["ring", "direct", "pull", "push"] + (["nvls", "nvls1"] if c.nvls and (numel * srcs[0].element_size()) % 16 == 0 else []):
                 b = c.symm_empty(numel, dtype)
                 b.copy_(srcs[rank])
                 torch.cuda.synchronize()
@@ -105,13 +105,23 @@ def main():
                 o = torch.zeros(numel, device="cuda", dtype=dtype)
                 torch.cuda.synchronize()
                 c.control.barrier()
-                if algo == "pull":
+                if algo in ("pull", "push"):
                     c.symm_free(b)
                     continue
                 c.reduce(b, root=0, out=o, algo=algo)
                 c.check()
                 if rank == 0:
                     close(o, ref, dtype, n if algo == "ring" else 1)
+                if algo in ("direct", "nvls"):  # symmetric output: summing spread over all ranks
+                    so = c.symm_zeros(numel, dtype)
+                    torch.cuda.synchronize()
+                    c.control.barrier()
+                    c.reduce(b, root=n - 1, out=so, algo=algo)
+                    c.check()
+                    if rank == n - 1:
+                        close(so, ref, dtype, 1)
+                    c.control.barrier()
+                    c.symm_free(so)
                 c.symm_free(b)
     # point to point: deferred API over a multi-hop ring route, direct pull and push, registered tensor
     os.environ["MINTCCL_ROUTE"] = "ring"

@@ -1,0 +1,141 @@
+"""CPU-only unit tests: configuration parsing, bandwidth formulas, topology search, timers."""
+import itertools
+import os
+
+import pytest
+
+import mintccl_b200 as m
+from mintccl_b200 import config as cfgmod
+from mintccl_b200.topology import _find_ring_py, _find_route_py, _matrix, ring_min_bandwidth, ring_plan
+from mintccl_b200.utils.busbw import algbw_gbs, busbw_factor, busbw_gbs
+
+
+def test_env_bool_parses_zero_as_false(monkeypatch):
+    # the reference's bool(os.getenv(...)) is true for "0" (common.py:113)
+    for v, want in [("0", False), ("false", False), ("", False), ("1", True), ("TRUE", True), ("on", True)]:
+        monkeypatch.setenv("MINTCCL_TEST_MODE", v)
+        assert cfgmod.env_bool("MINTCCL_TEST_MODE") is want
+    monkeypatch.setenv("MINTCCL_TEST_MODE", "maybe")
+    with pytest.raises(ValueError):
+        cfgmod.env_bool("MINTCCL_TEST_MODE")
+
+
+def test_config_defaults_match_reference_knobs(monkeypatch):
+    for k in list(os.environ):
+        if k.startswith("MINTCCL_"):
+            monkeypatch.delenv(k)
+    c = m.Config.from_env()
+    assert (c.num_blocks, c.num_warps, c.buff_size, c.test_count) == (16, 16, 4194304, 67108864)
+    assert m.WARP_SIZE == 32 and m.VECTORIZED_BYTES == 16 and m.NULL == 0
+    monkeypatch.setenv("MINTCCL_NUM_BLOCKS", "8")
+    monkeypatch.setenv("MINTCCL_BUFFSIZE", "1M")
+    monkeypatch.setenv("MINTCCL_ALGO", "ring")
+    c = m.Config.from_env()
+    assert c.num_blocks == 8 and c.buff_size == 1 << 20 and c.algo == "ring" and c.simple_slot_bytes == 256 << 10
+    monkeypatch.setenv("MINTCCL_BUFFSIZE", "3000000")
+    with pytest.raises(ValueError):
+        m.Config.from_env()
+    monkeypatch.setenv("MINTCCL_BUFFSIZE", "4M")
+    monkeypatch.setenv("MINTCCL_PROTO", "bogus")
+    with pytest.raises(ValueError):
+        m.Config.from_env()
+
+
+def test_busbw_formulas():
+    assert busbw_factor("allreduce", 8) == pytest.approx(1.75)
+    assert busbw_factor("allgather", 8) == pytest.approx(0.875)
+    assert busbw_factor("reducescatter", 4) == pytest.approx(0.75)
+    assert busbw_factor("alltoall", 2) == pytest.approx(0.5)
+    assert busbw_factor("broadcast", 8) == busbw_factor("reduce", 8) == busbw_factor("sendrecv", 8) == 1.0
+    assert algbw_gbs(1 << 30, 1e-3) == pytest.approx(1073.741824)
+    assert busbw_gbs("allreduce", 1 << 30, 1e-3, 8) == pytest.approx(1073.741824 * 1.75)
+    with pytest.raises(KeyError):
+        busbw_factor("gather", 2)
+
+
+def _topo(edges, n):
+    t = {i: [] for i in range(n)}
+    for a, b, bw in edges:
+        t[a].append((b, bw))
+        t[b].append((a, bw))
+    return {k: sorted(v, reverse=True) for k, v in t.items()}
+
+
+def _ring_ok(ring, n):
+    return len(ring) == n + 1 and ring[0] == ring[-1] and sorted(ring[:-1]) == list(range(n))
+
+
+def test_ring_and_route_on_synthetic_topologies():
+    # a line has no ring; routes go through the middle
+    line = _topo([(0, 1, 50.0), (1, 2, 25.0)], 3)
+    assert m.find_ring(line) == []
+    assert m.find_route(0, 2, line) == [0, 1, 2]
+    assert m.find_route(2, 2, line) == [2]
+    # ring of four: the only ring is the ring itself
+    sq = _topo([(0, 1, 50.0), (1, 2, 50.0), (2, 3, 50.0), (3, 0, 50.0)], 4)
+    r = m.find_ring(sq)
+    assert _ring_ok(r, 4) and ring_min_bandwidth(r, sq) == 50.0
+    assert m.find_route(0, 2, sq) in ([0, 1, 2], [0, 3, 2])
+    # a direct link wins when it is as wide as the detour, loses when it is narrower (widest path)
+    tri = _topo([(0, 1, 50.0), (1, 2, 50.0), (0, 2, 50.0)], 3)
+    assert m.find_route(0, 2, tri) == [0, 2]
+    tri2 = _topo([(0, 1, 50.0), (1, 2, 50.0), (0, 2, 10.0)], 3)
+    assert m.find_route(0, 2, tri2) == [0, 1, 2]
+    assert m.find_route(0, 2, tri2, shortest=True) == [0, 2]
+    # DGX-1 style hybrid cube mesh (V100 x8): double links inside quads, the best ring uses only them
+    dbl, sgl = 50.0, 25.0
+    edges = [(0, 3, dbl), (0, 4, dbl), (1, 2, dbl), (1, 5, dbl), (2, 3, dbl), (6, 7, dbl), (4, 7, dbl), (5, 6, dbl),
+             (0, 1, sgl), (0, 2, sgl), (1, 3, sgl), (2, 6, sgl), (3, 7, sgl), (4, 5, sgl), (4, 6, sgl), (5, 7, sgl)]
+    cube = _topo(edges, 8)
+    r = m.find_ring(cube)
+    assert _ring_ok(r, 8) and ring_min_bandwidth(r, cube) == dbl
+    # NVSwitch: uniform all-to-all, identity ring, direct routes
+    sw = m.uniform_topology(8)
+    assert m.find_ring(sw) == [0, 1, 2, 3, 4, 5, 6, 7, 0]
+    for a, b in itertools.permutations(range(8), 2):
+        assert m.find_route(a, b, sw) == [a, b]
+    assert ring_plan(m.find_ring(sw), 0) == (7, 1)
+    # disconnected
+    two = _topo([(0, 1, 50.0)], 3)
+    assert m.find_route(0, 2, two) == [] and m.find_ring(two) == []
+
+
+def test_native_and_python_searches_agree():
+    import random
+    rng = random.Random(7)
+    for trial in range(30):
+        n = rng.randint(3, 7)
+        edges = [(a, b, float(rng.choice([10, 25, 50]))) for a in range(n) for b in range(a + 1, n) if rng.random() < 0.7]
+        t = _topo(edges, n)
+        nodes, mat = _matrix(t)
+        ring_native = m.find_ring(t)
+        ring_py = _find_ring_py(mat, n)
+        assert (ring_native == []) == (ring_py == [])
+        if ring_native:
+            assert ring_min_bandwidth(ring_native, t) == ring_min_bandwidth(ring_py, t)
+        for s, d in [(0, n - 1), (1, 2)]:
+            a, b = m.find_route(s, d, t), _find_route_py(mat, n, s, d)
+            assert len(a) == len(b)
+            if a:
+                width = lambda p: min(dict(t[x])[y] for x, y in zip(p[:-1], p[1:]))  # noqa: E731
+                assert width(a) == width(b)
+
+
+def test_topology_cache_roundtrip(tmp_path):
+    import json
+    t = m.uniform_topology(4, 123.0)
+    f = tmp_path / "topo.json"
+    f.write_text(json.dumps(t))
+    assert m.get_topology(str(f)) == t
+    # without a GPU and without a cache the topology is the uniform one
+    assert m.get_topology(str(tmp_path / "none.json"), ndev=2) in (m.uniform_topology(2), m.get_topology(str(tmp_path / "none.json"), ndev=2))
+
+
+def test_timer_host(capsys):
+    with m.Timer(rank=3) as t:
+        sum(range(1000))
+    assert t.elapsed > 0
+    assert "# rank: 3 time:" in capsys.readouterr().out
+    with m.Timer(quiet=True):
+        pass
+    assert capsys.readouterr().out == ""

@@ -1,0 +1,156 @@
+"""CPU-only tests of the protocol layer: LL128 wire format against a NumPy oracle, the index arithmetic
+shared by kernels and host, the host-side simulator (deadlock-freedom, 1,000 back-to-back operations,
+fault injection) and descriptor passing between processes."""
+import ctypes as C
+import multiprocessing as mp
+import os
+
+import numpy as np
+import pytest
+
+from mintccl_b200 import _native as N
+from mintccl_b200.ops import ll128_ref as ll
+
+lib = N.lib()
+lib.mt_sched_split.argtypes = [C.c_uint64, C.c_uint32, C.c_uint32, C.c_uint64, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
+lib.mt_sched_ll128_lines.restype = C.c_uint64
+lib.mt_sched_ll128_lines.argtypes = [C.c_uint64]
+lib.mt_sched_ll128_line_of.restype = C.c_uint32
+lib.mt_sched_ll128_line_of.argtypes = [C.c_uint32, C.c_uint32]
+lib.mt_sim_run.restype = C.c_int
+lib.mt_sim_run.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint64, C.c_int, C.c_int, C.POINTER(C.c_int), C.c_int,
+                           C.POINTER(C.c_int), C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint32, C.c_uint64, C.c_uint32,
+                           C.POINTER(N.MtStatus)]
+
+
+def sim(n, nch, proto, op, count, root=0, spatial=0, chain=None, ring=None, iters=1, jitter=0, dead=-1, timeout_ms=4000,
+        seed=1, slot_bytes=4096, slots=2):
+    chain = chain or []
+    ch = (C.c_int * 9)(*chain)
+    rg = (C.c_int * 8)(*(ring or list(range(n))))
+    st = (N.MtStatus * 8)()
+    rc = lib.mt_sim_run(n, nch, proto, op, count, root, spatial, ch, len(chain), rg, iters, jitter, dead, timeout_ms, seed,
+                        slot_bytes, slots, st)
+    return rc, st
+
+
+@pytest.mark.parametrize("nbytes", [1, 8, 119, 120, 121, 127, 128, 129, 239, 240, 241, 1919, 1920, 1921, 5000])
+def test_ll128_pack_unpack_roundtrip(nbytes):
+    rng = np.random.default_rng(nbytes)
+    payload = rng.integers(0, 256, nbytes, dtype=np.uint8).tobytes()
+    wire = ll.pack(payload, flag=77)
+    assert len(wire) % ll.WARP_WIRE == 0
+    assert ll.valid(wire, nbytes, 77) and not ll.valid(wire, nbytes, 78)
+    assert ll.unpack(wire, nbytes) == payload
+    assert ll.wire_lines(min(nbytes, ll.WARP_PAYLOAD)) == lib.mt_sched_ll128_lines(min(nbytes, ll.WARP_PAYLOAD))
+
+
+def test_ll128_geometry_matches_native():
+    seen = set()
+    for pair in range(8):
+        for half in range(2):
+            a, b = ll.line_of(pair, half), lib.mt_sched_ll128_line_of(pair, half)
+            assert a == b
+            seen.add(a)
+    assert seen == set(range(16))  # the 16 lines of a warp chunk, each used once
+    assert ll.efficiency() == 0.9375
+    # bytes [120, 128) of a pair travel in the flag lane of the second line: 121..128 bytes need two lines
+    assert [ll.wire_lines(x) for x in (0, 1, 120, 121, 128, 240, 241)] == [0, 1, 1, 2, 2, 2, 3]
+
+
+def test_split_covers_message_without_gaps():
+    for total in (0, 1, 127, 128, 129, 4096, 1_000_003, (1 << 30) + 5):
+        for parts in (1, 3, 16, 148):
+            prev = 0
+            for i in range(parts):
+                lo, hi = C.c_uint64(), C.c_uint64()
+                lib.mt_sched_split(total, parts, i, 128, C.byref(lo), C.byref(hi))
+                assert lo.value == prev and hi.value >= lo.value
+                if hi.value < total:
+                    assert hi.value % 128 == 0
+                prev = hi.value
+            assert prev == total
+
+
+def test_ring_schedule_visits_every_shard_once():
+    lib.mt_sched_ag_shard.restype = C.c_int
+    lib.mt_sched_rs_shard.restype = C.c_int
+    for n in (2, 3, 4, 8):
+        for q in range(n):
+            assert sorted(lib.mt_sched_ag_shard(q, j, n) for j in range(n)) == list(range(n))
+            assert sorted(lib.mt_sched_rs_shard(q, j, n) for j in range(n)) == list(range(n))
+            assert lib.mt_sched_ag_shard(q, 0, n) == q            # all-gather starts with the own shard
+            assert lib.mt_sched_rs_shard(q, n - 1, n) == q        # reduce-scatter ends with the own shard
+            # what q sends at step j is what q+1 receives at step j+1
+            for j in range(n - 1):
+                assert lib.mt_sched_ag_shard(q, j, n) == lib.mt_sched_ag_shard((q + 1) % n, j + 1, n)
+                assert lib.mt_sched_rs_shard(q, j, n) == lib.mt_sched_rs_shard((q + 1) % n, j + 1, n)
+
+
+OPS = {"sendrecv": 0, "broadcast": 1, "reduce": 2, "allgather": 3, "reducescatter": 4, "allreduce": 5}
+
+
+@pytest.mark.parametrize("n", [2, 4, 8])
+@pytest.mark.parametrize("proto", [0, 1])
+@pytest.mark.parametrize("op", ["broadcast", "reduce", "allgather", "reducescatter", "allreduce"])
+def test_simulated_collectives_all_sizes(n, proto, op):
+    for count in (1, 30, 31, 32, 61, 1000, 5003):
+        for spatial in ((0, 1) if op in ("allgather", "reducescatter") else (0,)):
+            nch = n if spatial else 3
+            rc, st = sim(n, nch, proto, OPS[op], count, root=n - 1, spatial=spatial, jitter=20, seed=count)
+            assert rc == 0, (op, count, spatial, [(s.code, s.where) for s in st[:n]])
+
+
+def test_simulated_multihop_thousand_back_to_back():
+    """rank 0 -> 4 through 1, 2, 3 on a permuted ring, 1,000 operations in a row on two-slot FIFOs:
+    counters keep growing, nothing is cleared, nothing deadlocks (the reference documents a deadlock on
+    eight GPUs, README.md:62-63)."""
+    for proto in (0, 1):
+        rc, st = sim(8, 2, proto, OPS["sendrecv"], 600, chain=[0, 1, 2, 3, 4], iters=1000, jitter=0, slot_bytes=2048)
+        assert rc == 0, [(s.code, s.where, s.step) for s in st[:8]]
+
+
+def test_simulated_allreduce_eight_ranks_many_iterations_with_jitter():
+    for proto in (0, 1):
+        rc, _ = sim(8, 4, proto, OPS["allreduce"], 7001, iters=60, jitter=30, ring=[3, 1, 4, 0, 5, 7, 2, 6], slot_bytes=2048)
+        assert rc == 0
+
+
+@pytest.mark.parametrize("proto", [0, 1])
+def test_injected_dead_rank_is_reported_not_hung(proto):
+    """A rank that never joins: every rank that depends on it gives up after its budget, records who was
+    waiting for what, and raises the abort flag on its peers.  Nothing spins forever."""
+    rc, st = sim(4, 2, proto, OPS["allreduce"], 4000, dead=2, timeout_ms=300)
+    assert rc == 2
+    codes = [st[r].code for r in range(4)]
+    assert codes[2] == 0                      # the dead rank reported nothing
+    assert all(c in (1, 2, 3, 6) for i, c in enumerate(codes) if i != 2) and any(c in (1, 2, 3) for c in codes)
+    assert all(st[r].abort == 1 for r in range(4))
+
+
+def _fd_child(name, q):
+    from mintccl_b200 import _native as N2
+    L = N2.lib()
+    r, w = os.pipe()
+    os.write(w, b"hello from child")
+    assert L.mt_fd_send(name.encode(), 42, r, 5000) == 0
+    q.put("sent")
+
+
+def test_fd_passing_between_processes():
+    name = f"mintccl-test-{os.getpid()}"
+    sock = lib.mt_fd_listen(name.encode())
+    assert sock >= 0
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    p = ctx.Process(target=_fd_child, args=(name, q))
+    p.start()
+    tag = C.c_int(-1)
+    fd = lib.mt_fd_accept(sock, C.byref(tag), 20000)
+    assert fd >= 0 and tag.value == 42
+    assert os.read(fd, 64) == b"hello from child"
+    os.close(fd)
+    assert q.get(timeout=20) == "sent"
+    p.join(20)
+    lib.mt_fd_close(sock)
+    assert lib.mt_fd_accept(sock, C.byref(tag), 10) < 0  # closed socket: clean failure, no hang

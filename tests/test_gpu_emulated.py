@@ -235,16 +235,25 @@ def test_direct_collectives(n, numel):
         # broadcast and reduce
         for r in range(n):
             gb[r].view(-1).copy_(full[r])
-        w.broadcast(gb, root=n - 1, algo="direct")
-        w.check()
-        for r in range(n):
-            assert torch.equal(gb[r].view(-1), full[n - 1])
+        for algo in ("direct", "push", "pull"):
+            for r in range(n):
+                gb[r].view(-1).copy_(full[r])
+            w.broadcast(gb, root=n - 1, algo=algo)
+            w.check()
+            for r in range(n):
+                assert torch.equal(gb[r].view(-1), full[n - 1]), algo
         for r in range(n):
             gb[r].view(-1).copy_(full[r])
         routs = [torch.zeros(n, numel, device="cuda", dtype=dtype) for _ in range(n)]
         w.reduce(gb, root=1, out=routs, algo="direct")
         w.check()
         assert_sum_close(routs[1].view(-1), oracle_sum(full), dtype)
+        # symmetric output: every rank sums one sub-slice and stores it into the root's buffer
+        for o in ob:
+            o.zero_()
+        w.reduce(gb, root=0, out=ob, algo="direct")
+        w.check()
+        assert_sum_close(ob[0].view(-1), oracle_sum(full), dtype)
         w.symm_free(gb)
         w.symm_free(ob)
 
