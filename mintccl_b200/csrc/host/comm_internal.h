@@ -1,0 +1,46 @@
+// Host-side state of a communicator, shared by the translation units of the runtime.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string>
+#include <vector>
+
+#include "../mintccl.h"
+
+struct MtComm {
+  int rank = 0, nranks = 1, device = 0, nlocal = 1;
+  bool emulated = false;
+  int heap_kind = 0;
+  MtConfig cfg{};
+  MtHeapLayout L{};
+  uint64_t heap_bytes = 0;                 // rounded to the allocation granularity
+  uint64_t timeout_ns = 0;
+  // [local rank][peer] -> heap base in this process
+  uint8_t* heap[MT_MAX_RANKS][MT_MAX_RANKS] = {};
+  // VMM bookkeeping (real mode)
+  CUmemGenericAllocationHandle local_handle = 0;
+  CUmemGenericAllocationHandle peer_handle[MT_MAX_RANKS] = {};
+  bool peer_mapped[MT_MAX_RANKS] = {};
+  bool own_vmm = false;
+  void* ipc_opened[MT_MAX_RANKS] = {};
+  // multicast
+  CUmemGenericAllocationHandle mc_handle = 0;
+  bool mc_have_handle = false, mc_bound = false;
+  uint8_t* mc = nullptr;
+  int ring[MT_MAX_RANKS] = {};
+  MtDevComm h_comms[MT_MAX_RANKS];
+  MtDevComm* d_comms = nullptr;
+  uint64_t p2p_seq[MT_MAX_RANKS][MT_MAX_RANKS] = {};
+  uint64_t p2p_done[MT_MAX_RANKS][MT_MAX_RANKS] = {};
+  int ll_grid = 4;
+  uint64_t gemm_epoch[2] = {0, 0};         // call counters of the fused GEMM flag sets (AG, RS)
+  std::vector<void*> emu_allocs;
+};
+
+namespace mthost {
+// Records an error message for mt_last_error() and returns -1.
+int fail(const std::string& m);
+// Looks a driver entry point up through the runtime (no link-time dependency on the driver library).
+void* driver_entry(const char* name);
+}  // namespace mthost

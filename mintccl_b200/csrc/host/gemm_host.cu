@@ -1,0 +1,161 @@
+// Host side of the tcgen05 GEMM kernels: TMA descriptors, argument checks, launches.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <string.h>
+
+#include <string>
+
+#include "../kernels/gemm_tc.h"
+#include "comm_internal.h"
+
+using mthost::fail;
+
+namespace {
+
+constexpr int kBM = 128, kBN = 256, kBK = 64;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// [rows, K] bf16 row-major, tiles of box_rows x 64 elements, 128-byte swizzle.
+int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K, uint32_t box_rows) {
+  static EncodeTiledFn enc = (EncodeTiledFn)mthost::driver_entry("cuTensorMapEncodeTiled");
+  if (!enc) return fail("cuTensorMapEncodeTiled not available");
+  if (((uintptr_t)base & 15) || (K * 2) % 16) return fail("GEMM operands must be 16-byte aligned with K a multiple of 8");
+  cuuint64_t dims[2] = {K, rows};
+  cuuint64_t strides[1] = {K * 2};
+  cuuint32_t box[2] = {(cuuint32_t)kBK, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)base, dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled failed: CUresult " + std::to_string((int)r));
+  return 0;
+}
+
+int check_shape(int M, int N, int K, int nranks) {
+  if (M <= 0 || N <= 0 || K <= 0) return fail("bad GEMM shape");
+  if (M % (kBM * nranks) || N % kBN || K % kBK)
+    return fail("GEMM shape: M must be a multiple of 128 x ranks, N of 256, K of 64");
+  return 0;
+}
+
+int sm_count(int device) {
+  int n = 148;
+  cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device);
+  return n;
+}
+
+}  // namespace
+
+extern "C" {
+
+// C[M, ldc] = A[M, K] * B[N, K]^T in bf16 with fp32 accumulation, on the current device.
+int mt_gemm(void* stream, const void* A, const void* B, void* C, int M, int N, int K, int ldc, int nctas) {
+  if (check_shape(M, N, K, 1)) return -1;
+  if (ldc < N || ldc % 8 || ((uintptr_t)C & 15)) return fail("C must be 16-byte aligned with ldc >= N, ldc % 8 == 0");
+  int dev = 0;
+  cudaGetDevice(&dev);
+  mt::GemmMaps maps;
+  memset(&maps, 0, sizeof(maps));
+  if (make_map(&maps.a[0], A, M, K, kBM) || make_map(&maps.b[0], B, N, K, kBN)) return -1;
+  maps.a2[0] = maps.a[0];
+  mt::GemmArgs a;
+  memset(&a, 0, sizeof(a));
+  a.c[0] = C;
+  a.M = M;
+  a.N = N;
+  a.K = K;
+  a.ldc = ldc;
+  a.nranks = 1;
+  a.timeout_ns = 4000000000ull;
+  const int tiles = (M / kBM) * (N / kBN);
+  int grid = nctas > 0 ? nctas : sm_count(dev);
+  if (grid > tiles) grid = tiles;
+  cudaError_t e = mt::launch_gemm_tc(mt::MODE_PLAIN, maps, a, grid, 1, (cudaStream_t)stream);
+  if (e != cudaSuccess) return fail(std::string("gemm launch: ") + cudaGetErrorString(e));
+  return 0;
+}
+
+static int fused_common(MtComm* c, mt::GemmArgs& a, int M, int N, int K, uint64_t flags_off, uint64_t epoch) {
+  if (!c || !c->d_comms) return fail("communicator is not finalized");
+  if (check_shape(M, N, K, c->nranks)) return -1;
+  memset(&a, 0, sizeof(a));
+  a.M = M;
+  a.N = N;
+  a.K = K;
+  a.nranks = c->nranks;
+  a.comms = c->d_comms;
+  a.flags_off = flags_off;
+  a.epoch = epoch;
+  a.timeout_ns = c->timeout_ns;
+  for (int lr = 0; lr < c->nlocal; ++lr) {
+    const int r = c->emulated ? lr : c->rank;
+    a.rank[lr] = r;
+    a.status[lr] = c->heap[lr][r] + c->L.status_off;
+  }
+  return 0;
+}
+
+// C[M, ldc] = allgather(a_shard)[M, K] * B[N, K]^T.  `gather_off`: symmetric buffer of M * K bf16;
+// `flags_off`: symmetric u64 counters [ranks][M / ranks / 128], zero before the first call; `epoch`: 1 on the
+// first call on these counters, then 2, 3, ...; `ncomm` must not change between calls on the same counters.
+int mt_ag_gemm(MtComm* c, void* stream, const void* const* a_shard, const void* const* B, void* const* C,
+               uint64_t gather_off, uint64_t flags_off, uint64_t epoch, int M, int N, int K, int ldc, int ncomm,
+               int nctas) {
+  mt::GemmArgs a;
+  if (fused_common(c, a, M, N, K, flags_off, epoch)) return -1;
+  if (ldc < N || ldc % 8) return fail("ldc must be >= N and a multiple of 8");
+  const int n = c->nranks;
+  if (n == 1) ncomm = 0;
+  else if (ncomm < 1 || ncomm > 64) return fail("ncomm out of range");
+  int grid = nctas > 0 ? nctas : sm_count(c->device);
+  if (c->emulated && grid * c->nlocal > sm_count(c->device)) grid = sm_count(c->device) / c->nlocal;
+  if (grid <= ncomm) return fail("not enough CTAs for the requested comm CTAs");
+  if (ncomm > MT_MAX_BAR_SLOTS) return fail("too many comm CTAs");
+  a.ldc = ldc;
+  a.ncomm = ncomm;
+  a.gather_off = gather_off;
+  mt::GemmMaps maps;
+  memset(&maps, 0, sizeof(maps));
+  for (int lr = 0; lr < c->nlocal; ++lr) {
+    const int r = a.rank[lr];
+    a.c[lr] = C[lr];
+    a.a_local[lr] = a_shard[lr];
+    a.flags_local[lr] = c->heap[lr][r] + flags_off;
+    if (make_map(&maps.a[lr], c->heap[lr][r] + gather_off, M, K, kBM) || make_map(&maps.b[lr], B[lr], N, K, kBN) ||
+        make_map(&maps.a2[lr], a_shard[lr], M / n, K, kBM))
+      return -1;
+    if ((uintptr_t)C[lr] & 15) return fail("C must be 16-byte aligned");
+  }
+  cudaError_t e = mt::launch_gemm_tc(mt::MODE_AG_GEMM, maps, a, grid, c->nlocal, (cudaStream_t)stream);
+  if (e != cudaSuccess) return fail(std::string("ag_gemm launch: ") + cudaGetErrorString(e));
+  return 0;
+}
+
+// out[M / ranks, N] = reduce_scatter over rows of (A[M, K] * B[N, K]^T), K being this rank's slice of the
+// contraction.  `stage_off`: symmetric buffer of ranks * (M / ranks) * N bf16 partial tiles;
+// `flags_off`: symmetric u64 counters [ranks][M / ranks / 128][N / 256], zero before the first call.
+int mt_gemm_rs(MtComm* c, void* stream, const void* const* A, const void* const* B, void* const* out,
+               uint64_t stage_off, uint64_t flags_off, uint64_t epoch, int M, int N, int K, int nctas) {
+  mt::GemmArgs a;
+  if (fused_common(c, a, M, N, K, flags_off, epoch)) return -1;
+  int grid = nctas > 0 ? nctas : sm_count(c->device);
+  if (c->emulated && grid * c->nlocal > sm_count(c->device)) grid = sm_count(c->device) / c->nlocal;
+  a.ldc = N;
+  a.stage_off = stage_off;
+  mt::GemmMaps maps;
+  memset(&maps, 0, sizeof(maps));
+  for (int lr = 0; lr < c->nlocal; ++lr) {
+    a.c[lr] = out[lr];
+    if (make_map(&maps.a[lr], A[lr], M, K, kBM) || make_map(&maps.b[lr], B[lr], N, K, kBN)) return -1;
+    maps.a2[lr] = maps.a[lr];
+    if ((uintptr_t)out[lr] & 15) return fail("out must be 16-byte aligned");
+  }
+  cudaError_t e = mt::launch_gemm_tc(mt::MODE_GEMM_RS, maps, a, grid, c->nlocal, (cudaStream_t)stream);
+  if (e != cudaSuccess) return fail(std::string("gemm_rs launch: ") + cudaGetErrorString(e));
+  return 0;
+}
+
+}  // extern "C"

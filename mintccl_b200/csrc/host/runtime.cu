@@ -57,34 +57,11 @@ F drv(const char* name) {
 
 }  // namespace
 
-struct MtComm {
-  int rank = 0, nranks = 1, device = 0, nlocal = 1;
-  bool emulated = false;
-  int heap_kind = 0;
-  MtConfig cfg{};
-  MtHeapLayout L{};
-  uint64_t heap_bytes = 0;                 // rounded to the allocation granularity
-  uint64_t timeout_ns = 0;
-  // [local rank][peer] -> heap base in this process
-  uint8_t* heap[MT_MAX_RANKS][MT_MAX_RANKS] = {};
-  // VMM bookkeeping (real mode)
-  CUmemGenericAllocationHandle local_handle = 0;
-  CUmemGenericAllocationHandle peer_handle[MT_MAX_RANKS] = {};
-  bool peer_mapped[MT_MAX_RANKS] = {};
-  bool own_vmm = false;
-  void* ipc_opened[MT_MAX_RANKS] = {};
-  // multicast
-  CUmemGenericAllocationHandle mc_handle = 0;
-  bool mc_have_handle = false, mc_bound = false;
-  uint8_t* mc = nullptr;
-  int ring[MT_MAX_RANKS] = {};
-  MtDevComm h_comms[MT_MAX_RANKS];
-  MtDevComm* d_comms = nullptr;
-  uint64_t p2p_seq[MT_MAX_RANKS][MT_MAX_RANKS] = {};
-  uint64_t p2p_done[MT_MAX_RANKS][MT_MAX_RANKS] = {};
-  int ll_grid = 4;
-  std::vector<void*> emu_allocs;
-};
+#include "comm_internal.h"
+namespace mthost {
+int fail(const std::string& m) { return ::fail(m); }
+void* driver_entry(const char* name) { return (void*)drv<void*>(name); }
+}  // namespace mthost
 
 namespace mt {
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }

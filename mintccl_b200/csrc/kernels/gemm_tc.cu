@@ -1,0 +1,463 @@
+// Persistent bf16 GEMM on the 5th-generation tensor cores, and its two fusions with a collective:
+//
+//   MODE_PLAIN    C[M,N]  = A[M,K] * B[N,K]^T
+//   MODE_AG_GEMM  C[M,N]  = allgather(A_shard)[M,K] * B[N,K]^T       (column-parallel layer, sequence
+//                 parallel input): a few "comm" CTAs push this rank's rows into every peer's gathered
+//                 buffer chunk by chunk and count each chunk on the peer; the TMA producer of a GEMM CTA
+//                 waits for the count of the row block it is about to load.  Rows are consumed in arrival
+//                 order (own rows first), so transfer and MMA overlap tile by tile.
+//   MODE_GEMM_RS  out[M/n,N] = reduce_scatter(A[M,K_local] * B[N,K_local]^T)   (row-parallel layer):
+//                 tiles whose rows belong to other ranks are computed first; the epilogue writes each
+//                 partial tile straight into the owner's staging area over NVLink and counts it there;
+//                 when a CTA runs out of tiles it turns into a reducer that waits for the partial tiles
+//                 of one output tile, sums them in fp32 and writes the result.
+//
+// One CTA = 192 threads: warp 0 issues TMA loads (4-stage ring of 128x64 A and 256x64 B tiles, 128-byte
+// swizzle), warp 1 owns TMEM (512 columns: two 128x256 fp32 accumulators) and issues tcgen05.mma from a
+// single thread, warps 2..5 are the epilogue (tcgen05.ld, fp32 -> bf16, transposed through shared
+// memory so that global / peer stores are full 128-byte lines).  Every wait is bounded; on expiry the
+// CTA records an error, drains, frees its TMEM and returns.
+//
+// The reference has no counterpart: its README asks that collectives be "fused with other kernels"
+// (README.md:5) and stops there.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "../device/prims.cuh"
+#include "../device/sched.h"
+#include "../device/tc_prims.cuh"
+#include "gemm_tc.h"
+#include "launch.h"
+
+namespace mt {
+using namespace tc;
+
+constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16, STAGES = 4;
+constexpr int kGemmThreads = 192;
+constexpr uint32_t A_TILE_BYTES = BM * BK * 2, B_TILE_BYTES = BN * BK * 2;
+constexpr uint32_t STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
+constexpr int EPI_PITCH = 144;                      // bytes per staged row: 64 bf16 + 16 bytes of padding
+constexpr uint32_t EPI_BYTES = 4 * 32 * EPI_PITCH;  // 4 epilogue warps x 32 rows
+constexpr uint32_t SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + 256;
+constexpr uint32_t TMEM_COLS = 512;
+
+struct SharedCtl {
+  uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], drain;
+  uint32_t tmem_base;
+  int abort;
+};
+
+// Bounded mbarrier wait.  Returns false after the budget or when the CTA-wide abort flag is up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, uint64_t timeout_ns) {
+  uint32_t spins = 0;
+  uint64_t t0 = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 0x3ffu) == 0) {
+      if (*abort_flag) return false;
+      const uint64_t now = globaltimer();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > timeout_ns) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void gemm_report(const GemmArgs& a, int lr, uint32_t where) {
+  if (a.status[lr]) {
+    MtStatus* st = (MtStatus*)a.status[lr];
+    if (atomicCAS(&st->code, 0u, (uint32_t)MT_ERR_TIMEOUT_FLAG) == 0u) {
+      st->rank = a.rank[lr];
+      st->channel = blockIdx.x;
+      st->where = where;
+    }
+    store32_relaxed_sys(&st->abort, 1u);
+  }
+}
+
+// Tile order.  PLAIN: row-major over (m block, n block).  AG_GEMM: row blocks of rank r, r-1, r-2, ...
+// (arrival order of the pushes).  GEMM_RS: row blocks of rank r+1, r+2, ..., r (remote owners first).
+struct TileCoord {
+  int mb, nb, owner;
+};
+template <int MODE>
+__device__ __forceinline__ TileCoord tile_coord(const GemmArgs& a, int lr, int t) {
+  const int nbs = a.N / BN;
+  TileCoord c;
+  c.nb = t % nbs;
+  int mi = t / nbs;
+  if (MODE == MODE_PLAIN) {
+    c.mb = mi;
+    c.owner = 0;
+  } else {
+    const int per = (a.M / a.nranks) / BM;  // row blocks per rank
+    const int d = mi / per, j = mi % per;
+    c.owner = MODE == MODE_AG_GEMM ? mt_mod(a.rank[lr] - d, a.nranks) : mt_mod(a.rank[lr] + 1 + d, a.nranks);
+    c.mb = c.owner * per + j;
+  }
+  return c;
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_constant__ GemmMaps maps, GemmArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  const int lr = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * A_TILE_BYTES;
+  uint8_t* sEpi = smem + STAGES * STAGE_BYTES;
+  SharedCtl* ctl = (SharedCtl*)(sEpi + EPI_BYTES);
+  const int ncomm = MODE == MODE_AG_GEMM ? a.ncomm : 0;
+  const int ngemm = gridDim.x - ncomm;
+  const uint64_t timeout_ns = a.timeout_ns;
+
+  // ---------------------------------------------------------------- comm CTAs of the all-gather fusion
+  if (MODE == MODE_AG_GEMM && (int)blockIdx.x >= ngemm) {
+    const MtDevComm& c = a.comms[lr];
+    __shared__ int s_fail;
+    const int cc = blockIdx.x - ngemm;
+    // every rank has entered this call, so nobody still reads last call's gathered rows
+    if (!rank_barrier(c, cc, &s_fail)) return;
+    const int n = c.nranks, me = c.rank;
+    const uint64_t row_bytes = (uint64_t)a.K * 2;
+    const uint64_t shard_rows = a.M / n;
+    const int chunks = (int)(shard_rows / BM);
+    const uint8_t* src = (const uint8_t*)a.a_local[lr];
+    for (int d = 1; d < n; ++d) {
+      const int p = (me + d) % n;
+      uint8_t* dst = c.heap[p] + a.gather_off + (uint64_t)me * shard_rows * row_bytes;
+      uint64_t* cnt = (uint64_t*)(c.heap[p] + a.flags_off) + (uint64_t)me * chunks;
+      for (int ci = 0; ci < chunks; ++ci) {
+        const uint64_t chunk_bytes = (uint64_t)BM * row_bytes;
+        const MtRange r = mt_split(chunk_bytes, ncomm, cc, 128);
+        const uint64_t base = (uint64_t)ci * chunk_bytes;
+        const uint64_t nvec = (r.hi - r.lo) >> 4;
+        for (uint64_t i0 = 0; i0 < nvec; i0 += (uint64_t)kGemmThreads * 8) {
+          u128 v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const uint64_t i = i0 + (uint64_t)u * kGemmThreads + threadIdx.x;
+            if (i < nvec) v[u] = load128_stream(src + base + r.lo + (i << 4));
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const uint64_t i = i0 + (uint64_t)u * kGemmThreads + threadIdx.x;
+            if (i < nvec) store128_relaxed_sys(dst + base + r.lo + (i << 4), v[u]);
+          }
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+          fence_acq_rel_sys();
+          asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(cnt + ci), "l"(1ull) : "memory");
+        }
+      }
+    }
+    return;
+  }
+
+  // ---------------------------------------------------------------- GEMM CTAs: set-up
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&ctl->full[s], 1);
+      mbar_init(&ctl->empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&ctl->acc_full[s], 1);
+      mbar_init(&ctl->acc_empty[s], 4);  // one arrival per epilogue warp
+    }
+    mbar_init(&ctl->drain, 1);
+    ctl->abort = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&maps.a[lr]);
+    tma_prefetch_desc(&maps.b[lr]);
+    if (MODE == MODE_AG_GEMM) tma_prefetch_desc(&maps.a2[lr]);
+  }
+  if (warp == 1) {
+    tmem_alloc(&ctl->tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+  volatile int* abort_flag = &ctl->abort;
+
+  const int total_tiles = (a.M / BM) * (a.N / BN);
+  const int kblocks = a.K / BK;
+  const int first = blockIdx.x;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (one lane)
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int t = first; t < total_tiles && !*abort_flag; t += ngemm) {
+        const TileCoord tc_ = tile_coord<MODE>(a, lr, t);
+        const CUtensorMap* amap = &maps.a[lr];
+        int arow = tc_.mb * BM;
+        if (MODE == MODE_AG_GEMM) {
+          if (tc_.owner == a.rank[lr]) {
+            amap = &maps.a2[lr];  // own rows come straight from the local shard
+            arow = tc_.mb * BM - tc_.owner * (a.M / a.nranks);
+          } else {
+            // rows pushed by `owner`: wait until all comm CTAs of that rank have counted this block in
+            const int per = (a.M / a.nranks) / BM;
+            const uint64_t* cnt = (const uint64_t*)a.flags_local[lr] + (uint64_t)tc_.owner * per + (tc_.mb % per);
+            const uint64_t want = a.epoch * (uint64_t)a.ncomm;
+            uint32_t spins = 0;
+            uint64_t t0 = 0;
+            while (load64_acquire_sys(cnt) < want) {
+              if ((++spins & 0xffu) == 0) {
+                const uint64_t now = globaltimer();
+                if (t0 == 0) t0 = now;
+                else if (now - t0 > timeout_ns || *abort_flag) {
+                  *abort_flag = 1;
+                  gemm_report(a, lr, MT_WHERE_GEMM_FLAG);
+                  break;
+                }
+              }
+            }
+            if (*abort_flag) break;
+            fence_proxy_async_global();  // peer stores (generic proxy) before our TMA reads (async proxy)
+          }
+        }
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+          if (!mbar_wait(&ctl->empty[s], ph ^ 1, abort_flag, timeout_ns)) break;
+          mbar_expect_tx(&ctl->full[s], STAGE_BYTES);
+          tma_load_2d(sA + s * A_TILE_BYTES, amap, kb * BK, arow, &ctl->full[s]);
+          tma_load_2d(sB + s * B_TILE_BYTES, &maps.b[lr], kb * BK, tc_.nb * BN, &ctl->full[s]);
+        }
+      }
+      if (*abort_flag) {
+        // copies this thread issued may still be landing in shared memory: give them a bounded time
+        const uint64_t t0 = globaltimer();
+        while (globaltimer() - t0 < 100000ull) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (one lane)
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN);
+      uint32_t it = 0, tile_i = 0;
+      for (int t = first; t < total_tiles && !*abort_flag; t += ngemm, ++tile_i) {
+        const uint32_t as = tile_i & 1, aph = (tile_i >> 1) & 1;
+        if (!mbar_wait(&ctl->acc_empty[as], aph ^ 1, abort_flag, timeout_ns)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + as * BN;
+        bool ok = true;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+          if (!mbar_wait(&ctl->full[s], ph, abort_flag, timeout_ns)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint64_t da = make_smem_desc_sw128(sA + s * A_TILE_BYTES);
+          const uint64_t db = make_smem_desc_sw128(sB + s * B_TILE_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_bf16(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          umma_commit(&ctl->empty[s]);  // the stage is free once these MMAs have read it
+        }
+        if (!ok) break;
+        umma_commit(&ctl->acc_full[as]);
+      }
+      // no MMA may still be writing TMEM when it is freed, on the normal path or after an abort
+      umma_commit(&ctl->drain);
+      mbar_wait(&ctl->drain, 0, abort_flag, timeout_ns);
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue warps (2..5)
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    uint8_t* stg = sEpi + (warp - 2) * 32 * EPI_PITCH;
+    uint32_t tile_i = 0;
+    for (int t = first; t < total_tiles; t += ngemm, ++tile_i) {
+      const uint32_t as = tile_i & 1, aph = (tile_i >> 1) & 1;
+      if (!mbar_wait(&ctl->acc_full[as], aph, abort_flag, timeout_ns)) break;
+      tc_fence_after();
+      const TileCoord tc_ = tile_coord<MODE>(a, lr, t);
+      // destination of this tile's rows
+      uint8_t* dst;
+      uint64_t ld_bytes;
+      if (MODE == MODE_GEMM_RS) {
+        // partial tile -> staging[my rank] of the owner (peer memory unless the owner is this rank)
+        const MtDevComm& c = a.comms[lr];
+        const int per_rows = a.M / a.nranks;
+        ld_bytes = (uint64_t)a.N * 2;
+        dst = c.heap[tc_.owner] + a.stage_off + ((uint64_t)a.rank[lr] * per_rows + (tc_.mb * BM - tc_.owner * per_rows)) * ld_bytes +
+              (uint64_t)tc_.nb * BN * 2;
+      } else {
+        ld_bytes = (uint64_t)a.ldc * 2;
+        dst = (uint8_t*)a.c[lr] + (uint64_t)tc_.mb * BM * ld_bytes + (uint64_t)tc_.nb * BN * 2;
+      }
+      dst += (uint64_t)(q * 32) * ld_bytes;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + as * BN;
+#pragma unroll 1
+      for (int cb = 0; cb < BN / 64; ++cb) {
+        uint32_t r0[32], r1[32];
+        tmem_ld_32x32(taddr + cb * 64, r0);
+        tmem_ld_32x32(taddr + cb * 64 + 32, r1);
+        tmem_ld_wait();
+        // fp32 -> bf16, row `lane` of the staging tile (conflict-free: pitch 144 bytes)
+        uint4* row = (uint4*)(stg + lane * EPI_PITCH);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 o;
+          __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r0[8 * j + 0]), __uint_as_float(r0[8 * j + 1]));
+          __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r0[8 * j + 2]), __uint_as_float(r0[8 * j + 3]));
+          __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r0[8 * j + 4]), __uint_as_float(r0[8 * j + 5]));
+          __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r0[8 * j + 6]), __uint_as_float(r0[8 * j + 7]));
+          o.x = *(uint32_t*)&p0; o.y = *(uint32_t*)&p1; o.z = *(uint32_t*)&p2; o.w = *(uint32_t*)&p3;
+          row[j] = o;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 o;
+          __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r1[8 * j + 0]), __uint_as_float(r1[8 * j + 1]));
+          __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r1[8 * j + 2]), __uint_as_float(r1[8 * j + 3]));
+          __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r1[8 * j + 4]), __uint_as_float(r1[8 * j + 5]));
+          __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r1[8 * j + 6]), __uint_as_float(r1[8 * j + 7]));
+          o.x = *(uint32_t*)&p0; o.y = *(uint32_t*)&p1; o.z = *(uint32_t*)&p2; o.w = *(uint32_t*)&p3;
+          row[4 + j] = o;
+        }
+        __syncwarp();
+        // 8 lanes cover one 128-byte row segment: 4 rows per pass, full lines on the wire
+#pragma unroll
+        for (int p = 0; p < 8; ++p) {
+          const int rr = p * 4 + (lane >> 3), c16 = lane & 7;
+          const uint4 v = *(const uint4*)(stg + rr * EPI_PITCH + c16 * 16);
+          uint8_t* g = dst + (uint64_t)rr * ld_bytes + cb * 128 + c16 * 16;
+          if (MODE == MODE_GEMM_RS) {
+            u128 w;
+            w.x = (uint64_t)v.x | ((uint64_t)v.y << 32);
+            w.y = (uint64_t)v.z | ((uint64_t)v.w << 32);
+            store128_relaxed_sys(g, w);
+          } else {
+            *(uint4*)g = v;
+          }
+        }
+        __syncwarp();
+      }
+      // accumulator drained: hand it back to the MMA warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl->acc_empty[as]);
+      if (MODE == MODE_GEMM_RS) {
+        // count this warp's quarter of the tile on the owner (release: the stores above come first)
+        if (lane == 0) {
+          const MtDevComm& c = a.comms[lr];
+          const int per = (a.M / a.nranks) / BM;
+          uint64_t* cnt = (uint64_t*)(c.heap[tc_.owner] + a.flags_off) +
+                          ((uint64_t)a.rank[lr] * per + (tc_.mb % per)) * (a.N / BN) + tc_.nb;
+          fence_acq_rel_sys();
+          asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(cnt), "l"(1ull) : "memory");
+        }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- tear-down
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && *abort_flag) {
+    gemm_report(a, lr, MT_WHERE_GEMM_FLAG);
+  }
+
+  // ---------------------------------------------------------------- reducer phase of GEMM -> reduce-scatter
+  if (MODE == MODE_GEMM_RS) {
+    if (*abort_flag) return;
+    const MtDevComm& c = a.comms[lr];
+    const int n = a.nranks, me = a.rank[lr];
+    const int per_rows = a.M / n, per = per_rows / BM, nbs = a.N / BN;
+    const uint64_t ld_bytes = (uint64_t)a.N * 2;
+    const uint8_t* stage = c.heap[me] + a.stage_off;
+    const uint64_t* cnts = (const uint64_t*)(c.heap[me] + a.flags_off);
+    __shared__ int s_ok;
+    for (int ot = blockIdx.x; ot < per * nbs; ot += gridDim.x) {
+      const int mbl = ot / nbs, nb = ot % nbs;
+      if (threadIdx.x == 0) {
+        s_ok = 1;
+        const uint64_t want = a.epoch * 4ull;  // four epilogue warps count each partial tile
+        for (int s = 0; s < n && s_ok; ++s) {
+          const uint64_t* w = cnts + ((uint64_t)s * per + mbl) * nbs + nb;
+          uint32_t spins = 0;
+          uint64_t t0 = 0;
+          while (load64_acquire_sys(w) < want) {
+            if ((++spins & 0xffu) == 0) {
+              const uint64_t now = globaltimer();
+              if (t0 == 0) t0 = now;
+              else if (now - t0 > timeout_ns) {
+                s_ok = 0;
+                gemm_report(a, lr, MT_WHERE_GEMM_FLAG);
+                break;
+              }
+            }
+            __nanosleep(40);
+          }
+        }
+      }
+      __syncthreads();
+      if (!s_ok) return;
+      // 128 x 256 bf16 output tile: 4096 vectors of 16 bytes (8 elements)
+      uint8_t* out = (uint8_t*)a.c[lr] + (uint64_t)mbl * BM * ld_bytes + (uint64_t)nb * BN * 2;
+      for (int v = threadIdx.x; v < BM * (BN / 8); v += kGemmThreads) {
+        const int rr = v / (BN / 8), cv = v % (BN / 8);
+        float acc[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+        for (int s = 0; s < n; ++s) {
+          const uint8_t* p = stage + ((uint64_t)s * per_rows + (uint64_t)mbl * BM + rr) * ld_bytes + (uint64_t)nb * BN * 2 + cv * 16;
+          const u128 w = load128_relaxed_sys(p);
+          const uint32_t ww[4] = {(uint32_t)w.x, (uint32_t)(w.x >> 32), (uint32_t)w.y, (uint32_t)(w.y >> 32)};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            acc[2 * e] += __uint_as_float(ww[e] << 16);
+            acc[2 * e + 1] += __uint_as_float(ww[e] & 0xffff0000u);
+          }
+        }
+        uint4 o;
+        __nv_bfloat162 p0 = __floats2bfloat162_rn(acc[0], acc[1]), p1 = __floats2bfloat162_rn(acc[2], acc[3]);
+        __nv_bfloat162 p2 = __floats2bfloat162_rn(acc[4], acc[5]), p3 = __floats2bfloat162_rn(acc[6], acc[7]);
+        o.x = *(uint32_t*)&p0; o.y = *(uint32_t*)&p1; o.z = *(uint32_t*)&p2; o.w = *(uint32_t*)&p3;
+        *(uint4*)(out + (uint64_t)rr * ld_bytes + cv * 16) = o;
+      }
+      __syncthreads();
+    }
+  }
+}
+
+template <int MODE>
+static cudaError_t launch_mode(const GemmMaps& maps, const GemmArgs& a, int nctas, int nlocal, cudaStream_t s) {
+  static bool attr_set = false;
+  const void* fn = (const void*)gemm_tc_kernel<MODE>;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  GemmMaps m = maps;
+  GemmArgs args = a;
+  void* p[] = {(void*)&m, (void*)&args};
+  count_launch();
+  if (nlocal > 1) return cudaLaunchCooperativeKernel(fn, dim3(nctas, nlocal), dim3(kGemmThreads), p, SMEM_BYTES, s);
+  return cudaLaunchKernel(fn, dim3(nctas, nlocal), dim3(kGemmThreads), p, SMEM_BYTES, s);
+}
+
+cudaError_t launch_gemm_tc(int mode, const GemmMaps& maps, const GemmArgs& a, int nctas, int nlocal, cudaStream_t s) {
+  switch (mode) {
+    case MODE_PLAIN: return launch_mode<MODE_PLAIN>(maps, a, nctas, nlocal, s);
+    case MODE_AG_GEMM: return launch_mode<MODE_AG_GEMM>(maps, a, nctas, nlocal, s);
+    case MODE_GEMM_RS: return launch_mode<MODE_GEMM_RS>(maps, a, nctas, nlocal, s);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+}  // namespace mt

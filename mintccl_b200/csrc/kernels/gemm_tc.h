@@ -1,0 +1,38 @@
+// Arguments of the tcgen05 GEMM kernels (plain, all-gather -> GEMM, GEMM -> reduce-scatter).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "../device/layout.h"
+
+namespace mt {
+
+enum GemmMode : int { MODE_PLAIN = 0, MODE_AG_GEMM = 1, MODE_GEMM_RS = 2 };
+
+// TMA descriptors, one set per local rank (index 0 outside single-GPU emulation).
+struct GemmMaps {
+  CUtensorMap a[MT_MAX_RANKS];   // A operand: [M, K] (AG_GEMM: the gathered buffer)
+  CUtensorMap b[MT_MAX_RANKS];   // B operand: [N, K]
+  CUtensorMap a2[MT_MAX_RANKS];  // AG_GEMM: this rank's own rows [M / n, K]
+};
+
+struct GemmArgs {
+  void* c[MT_MAX_RANKS];               // output: C [M, ldc] (GEMM_RS: this rank's rows [M / n, N])
+  const void* a_local[MT_MAX_RANKS];   // AG_GEMM: own rows, pushed to the peers by the comm CTAs
+  const void* flags_local[MT_MAX_RANKS];  // AG_GEMM: this rank's arrival counters (local view)
+  void* status[MT_MAX_RANKS];          // MtStatus of the rank (or null)
+  const MtDevComm* comms;              // device descriptors (fused modes)
+  int32_t rank[MT_MAX_RANKS];
+  int32_t M, N, K, ldc;
+  int32_t nranks;
+  int32_t ncomm;                       // AG_GEMM: CTAs that move data instead of computing
+  uint64_t gather_off;                 // AG_GEMM: heap offset of the gathered A buffer [M, K]
+  uint64_t flags_off;                  // heap offset of the arrival counters
+  uint64_t stage_off;                  // GEMM_RS: heap offset of the partial tiles [n, M / n, N]
+  uint64_t epoch;                      // call number on these counters (they only ever grow)
+  uint64_t timeout_ns;
+};
+
+cudaError_t launch_gemm_tc(int mode, const GemmMaps& maps, const GemmArgs& a, int nctas, int nlocal, cudaStream_t s);
+
+}  // namespace mt

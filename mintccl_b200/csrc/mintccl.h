@@ -88,6 +88,14 @@ uint64_t mt_ll_capacity(MtComm* c);
 int mt_p2p(MtComm* c, void* stream, int src_rank, int dst_rank, const void* src_ptr, void* dst_ptr, uint64_t nbytes,
            int pull, int nctas);
 
+// ---- tcgen05 GEMM and its fusions with collectives (bf16, fp32 accumulate; B is [N, K] like nn.Linear) ----
+int mt_gemm(void* stream, const void* A, const void* B, void* C, int M, int N, int K, int ldc, int nctas);
+int mt_ag_gemm(MtComm* c, void* stream, const void* const* a_shard, const void* const* B, void* const* C,
+               uint64_t gather_off, uint64_t flags_off, uint64_t epoch, int M, int N, int K, int ldc, int ncomm,
+               int nctas);
+int mt_gemm_rs(MtComm* c, void* stream, const void* const* A, const void* const* B, void* const* out,
+               uint64_t stage_off, uint64_t flags_off, uint64_t epoch, int M, int N, int K, int nctas);
+
 // ---- device-wait self test: a wait nothing satisfies must time out and report, not hang -----------
 int mt_test_wait_timeout(MtComm* c, void* stream);
 

@@ -1,0 +1,134 @@
+"""bf16 GEMM on the tcgen05 tensor cores and its fusions with collectives.
+
+* ``gemm(a, w)``                : ``a @ w.T`` (``w`` is ``[N, K]`` like ``nn.Linear.weight``).
+* ``AllGatherGemm`` (``ag_gemm``): ``allgather(a_shard) @ w.T`` for a column-parallel layer whose input is
+  sharded over the token dimension (sequence parallelism).  One kernel: a few CTAs push this rank's rows
+  to the peers while the others multiply, starting with the rows that are already there.
+* ``GemmReduceScatter`` (``gemm_rs``): ``reduce_scatter(a @ w.T)`` over token rows for a row-parallel
+  layer.  One kernel: partial tiles go straight from the epilogue into the owner's memory over NVLink, the
+  owner sums them in fp32.
+
+Shapes: tokens ``M`` a multiple of ``128 * world``, ``N`` of 256, ``K`` of 64.  The reference has no such
+ops; its README (README.md:5) names fusion with other kernels as the purpose of the library.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional, Sequence, Union
+
+import torch
+
+from .. import _native as N
+
+TensorOrList = Union[torch.Tensor, Sequence[torch.Tensor]]
+BM, BN, BK = 128, 256, 64
+
+
+def _check(t: torch.Tensor, name: str) -> None:
+    if t.dtype != torch.bfloat16 or not t.is_cuda or not t.is_contiguous() or t.dim() != 2:
+        raise ValueError(f"{name} must be a contiguous 2-D bfloat16 CUDA tensor")
+
+
+def gemm(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, nctas: int = 0) -> torch.Tensor:
+    """``a [M, K] @ w[N, K].T -> [M, N]`` in bf16 with fp32 accumulation (hand-written tcgen05 kernel)."""
+    _check(a, "a")
+    _check(w, "w")
+    M, K = a.shape
+    Nn, K2 = w.shape
+    if K != K2:
+        raise ValueError("inner dimensions differ")
+    if out is None:
+        out = torch.empty(M, Nn, device=a.device, dtype=torch.bfloat16)
+    _check(out, "out")
+    stream = torch.cuda.current_stream(a.device).cuda_stream
+    if N.lib().mt_gemm(stream, a.data_ptr(), w.data_ptr(), out.data_ptr(), M, Nn, K, out.stride(0), nctas) < 0:
+        raise RuntimeError(f"mt_gemm: {N.last_error()}")
+    return out
+
+
+class _Fused:
+    def __init__(self, comm):
+        self.comm = comm
+        self.epoch = 0
+
+    def _lists(self, t: TensorOrList) -> List[torch.Tensor]:
+        ts = [t] if isinstance(t, torch.Tensor) else list(t)
+        if len(ts) != self.comm.nlocal:
+            raise ValueError(f"expected {self.comm.nlocal} tensors")
+        return ts
+
+    def _off(self, t: TensorOrList) -> int:
+        t0 = t[0] if isinstance(t, (list, tuple)) else t
+        return t0.data_ptr() - self.comm.heap_base[0]
+
+
+class AllGatherGemm(_Fused):
+    """Plan for ``allgather(a_shard)[M, K] @ w[N, K].T``: owns the gathered-input buffer and the arrival
+    counters in the symmetric heap.  Create it collectively (same order on every rank), call it every step."""
+
+    def __init__(self, comm, M: int, N_: int, K: int, ncomm: int = 20):
+        super().__init__(comm)
+        n = comm.world_size
+        if M % (BM * n) or N_ % BN or K % BK:
+            raise ValueError("M must be a multiple of 128 x world, N of 256, K of 64")
+        self.M, self.N, self.K, self.ncomm = M, N_, K, ncomm
+        self.gathered = comm.symm_empty((M, K), torch.bfloat16)
+        self.flags = comm.symm_zeros((n * (M // n // BM),), torch.int64)
+        torch.cuda.synchronize()
+        comm.control.barrier()
+
+    def __call__(self, a_shard: TensorOrList, w: TensorOrList, out: Optional[TensorOrList] = None, nctas: int = 0):
+        c = self.comm
+        a_s, ws = self._lists(a_shard), self._lists(w)
+        if out is None:
+            outs = [torch.empty(self.M, self.N, device=a_s[0].device, dtype=torch.bfloat16) for _ in a_s]
+        else:
+            outs = self._lists(out)
+        for t in a_s + ws + outs:
+            _check(t, "operand")
+        if tuple(a_s[0].shape) != (self.M // c.world_size, self.K) or tuple(ws[0].shape) != (self.N, self.K):
+            raise ValueError("operand shapes do not match the plan")
+        self.epoch += 1
+        rc = c.lib.mt_ag_gemm(c._handle, c._stream(), N.ptr_array([t.data_ptr() for t in a_s]),
+                              N.ptr_array([t.data_ptr() for t in ws]), N.ptr_array([t.data_ptr() for t in outs]),
+                              self._off(self.gathered), self._off(self.flags), self.epoch, self.M, self.N, self.K,
+                              outs[0].stride(0), self.ncomm, nctas)
+        if rc < 0:
+            raise RuntimeError(f"mt_ag_gemm: {N.last_error()}")
+        return outs if c.emulated else outs[0]
+
+
+class GemmReduceScatter(_Fused):
+    """Plan for ``reduce_scatter(a[M, K_local] @ w[N, K_local].T)`` over token rows: owns the staging area
+    for partial tiles and their arrival counters in the symmetric heap."""
+
+    def __init__(self, comm, M: int, N_: int, K: int):
+        super().__init__(comm)
+        n = comm.world_size
+        if M % (BM * n) or N_ % BN or K % BK:
+            raise ValueError("M must be a multiple of 128 x world, N of 256, K of 64")
+        self.M, self.N, self.K = M, N_, K
+        self.stage = comm.symm_empty((n, M // n, N_), torch.bfloat16)
+        self.flags = comm.symm_zeros((n * (M // n // BM) * (N_ // BN),), torch.int64)
+        torch.cuda.synchronize()
+        comm.control.barrier()
+
+    def __call__(self, a: TensorOrList, w: TensorOrList, out: Optional[TensorOrList] = None, nctas: int = 0):
+        c = self.comm
+        a_s, ws = self._lists(a), self._lists(w)
+        rows = self.M // c.world_size
+        if out is None:
+            outs = [torch.empty(rows, self.N, device=a_s[0].device, dtype=torch.bfloat16) for _ in a_s]
+        else:
+            outs = self._lists(out)
+        for t in a_s + ws + outs:
+            _check(t, "operand")
+        if tuple(a_s[0].shape) != (self.M, self.K) or tuple(ws[0].shape) != (self.N, self.K):
+            raise ValueError("operand shapes do not match the plan")
+        self.epoch += 1
+        rc = c.lib.mt_gemm_rs(c._handle, c._stream(), N.ptr_array([t.data_ptr() for t in a_s]),
+                              N.ptr_array([t.data_ptr() for t in ws]), N.ptr_array([t.data_ptr() for t in outs]),
+                              self._off(self.stage), self._off(self.flags), self.epoch, self.M, self.N, self.K, nctas)
+        if rc < 0:
+            raise RuntimeError(f"mt_gemm_rs: {N.last_error()}")
+        return outs if c.emulated else outs[0]

@@ -1,0 +1,78 @@
+"""tcgen05 GEMM and the fused GEMM + collective kernels against fp32 PyTorch references."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def ref_mm(a, w):
+    return a.float() @ w.float().t()
+
+
+def close(got, ref32, k):
+    # bf16 output of an fp32-accumulated product: one rounding of the result (2^-8 relative)
+    torch.testing.assert_close(got.float(), ref32, rtol=1.6e-2, atol=2e-2 * (k ** 0.5) * 0.05 + 1e-2)
+
+
+@pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 128), (384, 256, 1024), (1024, 1792, 4096), (2048, 4096, 1792)])
+def test_gemm_matches_fp32_reference(shape):
+    from mintccl_b200.ops.gemm import gemm
+    M, N, K = shape
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    a = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    out = gemm(a, w)
+    torch.cuda.synchronize()
+    close(out, ref_mm(a, w), K)
+    # a second call on the same stream (fresh barriers, TMEM re-allocated) and fewer CTAs than tiles
+    out2 = gemm(a, w, nctas=3)
+    torch.cuda.synchronize()
+    assert torch.equal(out, out2)
+
+
+_worlds = {}
+
+
+def world(n):
+    from mintccl_b200 import Config, emulated
+    if n not in _worlds:
+        cfg = Config.from_env(max_channels=4, num_blocks=4, buff_size=1 << 20, heap_bytes=768 << 20, scratch_bytes=1 << 20,
+                              wait_timeout_ms=4000)
+        _worlds[n] = emulated(n, 0, cfg)
+    return _worlds[n]
+
+
+@pytest.mark.parametrize("n", [1, 2, 4])
+def test_ag_gemm_emulated(n):
+    from mintccl_b200.ops.gemm import AllGatherGemm
+    w_ = world(n)
+    M, N, K = 128 * n * 2, 512, 256
+    plan = AllGatherGemm(w_, M, N, K, ncomm=4)
+    for it in range(3):  # counters keep growing across calls
+        g = torch.Generator(device="cuda").manual_seed(it)
+        shards = [torch.randn(M // n, K, generator=g, device="cuda").to(torch.bfloat16) for _ in range(n)]
+        ws = [(torch.randn(N, K, generator=g, device="cuda") * 0.05).to(torch.bfloat16) for _ in range(n)]
+        outs = plan(shards, ws)
+        w_.check()
+        full = torch.cat(shards, 0)
+        for r in range(n):
+            close(outs[r], ref_mm(full, ws[r]), K)
+
+
+@pytest.mark.parametrize("n", [1, 2, 4])
+def test_gemm_rs_emulated(n):
+    from mintccl_b200.ops.gemm import GemmReduceScatter
+    w_ = world(n)
+    M, N, K = 128 * n * 2, 512, 192
+    plan = GemmReduceScatter(w_, M, N, K)
+    for it in range(3):
+        g = torch.Generator(device="cuda").manual_seed(10 + it)
+        As = [torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16) for _ in range(n)]
+        ws = [(torch.randn(N, K, generator=g, device="cuda") * 0.05).to(torch.bfloat16) for _ in range(n)]
+        outs = plan(As, ws)
+        w_.check()
+        # partial products are rounded to bf16 before the fp32 sum over ranks
+        ref = sum(ref_mm(a, w).to(torch.bfloat16).float() for a, w in zip(As, ws))
+        rows = M // n
+        for r in range(n):
+            torch.testing.assert_close(outs[r].float(), ref[r * rows:(r + 1) * rows], rtol=2e-2, atol=3e-2)
