@@ -43,4 +43,6 @@ namespace mthost {
 int fail(const std::string& m);
 // Looks a driver entry point up through the runtime (no link-time dependency on the driver library).
 void* driver_entry(const char* name);
+// TMA descriptor of a row-major [rows, K] bf16 matrix cut into box_rows x 64 tiles (128-byte swizzle).
+int make_bf16_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K, uint32_t box_rows);
 }  // namespace mthost

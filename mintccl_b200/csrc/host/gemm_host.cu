@@ -49,6 +49,12 @@ int sm_count(int device) {
 
 }  // namespace
 
+namespace mthost {
+int make_bf16_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K, uint32_t box_rows) {
+  return make_map(map, base, rows, K, box_rows);
+}
+}  // namespace mthost
+
 extern "C" {
 
 // C[M, ldc] = A[M, K] * B[N, K]^T in bf16 with fp32 accumulation, on the current device.
