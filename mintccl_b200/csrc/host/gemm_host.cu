@@ -142,13 +142,16 @@ int mt_ag_gemm(MtComm* c, void* stream, const void* const* a_shard, const void* 
 
 // out[M / ranks, N] = reduce_scatter over rows of (A[M, K] * B[N, K]^T), K being this rank's slice of the
 // contraction.  `stage_off`: symmetric buffer of ranks * (M / ranks) * N bf16 partial tiles;
-// `flags_off`: symmetric u64 counters [ranks][M / ranks / 128][N / 256], zero before the first call.
+// `flags_off`: symmetric u64 counters [ranks][M / ranks / 128][N / 256] followed by two ticket words, all zero
+// before the first call.  `nred`: CTAs that only reduce (the others join them when their tiles are done).
 int mt_gemm_rs(MtComm* c, void* stream, const void* const* A, const void* const* B, void* const* out,
-               uint64_t stage_off, uint64_t flags_off, uint64_t epoch, int M, int N, int K, int nctas) {
+               uint64_t stage_off, uint64_t flags_off, uint64_t epoch, int M, int N, int K, int nred, int nctas) {
   mt::GemmArgs a;
   if (fused_common(c, a, M, N, K, flags_off, epoch)) return -1;
   int grid = nctas > 0 ? nctas : sm_count(c->device);
   if (c->emulated && grid * c->nlocal > sm_count(c->device)) grid = sm_count(c->device) / c->nlocal;
+  if (nred < 0 || nred >= grid) return fail("nred out of range");
+  a.ncomm = nred;
   a.ldc = N;
   a.stage_off = stage_off;
   mt::GemmMaps maps;

@@ -19,8 +19,8 @@ namespace {
 // Layout of the scratch array (offsets in bytes).
 constexpr uint64_t kCommOff = 0;          // MtDevComm read by the kernel
 constexpr uint64_t kStatusOff = 2048;     // MtStatus written by the kernel on a failed wait
-constexpr uint64_t kFlagsOff = 4096;      // u64 arrival counters [M / 128][N / 256]
-constexpr uint64_t kFlagsBytes = (MT_NOALLOC_MAX_M / 128) * (MT_NOALLOC_MAX_N / 256) * 8;
+constexpr uint64_t kFlagsOff = 4096;      // u64 arrival counters [M / 128][N / 256], then two ticket words
+constexpr uint64_t kFlagsBytes = (MT_NOALLOC_MAX_M / 128) * (MT_NOALLOC_MAX_N / 256) * 8 + 16;  // + two ticket words
 constexpr uint64_t kStageOff = 8192;      // bf16 partial tiles [M][N]
 constexpr uint64_t kStageBytes = (uint64_t)MT_NOALLOC_MAX_M * MT_NOALLOC_MAX_N * 2;
 constexpr uint64_t kScratchBytes = kStageOff + kStageBytes;

@@ -42,6 +42,14 @@ constexpr uint32_t EPI_BYTES = 4 * 32 * EPI_PITCH;  // 4 epilogue warps x 32 row
 constexpr uint32_t SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + 256;
 constexpr uint32_t TMEM_COLS = 512;
 
+// comm CTAs: ring of COMM_SLOTS pieces in shared memory, loads run COMM_LAG pieces ahead of stores
+constexpr uint32_t COMM_PIECE = 32768;
+constexpr int COMM_SLOTS = 6, COMM_LAG = 3;
+struct CommCtl {
+  uint64_t full[COMM_SLOTS];
+  int abort;
+};
+
 struct SharedCtl {
   uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], drain;
   uint32_t tmem_base;
@@ -79,7 +87,7 @@ __device__ __forceinline__ void gemm_report(const GemmArgs& a, int lr, uint32_t 
 }
 
 // Tile order.  PLAIN: row-major over (m block, n block).  AG_GEMM: row blocks of rank r, r-1, r-2, ...
-// (arrival order of the pushes).  GEMM_RS: row blocks of rank r+1, r+2, ..., r (remote owners first).
+// (arrival order of the pushes).  GEMM_RS: see below.
 struct TileCoord {
   int mb, nb, owner;
 };
@@ -94,11 +102,115 @@ __device__ __forceinline__ TileCoord tile_coord(const GemmArgs& a, int lr, int t
     c.owner = 0;
   } else {
     const int per = (a.M / a.nranks) / BM;  // row blocks per rank
-    const int d = mi / per, j = mi % per;
-    c.owner = MODE == MODE_AG_GEMM ? mt_mod(a.rank[lr] - d, a.nranks) : mt_mod(a.rank[lr] + 1 + d, a.nranks);
+    int d, j;
+    if (MODE == MODE_AG_GEMM) {
+      d = mi / per;
+      j = mi % per;
+      c.owner = mt_mod(a.rank[lr] - d, a.nranks);
+    } else {
+      // every rank walks the row blocks j = 0, 1, ... of all owners in step, each starting at a
+      // different owner: the links stay balanced and block j of every owner is complete everywhere
+      // after (j + 1) / per of the run, so the reducers work alongside the GEMM instead of after it
+      j = mi / a.nranks;
+      d = mi % a.nranks;
+      c.owner = mt_mod(a.rank[lr] + 1 + d, a.nranks);
+    }
     c.mb = c.owner * per + j;
   }
   return c;
+}
+
+// Reducer of GEMM -> reduce-scatter: output tiles of this rank are handed out by tickets (an atomic
+// counter that alternates between two words from call to call; the idle one is zeroed for the next
+// call), in the order in which their partial tiles complete.  A CTA takes tickets until none is left.
+__device__ void rs_reduce_loop(const GemmArgs& a, int lr) {
+  const MtDevComm& c = a.comms[lr];
+  const int n = a.nranks, me = a.rank[lr];
+  const int per_rows = a.M / n, per = per_rows / BM, nbs = a.N / BN;
+  const uint64_t ld_bytes = (uint64_t)a.N * 2;
+  const uint8_t* stage = c.heap[me] + a.stage_off;
+  uint64_t* cnts = (uint64_t*)(c.heap[me] + a.flags_off);
+  unsigned long long* tickets = (unsigned long long*)(cnts + (uint64_t)n * per * nbs);
+  const uint64_t timeout_ns = a.timeout_ns;
+  __shared__ int s_ok, s_ot;
+  if (blockIdx.x == 0 && threadIdx.x == 0) tickets[(a.epoch + 1) & 1] = 0;  // next call's counter
+  while (true) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      s_ok = 1;
+      s_ot = (int)atomicAdd(&tickets[a.epoch & 1], 1ull);
+      if (s_ot < per * nbs) {
+        const int mbl = s_ot / nbs, nb = s_ot % nbs;
+        const uint64_t want = a.epoch * 4ull;  // four epilogue warps count each partial tile
+        for (int s = 0; s < n && s_ok; ++s) {
+          const uint64_t* w = cnts + ((uint64_t)s * per + mbl) * nbs + nb;
+          uint32_t spins = 0;
+          uint64_t t0 = 0;
+          while (load64_acquire_sys(w) < want) {
+            if ((++spins & 0xffu) == 0) {
+              const uint64_t now = globaltimer();
+              if (t0 == 0) t0 = now;
+              else if (now - t0 > timeout_ns) {
+                s_ok = 0;
+                gemm_report(a, lr, MT_WHERE_GEMM_FLAG);
+                break;
+              }
+            }
+            __nanosleep(40);
+          }
+        }
+      }
+    }
+    __syncthreads();
+    const int ot = s_ot;
+    if (!s_ok || ot >= per * nbs) return;
+    {
+      const int mbl = ot / nbs, nb = ot % nbs;
+      // 128 x 256 bf16 output tile: 4096 vectors of 16 bytes (8 elements)
+      uint8_t* out = (uint8_t*)a.c[lr] + (uint64_t)mbl * BM * ld_bytes + (uint64_t)nb * BN * 2;
+      constexpr int RU = 4;  // vectors per thread and pass: RU x ranks loads in flight
+      for (int v0 = threadIdx.x; v0 < BM * (BN / 8); v0 += kGemmThreads * RU) {
+        float acc[RU][8];
+#pragma unroll
+        for (int u = 0; u < RU; ++u)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[u][e] = 0.f;
+        for (int s = 0; s < n; ++s) {
+          u128 w[RU];
+#pragma unroll
+          for (int u = 0; u < RU; ++u) {
+            const int v = v0 + u * kGemmThreads;
+            if (v < BM * (BN / 8)) {
+              const int rr = v / (BN / 8), cv = v % (BN / 8);
+              w[u] = load128_relaxed_sys(stage + ((uint64_t)s * per_rows + (uint64_t)mbl * BM + rr) * ld_bytes +
+                                         (uint64_t)nb * BN * 2 + cv * 16);
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < RU; ++u) {
+            const uint32_t ww[4] = {(uint32_t)w[u].x, (uint32_t)(w[u].x >> 32), (uint32_t)w[u].y, (uint32_t)(w[u].y >> 32)};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              acc[u][2 * e] += __uint_as_float(ww[e] << 16);
+              acc[u][2 * e + 1] += __uint_as_float(ww[e] & 0xffff0000u);
+            }
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < RU; ++u) {
+          const int v = v0 + u * kGemmThreads;
+          if (v < BM * (BN / 8)) {
+            const int rr = v / (BN / 8), cv = v % (BN / 8);
+            uint4 o;
+            __nv_bfloat162 p0 = __floats2bfloat162_rn(acc[u][0], acc[u][1]), p1 = __floats2bfloat162_rn(acc[u][2], acc[u][3]);
+            __nv_bfloat162 p2 = __floats2bfloat162_rn(acc[u][4], acc[u][5]), p3 = __floats2bfloat162_rn(acc[u][6], acc[u][7]);
+            o.x = *(uint32_t*)&p0; o.y = *(uint32_t*)&p1; o.z = *(uint32_t*)&p2; o.w = *(uint32_t*)&p3;
+            *(uint4*)(out + (uint64_t)rr * ld_bytes + cv * 16) = o;
+          }
+        }
+      }
+    }
+  }
 }
 
 template <int MODE>
@@ -111,7 +223,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_c
   uint8_t* sB = smem + STAGES * A_TILE_BYTES;
   uint8_t* sEpi = smem + STAGES * STAGE_BYTES;
   SharedCtl* ctl = (SharedCtl*)(sEpi + EPI_BYTES);
-  const int ncomm = MODE == MODE_AG_GEMM ? a.ncomm : 0;
+  const int ncomm = MODE == MODE_PLAIN ? 0 : a.ncomm;  // AG: data movers, RS: dedicated reducers
   const int ngemm = gridDim.x - ncomm;
   const uint64_t timeout_ns = a.timeout_ns;
 
@@ -127,35 +239,89 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_c
     const uint64_t shard_rows = a.M / n;
     const int chunks = (int)(shard_rows / BM);
     const uint8_t* src = (const uint8_t*)a.a_local[lr];
-    for (int d = 1; d < n; ++d) {
-      const int p = (me + d) % n;
-      uint8_t* dst = c.heap[p] + a.gather_off + (uint64_t)me * shard_rows * row_bytes;
-      uint64_t* cnt = (uint64_t*)(c.heap[p] + a.flags_off) + (uint64_t)me * chunks;
-      for (int ci = 0; ci < chunks; ++ci) {
-        const uint64_t chunk_bytes = (uint64_t)BM * row_bytes;
-        const MtRange r = mt_split(chunk_bytes, ncomm, cc, 128);
-        const uint64_t base = (uint64_t)ci * chunk_bytes;
-        const uint64_t nvec = (r.hi - r.lo) >> 4;
-        for (uint64_t i0 = 0; i0 < nvec; i0 += (uint64_t)kGemmThreads * 8) {
-          u128 v[8];
-#pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            const uint64_t i = i0 + (uint64_t)u * kGemmThreads + threadIdx.x;
-            if (i < nvec) v[u] = load128_stream(src + base + r.lo + (i << 4));
-          }
-#pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            const uint64_t i = i0 + (uint64_t)u * kGemmThreads + threadIdx.x;
-            if (i < nvec) store128_relaxed_sys(dst + base + r.lo + (i << 4), v[u]);
-          }
+    // One thread drives the copy engine: bulk copies local HBM -> shared memory ring -> peer HBM, so a
+    // handful of CTAs keeps hundreds of KiB in flight and the other SMs stay free for the GEMM.
+    CommCtl* cm = (CommCtl*)(sEpi + EPI_BYTES);
+    if (threadIdx.x == 0) {
+      for (int s = 0; s < COMM_SLOTS; ++s) mbar_init(&cm->full[s], 1);
+      cm->abort = 0;
+      fence_barrier_init();
+      const uint64_t chunk_bytes = (uint64_t)BM * row_bytes;
+      const MtRange r = mt_split(chunk_bytes, ncomm, cc, 128);
+      const uint32_t ppc = (uint32_t)mt_div_up(r.hi - r.lo, COMM_PIECE);   // pieces per chunk for this CTA
+      const uint32_t total = ppc * (uint32_t)chunks * (uint32_t)(n - 1);
+      volatile int* ab = &cm->abort;
+      auto locate = [&](uint32_t i, int& p, int& ci, uint64_t& off, uint32_t& nb) {
+        const uint32_t piece = i % ppc, ch_i = i / ppc;
+        ci = (int)(ch_i % chunks);
+        p = (me + 1 + (int)(ch_i / chunks)) % n;
+        off = (uint64_t)ci * chunk_bytes + r.lo + (uint64_t)piece * COMM_PIECE;
+        const uint64_t left = r.hi - r.lo - (uint64_t)piece * COMM_PIECE;
+        nb = (uint32_t)(left < COMM_PIECE ? left : COMM_PIECE);
+      };
+      auto signal = [&](uint32_t i) {
+        int p, ci;
+        uint64_t off;
+        uint32_t nb;
+        locate(i, p, ci, off, nb);
+        uint64_t* cnt = (uint64_t*)(c.heap[p] + a.flags_off) + (uint64_t)me * chunks + ci;
+        asm volatile("fence.proxy.async;" ::: "memory");
+        fence_acq_rel_sys();
+        asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(cnt), "l"(1ull) : "memory");
+      };
+      bool ok = ppc > 0;
+      for (uint32_t i = 0; ok && i < total + COMM_LAG; ++i) {
+        if (i < total) {
+          int p, ci;
+          uint64_t off;
+          uint32_t nb;
+          locate(i, p, ci, off, nb);
+          const uint32_t s_ = i % COMM_SLOTS;
+          // the store that last used this slot (piece i - COMM_SLOTS) must have finished reading it
+          if (i >= COMM_SLOTS) asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(COMM_SLOTS - COMM_LAG - 1) : "memory");
+          mbar_expect_tx(&cm->full[s_], nb);
+          asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                           smem_u32(smem + (uint64_t)s_ * COMM_PIECE)),
+                       "l"(src + off), "r"(nb), "r"(smem_u32(&cm->full[s_]))
+                       : "memory");
         }
-        __syncthreads();
-        if (threadIdx.x == 0) {
-          fence_acq_rel_sys();
-          asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(cnt + ci), "l"(1ull) : "memory");
+        if (i >= COMM_LAG) {
+          const uint32_t j = i - COMM_LAG;
+          int p, ci;
+          uint64_t off;
+          uint32_t nb;
+          locate(j, p, ci, off, nb);
+          const uint32_t s_ = j % COMM_SLOTS;
+          if (!mbar_wait(&cm->full[s_], (j / COMM_SLOTS) & 1, ab, timeout_ns)) {
+            ok = false;
+            break;
+          }
+          uint8_t* dst = c.heap[p] + a.gather_off + (uint64_t)me * shard_rows * row_bytes + off;
+          asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst),
+                       "r"(smem_u32(smem + (uint64_t)s_ * COMM_PIECE)), "r"(nb)
+                       : "memory");
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          // piece j - COMM_LAG completed its chunk?  Then all but the COMM_LAG newest stores are done.
+          if (j >= COMM_LAG && ((j - COMM_LAG) % ppc) == ppc - 1) {
+            asm volatile("cp.async.bulk.wait_group %0;" ::"n"(COMM_LAG) : "memory");
+            signal(j - COMM_LAG);
+          }
         }
       }
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+      if (ok) {
+        for (uint32_t j = total > COMM_LAG ? total - COMM_LAG : 0; j < total; ++j)
+          if (j % ppc == ppc - 1) signal(j);
+      } else {
+        gemm_report(a, lr, MT_WHERE_GEMM_FLAG);
+      }
     }
+    return;
+  }
+
+  // ---------------------------------------------------------------- dedicated reducer CTAs
+  if (MODE == MODE_GEMM_RS && (int)blockIdx.x >= ngemm) {
+    rs_reduce_loop(a, lr);
     return;
   }
 
@@ -374,63 +540,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_c
   // ---------------------------------------------------------------- reducer phase of GEMM -> reduce-scatter
   if (MODE == MODE_GEMM_RS) {
     if (*abort_flag) return;
-    const MtDevComm& c = a.comms[lr];
-    const int n = a.nranks, me = a.rank[lr];
-    const int per_rows = a.M / n, per = per_rows / BM, nbs = a.N / BN;
-    const uint64_t ld_bytes = (uint64_t)a.N * 2;
-    const uint8_t* stage = c.heap[me] + a.stage_off;
-    const uint64_t* cnts = (const uint64_t*)(c.heap[me] + a.flags_off);
-    __shared__ int s_ok;
-    for (int ot = blockIdx.x; ot < per * nbs; ot += gridDim.x) {
-      const int mbl = ot / nbs, nb = ot % nbs;
-      if (threadIdx.x == 0) {
-        s_ok = 1;
-        const uint64_t want = a.epoch * 4ull;  // four epilogue warps count each partial tile
-        for (int s = 0; s < n && s_ok; ++s) {
-          const uint64_t* w = cnts + ((uint64_t)s * per + mbl) * nbs + nb;
-          uint32_t spins = 0;
-          uint64_t t0 = 0;
-          while (load64_acquire_sys(w) < want) {
-            if ((++spins & 0xffu) == 0) {
-              const uint64_t now = globaltimer();
-              if (t0 == 0) t0 = now;
-              else if (now - t0 > timeout_ns) {
-                s_ok = 0;
-                gemm_report(a, lr, MT_WHERE_GEMM_FLAG);
-                break;
-              }
-            }
-            __nanosleep(40);
-          }
-        }
-      }
-      __syncthreads();
-      if (!s_ok) return;
-      // 128 x 256 bf16 output tile: 4096 vectors of 16 bytes (8 elements)
-      uint8_t* out = (uint8_t*)a.c[lr] + (uint64_t)mbl * BM * ld_bytes + (uint64_t)nb * BN * 2;
-      for (int v = threadIdx.x; v < BM * (BN / 8); v += kGemmThreads) {
-        const int rr = v / (BN / 8), cv = v % (BN / 8);
-        float acc[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-        for (int s = 0; s < n; ++s) {
-          const uint8_t* p = stage + ((uint64_t)s * per_rows + (uint64_t)mbl * BM + rr) * ld_bytes + (uint64_t)nb * BN * 2 + cv * 16;
-          const u128 w = load128_relaxed_sys(p);
-          const uint32_t ww[4] = {(uint32_t)w.x, (uint32_t)(w.x >> 32), (uint32_t)w.y, (uint32_t)(w.y >> 32)};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            acc[2 * e] += __uint_as_float(ww[e] << 16);
-            acc[2 * e + 1] += __uint_as_float(ww[e] & 0xffff0000u);
-          }
-        }
-        uint4 o;
-        __nv_bfloat162 p0 = __floats2bfloat162_rn(acc[0], acc[1]), p1 = __floats2bfloat162_rn(acc[2], acc[3]);
-        __nv_bfloat162 p2 = __floats2bfloat162_rn(acc[4], acc[5]), p3 = __floats2bfloat162_rn(acc[6], acc[7]);
-        o.x = *(uint32_t*)&p0; o.y = *(uint32_t*)&p1; o.z = *(uint32_t*)&p2; o.w = *(uint32_t*)&p3;
-        *(uint4*)(out + (uint64_t)rr * ld_bytes + cv * 16) = o;
-      }
-      __syncthreads();
-    }
+    rs_reduce_loop(a, lr);
   }
 }
 

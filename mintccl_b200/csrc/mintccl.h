@@ -94,7 +94,7 @@ int mt_ag_gemm(MtComm* c, void* stream, const void* const* a_shard, const void* 
                uint64_t gather_off, uint64_t flags_off, uint64_t epoch, int M, int N, int K, int ldc, int ncomm,
                int nctas);
 int mt_gemm_rs(MtComm* c, void* stream, const void* const* A, const void* const* B, void* const* out,
-               uint64_t stage_off, uint64_t flags_off, uint64_t epoch, int M, int N, int K, int nctas);
+               uint64_t stage_off, uint64_t flags_off, uint64_t epoch, int M, int N, int K, int nred, int nctas);
 
 // ---- device-wait self test: a wait nothing satisfies must time out and report, not hang -----------
 int mt_test_wait_timeout(MtComm* c, void* stream);

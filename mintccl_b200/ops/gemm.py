@@ -102,14 +102,15 @@ class GemmReduceScatter(_Fused):
     """Plan for ``reduce_scatter(a[M, K_local] @ w[N, K_local].T)`` over token rows: owns the staging area
     for partial tiles and their arrival counters in the symmetric heap."""
 
-    def __init__(self, comm, M: int, N_: int, K: int):
+    def __init__(self, comm, M: int, N_: int, K: int, nred: int = 12):
         super().__init__(comm)
         n = comm.world_size
         if M % (BM * n) or N_ % BN or K % BK:
             raise ValueError("M must be a multiple of 128 x world, N of 256, K of 64")
         self.M, self.N, self.K = M, N_, K
+        self.nred = nred if n > 1 else 0
         self.stage = comm.symm_empty((n, M // n, N_), torch.bfloat16)
-        self.flags = comm.symm_zeros((n * (M // n // BM) * (N_ // BN),), torch.int64)
+        self.flags = comm.symm_zeros((n * (M // n // BM) * (N_ // BN) + 2,), torch.int64)
         torch.cuda.synchronize()
         comm.control.barrier()
 
@@ -128,7 +129,8 @@ class GemmReduceScatter(_Fused):
         self.epoch += 1
         rc = c.lib.mt_gemm_rs(c._handle, c._stream(), N.ptr_array([t.data_ptr() for t in a_s]),
                               N.ptr_array([t.data_ptr() for t in ws]), N.ptr_array([t.data_ptr() for t in outs]),
-                              self._off(self.stage), self._off(self.flags), self.epoch, self.M, self.N, self.K, nctas)
+                              self._off(self.stage), self._off(self.flags), self.epoch, self.M, self.N, self.K,
+                              min(self.nred, 148 // c.nlocal - 1) if c.emulated else self.nred, nctas)
         if rc < 0:
             raise RuntimeError(f"mt_gemm_rs: {N.last_error()}")
         return outs if c.emulated else outs[0]

@@ -123,6 +123,26 @@ def main():
                     c.control.barrier()
                     c.symm_free(so)
                 c.symm_free(b)
+    # fused GEMM + collective kernels against the unfused fp32 reference
+    from mintccl_b200.ops.gemm import AllGatherGemm, GemmReduceScatter
+    M, Nn, K = 128 * n * 2, 512, 256
+    ag = AllGatherGemm(c, M, Nn, K, ncomm=4)
+    rs = GemmReduceScatter(c, M, Nn, K)
+    for it in range(3):
+        shards = [gen(r, (M // n) * K, torch.bfloat16, seed0=50 + it).view(M // n, K) for r in range(n)]
+        w = (gen(rank, Nn * K, torch.float32, seed0=60 + it) * 0.05).to(torch.bfloat16).view(Nn, K)
+        out = ag(shards[rank].contiguous(), w)
+        c.check()
+        ref = torch.cat(shards, 0).float() @ w.float().t()
+        torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=3e-2)
+        As = [gen(r, M * K, torch.bfloat16, seed0=70 + it).view(M, K) for r in range(n)]
+        Ws = [(gen(r, Nn * K, torch.float32, seed0=80 + it) * 0.05).to(torch.bfloat16).view(Nn, K) for r in range(n)]
+        y = rs(As[rank].contiguous(), Ws[rank].contiguous())
+        c.check()
+        ref = sum((a_.float() @ w_.float().t()).to(torch.bfloat16).float() for a_, w_ in zip(As, Ws))
+        rows = M // n
+        torch.testing.assert_close(y.float(), ref[rank * rows:(rank + 1) * rows], rtol=2e-2, atol=4e-2)
+    c.control.barrier()
     # point to point: deferred API over a multi-hop ring route, direct pull and push, registered tensor
     os.environ["MINTCCL_ROUTE"] = "ring"
     a = gen(0, 1_000_003, torch.float16)

@@ -76,3 +76,8 @@ def test_gemm_rs_emulated(n):
         rows = M // n
         for r in range(n):
             torch.testing.assert_close(outs[r].float(), ref[r * rows:(r + 1) * rows], rtol=2e-2, atol=3e-2)
+
+
+def test_tp_mlp_forward_backward_single_rank():
+    from mintccl_b200.models.tp_mlp import smoke_mlp
+    smoke_mlp()
