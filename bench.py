@@ -184,6 +184,7 @@ def main() -> None:
     from mintccl_b200.utils.busbw import busbw_factor
     from mintccl_b200.utils.clocks import ClockSampler
 
+    sampler = ClockSampler(local).start() if rank == 0 else None
     w = Work(a.impl, world, rank, a.size)
     size = w.numel * 2
     for _ in range(max(3, a.warmup)):
@@ -197,10 +198,13 @@ def main() -> None:
         per[name] = max_over_ranks(ms, world)
 
     # the headline: K whole steps
-    sampler = ClockSampler(local).start() if rank == 0 else None
     if a.impl == "mintccl_b200":
         _native.lib().mt_reset_launch_count()
+    if sampler:
+        sampler.mark_begin()
     ms_total = time_region(w.step, a.steps, world)
+    if sampler:
+        sampler.mark_end()
     launches = int(_native.lib().mt_launch_count()) if a.impl == "mintccl_b200" else 0
     ms_step = max_over_ranks(ms_total / a.steps, world)
     clocks = sampler.stop() if sampler else None
@@ -234,7 +238,7 @@ def main() -> None:
     e2e_value = world * bus_bytes / (ms_e2e * 1e-3) / 1e9
 
     # 8-byte all-reduce latency (median of 1000 back-to-back device-timed calls)
-    lat_us = None
+    lat_us = lat_graph_us = None
     if world > 1:
         small_in = (w.comm.symm_empty(4, torch.float16) if w.comm else torch.ones(4, dtype=torch.float16, device="cuda"))
         small_out = torch.empty(4, dtype=torch.float16, device="cuda")
@@ -250,6 +254,21 @@ def main() -> None:
         for _ in range(20):
             small()
         lat_us = max_over_ranks(time_region(small, 1000, world), world)  # 1000 calls: ms total == us per call
+        # the same 1000 calls replayed from a CUDA graph: device-side latency without the host's launch cost
+        try:
+            gr = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(gr, stream=side):
+                    for _ in range(100):
+                        small()
+            torch.cuda.current_stream().wait_stream(side)
+            gr.replay()
+            lat_graph_us = max_over_ranks(time_region(gr.replay, 10, world), world)  # 10 x 100 calls
+        except Exception as e:  # noqa: BLE001
+            lat_graph_us = None
+            print(f"# graph latency skipped: {type(e).__name__}: {e}", file=sys.stderr)
     w.check()
 
     if rank == 0:
@@ -265,6 +284,7 @@ def main() -> None:
                        "l2": "buffers touched per step are about 4.1 x message_bytes (268 MB at the default), larger than the 126 MB L2"},
             "busbw_GBps": busbw, "ms": {k: round(v, 4) for k, v in per.items()},
             "latency_8B_us": None if lat_us is None else round(lat_us, 2),
+            "latency_8B_graph_us": None if lat_graph_us is None else round(lat_graph_us, 2),
             "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": size,
                     "d2h_bytes_per_step": 4096, "ms_per_step": round(ms_e2e, 4), "wall_ms_per_step": round(wall / a.steps, 4)},
             "gpu_launches": launches, "clocks": clocks,
