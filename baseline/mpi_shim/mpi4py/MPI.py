@@ -48,31 +48,36 @@ class _Comm:
         return dist.get_world_size(self._g())
 
     def _send_bytes(self, payload: bytes, dest: int, tag: int):
+        # MPI sends small messages eagerly (the reference relies on it: every rank sends to its neighbour
+        # before anybody receives); a blocking gloo send would deadlock there, so post it and move on.
         g = self._g()
-        head = torch.tensor([len(payload), tag], dtype=torch.int64)
-        dist.send(head, dest, group=g)
-        dist.send(torch.frombuffer(bytearray(payload), dtype=torch.uint8), dest, group=g)
+        head = torch.tensor([len(payload), tag], dtype=torch.int64, device="cpu")
+        body = torch.frombuffer(bytearray(payload), dtype=torch.uint8)
+        self._inflight = [w for w in getattr(self, "_inflight", []) if not w[0].is_completed()]
+        self._inflight.append((dist.isend(head, dest, group=g), head))
+        self._inflight.append((dist.isend(body, dest, group=g), body))
 
     def send(self, obj, dest, tag=0):
         self._send_bytes(pickle.dumps(obj), dest, tag)
 
     def recv(self, source=ANY_SOURCE, tag=ANY_TAG, status=None):
         g = self._g()
-        head = torch.zeros(2, dtype=torch.int64)
+        head = torch.zeros(2, dtype=torch.int64, device="cpu")
         if source == ANY_SOURCE:
             src = dist.recv(head, group=g)
         else:
             dist.recv(head, source, group=g)
             src = source
-        buf = torch.empty(int(head[0]), dtype=torch.uint8)
+        buf = torch.empty(int(head[0]), dtype=torch.uint8, device="cpu")
         dist.recv(buf, src, group=g)
         if status is not None:
             status.source, status.tag = src, int(head[1])
         return pickle.loads(buf.numpy().tobytes())
 
     def bcast(self, obj, root=0):
+        # the reference sets a CUDA default device; object collectives of gloo need host tensors
         box = [obj]
-        dist.broadcast_object_list(box, src=root, group=self._g())
+        dist.broadcast_object_list(box, src=root, group=self._g(), device=torch.device("cpu"))
         return box[0]
 
     def barrier(self):
