@@ -27,7 +27,9 @@ def main() -> None:
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--ffn", type=int, default=14336)
     ap.add_argument("--iters", type=int, default=20)
-    ap.add_argument("--ncomm", default="20", help="comma list of comm-CTA counts to try for the all-gather fusion")
+    ap.add_argument("--ncomm", default="16", help="comma list of comm-CTA counts to try for the all-gather fusion")
+    ap.add_argument("--split", default="1", help="comma list: comm CTAs that share one 128-row chunk")
+    ap.add_argument("--modes", default="push", help="comma list of all-gather transports: push, pull, push_st")
     a = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -41,7 +43,8 @@ def main() -> None:
     n, T, H = world, a.tokens, a.hidden
     F = a.ffn // n // 256 * 256  # the kernels tile N in 256 columns
     g = torch.Generator(device="cuda").manual_seed(rank)
-    x_shard = torch.randn(T // n, H, generator=g, device="cuda").to(torch.bfloat16)
+    x_shard = comm.symm_empty((T // n, H), torch.bfloat16)
+    x_shard.copy_(torch.randn(T // n, H, generator=g, device="cuda").to(torch.bfloat16))
     w_up = (torch.randn(F, H, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
     w_down = (torch.randn(H, F, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
     act = torch.randn(T, F, generator=g, device="cuda").to(torch.bfloat16)
@@ -90,11 +93,13 @@ def main() -> None:
     # ---- fused
     h = torch.empty(T, F, device="cuda", dtype=torch.bfloat16)
     best = None
-    for nc in [int(v) for v in a.ncomm.split(",")]:
-        plan = AllGatherGemm(comm, T, F, H, ncomm=nc)
+    for mode, nc, sp in [(m, int(v), int(q)) for m in a.modes.split(",") for v in a.ncomm.split(",") for q in a.split.split(",")]:
+        if sp > nc:
+            continue
+        plan = AllGatherGemm(comm, T, F, H, ncomm=nc, mode=mode, split=sp)
         us = timed(lambda: plan(x_shard, w_up, out=h))
         comm.check()
-        out[f"up_fused_us_ncomm{nc}"] = round(us, 1)
+        out[f"up_fused_us_{mode}_ncomm{nc}_split{sp}"] = round(us, 1)
         if best is None or us < best:
             best = us
         comm.symm_free(plan.gathered)

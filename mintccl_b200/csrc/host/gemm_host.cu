@@ -109,7 +109,7 @@ static int fused_common(MtComm* c, mt::GemmArgs& a, int M, int N, int K, uint64_
 // first call on these counters, then 2, 3, ...; `ncomm` must not change between calls on the same counters.
 int mt_ag_gemm(MtComm* c, void* stream, const void* const* a_shard, const void* const* B, void* const* C,
                uint64_t gather_off, uint64_t flags_off, uint64_t epoch, int M, int N, int K, int ldc, int ncomm,
-               int nctas) {
+               int nctas, int comm_mode, uint64_t shard_off, int comm_split) {
   mt::GemmArgs a;
   if (fused_common(c, a, M, N, K, flags_off, epoch)) return -1;
   if (ldc < N || ldc % 8) return fail("ldc must be >= N and a multiple of 8");
@@ -123,6 +123,11 @@ int mt_ag_gemm(MtComm* c, void* stream, const void* const* a_shard, const void* 
   a.ldc = ldc;
   a.ncomm = ncomm;
   a.gather_off = gather_off;
+  a.comm_mode = comm_mode;
+  if (n > 1 && (comm_split < 1 || comm_split > ncomm)) return fail("comm_split must be in [1, ncomm]");
+  a.comm_split = n > 1 ? comm_split : 1;
+  a.shard_off = shard_off;
+  if (comm_mode < 0 || comm_mode > 2) return fail("comm_mode must be 0, 1 or 2");
   mt::GemmMaps maps;
   memset(&maps, 0, sizeof(maps));
   for (int lr = 0; lr < c->nlocal; ++lr) {

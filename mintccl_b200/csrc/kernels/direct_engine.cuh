@@ -191,7 +191,7 @@ __device__ __forceinline__ u128 mc_ld_reduce<U8>(const void* p) { return load128
 
 // NVLS loops with several multimem operations in flight per thread (a multimem round trip through the
 // switch is several microseconds, so the depth matters more than for plain peer loads).
-static constexpr int kNvlsUnroll = 8;
+static constexpr int kNvlsUnroll = 4;
 // dst[i] = sum over all ranks of mc_src[i]; dst is local memory, or the multicast alias when TO_MC.
 template <class T, int NTHREADS, bool TO_MC>
 __device__ __forceinline__ void nvls_reduce_range(const uint8_t* mc_src, uint8_t* dst, uint64_t nvec) {
@@ -227,6 +227,30 @@ __device__ __forceinline__ void nvls_bcast_range(const uint8_t* src, uint8_t* mc
     for (int u = 0; u < kNvlsUnroll; ++u) {
       const uint64_t i = base + (uint64_t)u * NTHREADS + threadIdx.x;
       if (i < nvec) multimem_st_128(mc_dst + (i << 4), v[u]);
+    }
+  }
+}
+
+// dst_off of every peer (and local_dst unless skip_local) = src, reading each vector once.
+template <int NTHREADS>
+__device__ __forceinline__ void bcast_fanout(const MtDevComm& c, const uint8_t* src, uint64_t dst_off, uint8_t* local_dst,
+                                             uint64_t nbytes, bool skip_local) {
+  const int n = c.nranks;
+  const uint64_t nvec = nbytes >> 4;
+  for (uint64_t base = 0; base < nvec; base += (uint64_t)NTHREADS * kDirectUnroll) {
+    u128 v[kDirectUnroll];
+#pragma unroll
+    for (int u = 0; u < kDirectUnroll; ++u) {
+      const uint64_t i = base + (uint64_t)u * NTHREADS + threadIdx.x;
+      if (i < nvec) v[u] = load128_relaxed_sys(src + (i << 4));
+    }
+#pragma unroll
+    for (int u = 0; u < kDirectUnroll; ++u) {
+      const uint64_t i = base + (uint64_t)u * NTHREADS + threadIdx.x;
+      if (i < nvec) {
+        for (int d = 1; d < n; ++d) store128_relaxed_sys(c.heap[(c.rank + d) % n] + dst_off + (i << 4), v[u]);
+        if (!skip_local) *reinterpret_cast<u128*>(local_dst + (i << 4)) = v[u];
+      }
     }
   }
 }
@@ -332,31 +356,20 @@ __device__ void direct_body(const MtDevComm& c, const DirectArgs& a, int lr, int
     case DOP_BROADCAST: {
       const MtRange r = mt_split(B, ncta, cta, kSplitAlignDirect);
       if (a.variant == 2) {
-        // scatter + all-gather: the root hands sub-slice j to rank j, then every rank replicates its
-        // sub-slice (multimem.st, or plain stores to every peer).  One source can only inject so many
-        // multicast stores per second; spreading the replication over all ranks lifts that limit.
+        // pull + replicate: rank j fetches sub-slice j straight from the root's buffer and replicates it
+        // to everybody (one multimem.st per vector, or plain stores to every peer).  The root's link only
+        // carries each byte once, the replication is spread over all ranks (a single source of multicast
+        // stores tops out near 400 GB/s), and there is no phase in which only the root's link is busy.
         const uint64_t len = r.hi - r.lo;
-        if (me == a.root && len) {
-          for (int d = 1; d < n; ++d) {
-            const int j = (me + d) % n;
-            const MtRange sj = mt_split(len, n, j, 16);
-            if (sj.hi > sj.lo)
-              copy_range<NTHREADS, false, true>(in + r.lo + sj.lo, c.heap[j] + a.out_off + r.lo + sj.lo, sj.hi - sj.lo);
-          }
-        }
-        if (!rank_barrier(c, cta, s_fail)) return;
         const MtRange sm = mt_split(len, n, me, 16);
         if (sm.hi > sm.lo) {
-          const uint8_t* src = (me == a.root ? in : out) + r.lo + sm.lo;
+          const uint8_t* src = (me == a.root ? in : c.heap[a.root] + a.in_off) + r.lo + sm.lo;
           const uint64_t nb = sm.hi - sm.lo;
           if (a.nvls) {
-            nvls_bcast_range<NTHREADS, true>(src, c.mc + a.out_off + r.lo + sm.lo, nb >> 4);
+            if (me == a.root) nvls_bcast_range<NTHREADS, false>(src, c.mc + a.out_off + r.lo + sm.lo, nb >> 4);
+            else nvls_bcast_range<NTHREADS, true>(src, c.mc + a.out_off + r.lo + sm.lo, nb >> 4);
           } else {
-            for (int d = 1; d < n; ++d) {
-              const int p = (me + d) % n;
-              copy_range<NTHREADS, true, true>(src, c.heap[p] + a.out_off + r.lo + sm.lo, nb);
-            }
-            if (me == a.root && in != out) copy_range<NTHREADS, false, false>(src, out + r.lo + sm.lo, nb);
+            bcast_fanout<NTHREADS>(c, src, a.out_off + r.lo + sm.lo, out + r.lo + sm.lo, nb, me == a.root && in == out);
           }
         }
         break;
@@ -400,6 +413,19 @@ __device__ void direct_body(const MtDevComm& c, const DirectArgs& a, int lr, int
           } else {
             pull_reduce_range<T, NTHREADS, false, false>(c, a.in_off, 0, dst, lo, hi, 0);
           }
+        }
+        break;
+      }
+      if (a.variant == 3) {
+        // the root only receives: the other n - 1 ranks each sum one sub-slice (pulling it from everybody,
+        // the root included) and store the result into the root's output.  Every link then carries about
+        // one message size, where "root sums everything" puts (n - 1) messages on the root's link.
+        if (me != a.root) {
+          const int idx = mt_mod(me - a.root - 1, n);
+          const MtRange sm = mt_split(r.hi - r.lo, n - 1, idx, 16);
+          if (sm.hi > sm.lo)
+            pull_reduce_range<T, NTHREADS, false, false>(c, a.in_off, 0, c.heap[a.root] + a.out_off, r.lo + sm.lo,
+                                                         r.lo + sm.hi, 0);
         }
         break;
       }

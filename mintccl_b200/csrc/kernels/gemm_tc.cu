@@ -44,7 +44,7 @@ constexpr uint32_t TMEM_COLS = 512;
 
 // comm CTAs: ring of COMM_SLOTS pieces in shared memory, loads run COMM_LAG pieces ahead of stores
 constexpr uint32_t COMM_PIECE = 32768;
-constexpr int COMM_SLOTS = 6, COMM_LAG = 3;
+constexpr int COMM_SLOTS = 6, COMM_LAG = 3, COMM_SIGLAG = 12;
 struct CommCtl {
   uint64_t full[COMM_SLOTS];
   int abort;
@@ -182,8 +182,8 @@ __device__ void rs_reduce_loop(const GemmArgs& a, int lr) {
             const int v = v0 + u * kGemmThreads;
             if (v < BM * (BN / 8)) {
               const int rr = v / (BN / 8), cv = v % (BN / 8);
-              w[u] = load128_relaxed_sys(stage + ((uint64_t)s * per_rows + (uint64_t)mbl * BM + rr) * ld_bytes +
-                                         (uint64_t)nb * BN * 2 + cv * 16);
+              w[u] = load128_relaxed_sys(stage + (((uint64_t)s * per + mbl) * nbs + nb) * (uint64_t)(BM * BN * 2) +
+                                         (uint64_t)rr * (BN * 2) + cv * 16);
             }
           }
 #pragma unroll
@@ -242,19 +242,61 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_c
     // One thread drives the copy engine: bulk copies local HBM -> shared memory ring -> peer HBM, so a
     // handful of CTAs keeps hundreds of KiB in flight and the other SMs stay free for the GEMM.
     CommCtl* cm = (CommCtl*)(sEpi + EPI_BYTES);
+    const bool pull = a.comm_mode == 1;
+    if (a.comm_mode == 2) {
+      // plain loads and peer stores from every thread of the CTA (no copy engine)
+      const uint64_t chunk_bytes = (uint64_t)BM * row_bytes;
+      const int split = a.comm_split, ngroups = ncomm / split, grp = cc / split;
+      const MtRange r = mt_split(chunk_bytes, split, cc % split, 128);
+      if (grp >= ngroups) return;
+      for (int w = grp; w < chunks * (n - 1); w += ngroups) {
+        {
+          const int p = (me + 1 + w / chunks) % n, ci = w % chunks;
+          uint8_t* dst = c.heap[p] + a.gather_off + (uint64_t)me * shard_rows * row_bytes;
+          uint64_t* cnt = (uint64_t*)(c.heap[p] + a.flags_off) + (uint64_t)me * chunks;
+          const uint64_t base = (uint64_t)ci * chunk_bytes + r.lo;
+          const uint64_t nvec = (r.hi - r.lo) >> 4;
+          for (uint64_t i0 = 0; i0 < nvec; i0 += (uint64_t)kGemmThreads * 8) {
+            u128 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const uint64_t i = i0 + (uint64_t)u * kGemmThreads + threadIdx.x;
+              if (i < nvec) v[u] = load128_stream(src + base + (i << 4));
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const uint64_t i = i0 + (uint64_t)u * kGemmThreads + threadIdx.x;
+              if (i < nvec) store128_relaxed_sys(dst + base + (i << 4), v[u]);
+            }
+          }
+          __syncthreads();
+          if (threadIdx.x == 0) {
+            fence_acq_rel_sys();
+            asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(cnt + ci), "l"(1ull) : "memory");
+          }
+        }
+      }
+      return;
+    }
     if (threadIdx.x == 0) {
       for (int s = 0; s < COMM_SLOTS; ++s) mbar_init(&cm->full[s], 1);
       cm->abort = 0;
       fence_barrier_init();
+      // The comm CTAs form groups of `split` CTAs; a group moves whole 128-row chunks (each CTA a contiguous
+      // 1/split of it), the groups work on different chunks at the same time.  Few large contiguous streams
+      // per chunk use the link better than every CTA touching every chunk.
       const uint64_t chunk_bytes = (uint64_t)BM * row_bytes;
-      const MtRange r = mt_split(chunk_bytes, ncomm, cc, 128);
+      const int split = a.comm_split, ngroups = ncomm / split, grp = cc / split;
+      const MtRange r = mt_split(chunk_bytes, split, cc % split, 128);
       const uint32_t ppc = (uint32_t)mt_div_up(r.hi - r.lo, COMM_PIECE);   // pieces per chunk for this CTA
-      const uint32_t total = ppc * (uint32_t)chunks * (uint32_t)(n - 1);
+      const uint32_t npairs = (uint32_t)chunks * (uint32_t)(n - 1);       // (peer, chunk) pairs, in push order
+      const uint32_t mine = grp < ngroups ? (npairs - grp + ngroups - 1) / ngroups : 0;  // pairs grp, grp+ngroups, ...
+      const uint32_t total = ppc * mine;
       volatile int* ab = &cm->abort;
       auto locate = [&](uint32_t i, int& p, int& ci, uint64_t& off, uint32_t& nb) {
-        const uint32_t piece = i % ppc, ch_i = i / ppc;
+        const uint32_t piece = i % ppc, ch_i = grp + (i / ppc) * ngroups;
         ci = (int)(ch_i % chunks);
-        p = (me + 1 + (int)(ch_i / chunks)) % n;
+        p = pull ? mt_mod(me - 1 - (int)(ch_i / chunks), n) : (me + 1 + (int)(ch_i / chunks)) % n;
         off = (uint64_t)ci * chunk_bytes + r.lo + (uint64_t)piece * COMM_PIECE;
         const uint64_t left = r.hi - r.lo - (uint64_t)piece * COMM_PIECE;
         nb = (uint32_t)(left < COMM_PIECE ? left : COMM_PIECE);
@@ -264,9 +306,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_c
         uint64_t off;
         uint32_t nb;
         locate(i, p, ci, off, nb);
-        uint64_t* cnt = (uint64_t*)(c.heap[p] + a.flags_off) + (uint64_t)me * chunks + ci;
-        asm volatile("fence.proxy.async;" ::: "memory");
-        fence_acq_rel_sys();
+        // push: count on the peer, in my row of its counters; pull: count locally, in the peer's row
+        uint64_t* cnt = pull ? (uint64_t*)(c.heap[me] + a.flags_off) + (uint64_t)p * chunks + ci
+                             : (uint64_t*)(c.heap[p] + a.flags_off) + (uint64_t)me * chunks + ci;
+        // the bulk stores of this chunk have completed (wait_group above); the release orders them before
+        // the count.  No proxy fence here: it would drain every copy still in flight.
         asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(cnt), "l"(1ull) : "memory");
       };
       bool ok = ppc > 0;
@@ -282,7 +326,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_c
           mbar_expect_tx(&cm->full[s_], nb);
           asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
                            smem_u32(smem + (uint64_t)s_ * COMM_PIECE)),
-                       "l"(src + off), "r"(nb), "r"(smem_u32(&cm->full[s_]))
+                       "l"(pull ? c.heap[p] + a.shard_off + off : src + off), "r"(nb), "r"(smem_u32(&cm->full[s_]))
                        : "memory");
         }
         if (i >= COMM_LAG) {
@@ -296,26 +340,31 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_c
             ok = false;
             break;
           }
-          uint8_t* dst = c.heap[p] + a.gather_off + (uint64_t)me * shard_rows * row_bytes + off;
+          uint8_t* dst = pull ? c.heap[me] + a.gather_off + (uint64_t)p * shard_rows * row_bytes + off
+                              : c.heap[p] + a.gather_off + (uint64_t)me * shard_rows * row_bytes + off;
           asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst),
                        "r"(smem_u32(smem + (uint64_t)s_ * COMM_PIECE)), "r"(nb)
                        : "memory");
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-          // piece j - COMM_LAG completed its chunk?  Then all but the COMM_LAG newest stores are done.
-          if (j >= COMM_LAG && ((j - COMM_LAG) % ppc) == ppc - 1) {
-            asm volatile("cp.async.bulk.wait_group %0;" ::"n"(COMM_LAG) : "memory");
-            signal(j - COMM_LAG);
+          // A chunk is announced once its last store has COMPLETED (not merely left shared memory).  That
+          // takes a round trip to the peer, so announcements trail the stores by COMM_SIGLAG pieces: up to
+          // that many stores are in flight per CTA and nothing waits for an acknowledgement it needs now.
+          if (j >= COMM_SIGLAG && ((j - COMM_SIGLAG) % ppc) == ppc - 1) {
+            asm volatile("cp.async.bulk.wait_group %0;" ::"n"(COMM_SIGLAG) : "memory");
+            signal(j - COMM_SIGLAG);
           }
         }
       }
       asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
       if (ok) {
-        for (uint32_t j = total > COMM_LAG ? total - COMM_LAG : 0; j < total; ++j)
+        for (uint32_t j = total > COMM_SIGLAG ? total - COMM_SIGLAG : 0; j < total; ++j)
           if (j % ppc == ppc - 1) signal(j);
       } else {
         gemm_report(a, lr, MT_WHERE_GEMM_FLAG);
       }
     }
+    // pull: the peers read my rows; they must stay untouched until everybody has finished reading
+    if (pull) rank_barrier(c, cc, &s_fail);
     return;
   }
 
@@ -372,7 +421,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_c
             // rows pushed by `owner`: wait until all comm CTAs of that rank have counted this block in
             const int per = (a.M / a.nranks) / BM;
             const uint64_t* cnt = (const uint64_t*)a.flags_local[lr] + (uint64_t)tc_.owner * per + (tc_.mb % per);
-            const uint64_t want = a.epoch * (uint64_t)a.ncomm;
+            const uint64_t want = a.epoch * (uint64_t)a.comm_split;  // every CTA of the group counts the chunk once
             uint32_t spins = 0;
             uint64_t t0 = 0;
             while (load64_acquire_sys(cnt) < want) {
@@ -451,11 +500,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_c
       uint64_t ld_bytes;
       if (MODE == MODE_GEMM_RS) {
         // partial tile -> staging[my rank] of the owner (peer memory unless the owner is this rank)
+        // The staging area is tile-major: [source rank][row block][column block][128 x 256], so a CTA
+        // writes one contiguous 64 KiB region (contiguous streams use the link far better than rows
+        // interleaved with other CTAs' rows).
         const MtDevComm& c = a.comms[lr];
-        const int per_rows = a.M / a.nranks;
-        ld_bytes = (uint64_t)a.N * 2;
-        dst = c.heap[tc_.owner] + a.stage_off + ((uint64_t)a.rank[lr] * per_rows + (tc_.mb * BM - tc_.owner * per_rows)) * ld_bytes +
-              (uint64_t)tc_.nb * BN * 2;
+        const int per = (a.M / a.nranks) / BM;
+        ld_bytes = (uint64_t)BN * 2;
+        dst = c.heap[tc_.owner] + a.stage_off +
+              (((uint64_t)a.rank[lr] * per + (tc_.mb % per)) * (a.N / BN) + tc_.nb) * (uint64_t)(BM * BN * 2);
       } else {
         ld_bytes = (uint64_t)a.ldc * 2;
         dst = (uint8_t*)a.c[lr] + (uint64_t)tc_.mb * BM * ld_bytes + (uint64_t)tc_.nb * BN * 2;
@@ -519,7 +571,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_c
           const int per = (a.M / a.nranks) / BM;
           uint64_t* cnt = (uint64_t*)(c.heap[tc_.owner] + a.flags_off) +
                           ((uint64_t)a.rank[lr] * per + (tc_.mb % per)) * (a.N / BN) + tc_.nb;
-          fence_acq_rel_sys();
           asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(cnt), "l"(1ull) : "memory");
         }
       }

@@ -25,7 +25,10 @@ struct GemmArgs {
   int32_t rank[MT_MAX_RANKS];
   int32_t M, N, K, ldc;
   int32_t nranks;
-  int32_t ncomm;                       // AG_GEMM: CTAs that move data instead of computing
+  int32_t ncomm;                       // AG_GEMM: CTAs that move data instead of computing; GEMM_RS: reducers
+  int32_t comm_mode;                   // AG_GEMM: 0 copy-engine push, 1 copy-engine pull, 2 push with plain stores
+  int32_t comm_split;                  // AG_GEMM: comm CTAs that share one 128-row chunk
+  uint64_t shard_off;                  // AG_GEMM pull: heap offset of every rank's own rows
   uint64_t gather_off;                 // AG_GEMM: heap offset of the gathered A buffer [M, K]
   uint64_t flags_off;                  // heap offset of the arrival counters
   uint64_t stage_off;                  // GEMM_RS: heap offset of the partial tiles [n, M / n, N]

@@ -92,7 +92,7 @@ int mt_p2p(MtComm* c, void* stream, int src_rank, int dst_rank, const void* src_
 int mt_gemm(void* stream, const void* A, const void* B, void* C, int M, int N, int K, int ldc, int nctas);
 int mt_ag_gemm(MtComm* c, void* stream, const void* const* a_shard, const void* const* B, void* const* C,
                uint64_t gather_off, uint64_t flags_off, uint64_t epoch, int M, int N, int K, int ldc, int ncomm,
-               int nctas);
+               int nctas, int comm_mode, uint64_t shard_off, int comm_split);
 int mt_gemm_rs(MtComm* c, void* stream, const void* const* A, const void* const* B, void* const* out,
                uint64_t stage_off, uint64_t flags_off, uint64_t epoch, int M, int N, int K, int nred, int nctas);
 

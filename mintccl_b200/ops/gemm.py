@@ -66,8 +66,12 @@ class AllGatherGemm(_Fused):
     """Plan for ``allgather(a_shard)[M, K] @ w[N, K].T``: owns the gathered-input buffer and the arrival
     counters in the symmetric heap.  Create it collectively (same order on every rank), call it every step."""
 
-    def __init__(self, comm, M: int, N_: int, K: int, ncomm: int = 20):
+    MODES = {"push": 0, "pull": 1, "push_st": 2}
+
+    def __init__(self, comm, M: int, N_: int, K: int, ncomm: int = 16, mode: str = "push", split: int = 1):
         super().__init__(comm)
+        self.mode = self.MODES[mode]
+        self.split = max(1, min(split, ncomm))
         n = comm.world_size
         if M % (BM * n) or N_ % BN or K % BK:
             raise ValueError("M must be a multiple of 128 x world, N of 256, K of 64")
@@ -88,11 +92,17 @@ class AllGatherGemm(_Fused):
             _check(t, "operand")
         if tuple(a_s[0].shape) != (self.M // c.world_size, self.K) or tuple(ws[0].shape) != (self.N, self.K):
             raise ValueError("operand shapes do not match the plan")
+        shard_off = 0
+        if self.mode == 1:  # the peers read this rank's rows: they must sit at the same heap offset everywhere
+            offs = [c.symm_offset(t, lr) for lr, t in enumerate(a_s)]
+            if offs[0] is None or any(o != offs[0] for o in offs):
+                raise ValueError("mode='pull' needs a_shard from the symmetric heap")
+            shard_off = offs[0]
         self.epoch += 1
         rc = c.lib.mt_ag_gemm(c._handle, c._stream(), N.ptr_array([t.data_ptr() for t in a_s]),
                               N.ptr_array([t.data_ptr() for t in ws]), N.ptr_array([t.data_ptr() for t in outs]),
                               self._off(self.gathered), self._off(self.flags), self.epoch, self.M, self.N, self.K,
-                              outs[0].stride(0), self.ncomm, nctas)
+                              outs[0].stride(0), self.ncomm, nctas, self.mode, shard_off, self.split)
         if rc < 0:
             raise RuntimeError(f"mt_ag_gemm: {N.last_error()}")
         return outs if c.emulated else outs[0]

@@ -406,7 +406,7 @@ class Communicator:
                                      len(chain or []), nch))
 
     def _launch_direct(self, dop, ins, outs, in_off, out_off, nbytes, dtype, root=0, variant=0, nvls=False, nctas=None):
-        nctas = self._direct_ctas(nbytes, nctas)
+        nctas = self._direct_ctas(nbytes, nctas if nctas is not None or not nvls else min(64, self._direct_ctas(nbytes, None)))
         if nvls and (nbytes % 16 or (in_off or 0) % 16 or (out_off or 0) % 16
                      or any(t is not None and t.data_ptr() % 16 for t in list(ins) + list(outs))):
             raise ValueError("NVLS algorithms need 16-byte aligned buffers and a byte count that is a multiple of 16")
@@ -656,8 +656,10 @@ class Communicator:
             # ("reduce-scatter + gather"); otherwise ("direct1"/"nvls1" force this) the root sums everything
             out_off = self._symm_off_all(outs)
             spread = out_off is not None and not algo.endswith("1") and self.world_size > 2 and nbytes % 16 == 0
+            # NVLS: every rank sums 1/n in the switch; plain loads: the n - 1 other ranks sum 1/(n-1) each
+            variant = 0 if not spread else (2 if algo.startswith("nvls") else 3)
             self._launch_direct(N.DOP_REDUCE, ins, outs, off, out_off if spread else 0, nbytes, dt, root=root,
-                                variant=2 if spread else 0, nvls=algo.startswith("nvls"), nctas=nch)
+                                variant=variant, nvls=algo.startswith("nvls"), nctas=nch)
         else:
             self._launch_ring(N.OP_REDUCE, ins, outs, nbytes, dt, self._pick_proto(nbytes, proto), root=root, nch=nch)
 
