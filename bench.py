@@ -89,7 +89,7 @@ class Work:
         if impl == "mintccl_b200":
             import mintccl_b200
             from mintccl_b200 import Config
-            heap = max(2 << 30, 8 * size + (2 << 30))
+            heap = 8 * size + (4 << 30)
             self.comm = mintccl_b200.Communicator(config=Config.from_env(heap_bytes=heap))
             alloc = lambda *shape: self.comm.symm_empty(shape, torch.float16)  # noqa: E731
         else:

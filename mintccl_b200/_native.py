@@ -14,7 +14,7 @@ _LIB_PATH = Path(__file__).resolve().parent / "_C" / "libmintccl_b200.so"
 _lib = None
 
 MT_MAX_RANKS = 8
-MT_MAX_CHANNELS = 32
+MT_MAX_CHANNELS = 96
 PROTO_SIMPLE, PROTO_LL128 = 0, 1
 DT_F32, DT_F16, DT_BF16, DT_U8 = 0, 1, 2, 3
 OP_SENDRECV, OP_BROADCAST, OP_REDUCE, OP_ALLGATHER, OP_REDUCESCATTER, OP_ALLREDUCE = range(6)

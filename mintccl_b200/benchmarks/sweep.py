@@ -59,7 +59,7 @@ def main() -> None:
     esz = torch.empty((), dtype=dtype).element_size()
     lo, hi = parse_size(a.size_lo), parse_size(a.size_hi)
     pool_bytes = max(4 * hi, 512 << 20)
-    comm = mintccl_b200.Communicator(group=gloo, config=Config.from_env(heap_bytes=2 * pool_bytes + (3 << 30)))
+    comm = mintccl_b200.Communicator(group=gloo, config=Config.from_env(heap_bytes=2 * pool_bytes + (4 << 30)))
     n = world
 
     sizes = []

@@ -27,7 +27,7 @@ def main() -> None:
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--ffn", type=int, default=14336)
     ap.add_argument("--iters", type=int, default=20)
-    ap.add_argument("--ncomm", default="16", help="comma list of comm-CTA counts to try for the all-gather fusion")
+    ap.add_argument("--ncomm", default="24", help="comma list of comm-CTA counts to try for the all-gather fusion")
     ap.add_argument("--split", default="1", help="comma list: comm CTAs that share one 128-row chunk")
     ap.add_argument("--modes", default="push", help="comma list of all-gather transports: push, pull, push_st")
     a = ap.parse_args()
@@ -39,7 +39,7 @@ def main() -> None:
     import mintccl_b200
     from mintccl_b200 import Config
     from mintccl_b200.ops.gemm import AllGatherGemm, GemmReduceScatter, gemm
-    comm = mintccl_b200.Communicator(group=gloo, config=Config.from_env(heap_bytes=4 << 30))
+    comm = mintccl_b200.Communicator(group=gloo, config=Config.from_env(heap_bytes=6 << 30))
     n, T, H = world, a.tokens, a.hidden
     F = a.ffn // n // 256 * 256  # the kernels tile N in 256 columns
     g = torch.Generator(device="cuda").manual_seed(rank)

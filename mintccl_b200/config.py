@@ -58,7 +58,8 @@ def _is_pow2(x: int) -> bool:
 class Config:
     """All tunables of a communicator.  ``Config.from_env()`` reads the environment."""
     # reference knobs
-    num_blocks: int = 16                  # MINTCCL_NUM_BLOCKS: channels (CTAs) of ring kernels
+    num_blocks: int = 0                   # MINTCCL_NUM_BLOCKS: most channels (CTAs) of a ring kernel; 0 = up to
+                                          # max_channels, by message size (the reference always uses 16)
     num_warps: int = 16                   # MINTCCL_NUM_WARPS: fixed at 16 in the compiled kernels
     buff_size: int = 4 << 20              # MINTCCL_BUFFSIZE: Simple FIFO bytes per connection
     test_mode: bool = False               # MINTCCL_TEST_MODE
@@ -67,14 +68,15 @@ class Config:
     # algorithm / protocol selection
     algo: str = "auto"                    # ring | direct | nvls | ll | auto
     proto: str = "auto"                   # simple | ll128 | auto
-    max_channels: int = 16                # channels the FIFOs are sized for
-    direct_ctas: int = 0                  # CTAs of direct/NVLS kernels (0 = by message size)
+    max_channels: int = 64                # channels the FIFOs are sized for
+    direct_ctas: int = 0                  # CTAs of direct kernels (0 = by message size, at most 128)
+    nvls_ctas: int = 32                   # most CTAs of an NVLS kernel (the switch saturates with few)
     simple_slots: int = 4
     ll128_slot_bytes: int = 128 << 10
     ll128_slots: int = 4
     ll_bytes: int = 256 << 10             # one-shot area per (parity, sender)
     scratch_bytes: int = 64 << 20
-    heap_bytes: int = 2 << 30
+    heap_bytes: int = 4 << 30
     wait_timeout_ms: int = 10000
     heap_kind: str = "auto"               # vmm | ipc | auto
     nvls: str = "auto"                    # on | off | auto
@@ -90,8 +92,8 @@ class Config:
         return self.buff_size // self.simple_slots
 
     def validate(self) -> "Config":
-        if not 1 <= self.num_blocks <= self.max_channels <= 32:
-            raise ValueError("need 1 <= MINTCCL_NUM_BLOCKS <= MINTCCL_MAX_CHANNELS <= 32")
+        if not 0 <= self.num_blocks <= self.max_channels <= 96 or self.max_channels < 1:
+            raise ValueError("need 0 <= MINTCCL_NUM_BLOCKS <= MINTCCL_MAX_CHANNELS <= 96")
         if self.num_warps != 16:
             raise ValueError("MINTCCL_NUM_WARPS: the compiled kernels use 16 warps per CTA")
         if not _is_pow2(self.buff_size) or self.buff_size < 64 << 10:
@@ -109,7 +111,7 @@ class Config:
     @classmethod
     def from_env(cls, **overrides) -> "Config":
         c = cls(
-            num_blocks=env_int("MINTCCL_NUM_BLOCKS", 16),
+            num_blocks=env_int("MINTCCL_NUM_BLOCKS", 0),
             num_warps=env_int("MINTCCL_NUM_WARPS", 16),
             buff_size=env_int("MINTCCL_BUFFSIZE", 4 << 20),
             test_mode=env_bool("MINTCCL_TEST_MODE", False),
@@ -117,14 +119,15 @@ class Config:
             verbose=env_bool("MINTCCL_TEST_VERBOSE", False),
             algo=env_str("MINTCCL_ALGO", "auto", ("ring", "direct", "nvls", "ll", "auto")),
             proto=env_str("MINTCCL_PROTO", "auto", ("simple", "ll128", "auto")),
-            max_channels=env_int("MINTCCL_MAX_CHANNELS", 16),
+            max_channels=env_int("MINTCCL_MAX_CHANNELS", 64),
             direct_ctas=env_int("MINTCCL_DIRECT_CTAS", 0),
+            nvls_ctas=env_int("MINTCCL_NVLS_CTAS", 32),
             simple_slots=env_int("MINTCCL_SIMPLE_SLOTS", 4),
             ll128_slot_bytes=env_int("MINTCCL_LL128_SLOT_BYTES", 128 << 10),
             ll128_slots=env_int("MINTCCL_LL128_SLOTS", 4),
             ll_bytes=env_int("MINTCCL_LL_BYTES", 256 << 10),
             scratch_bytes=env_int("MINTCCL_SCRATCH_BYTES", 64 << 20),
-            heap_bytes=env_int("MINTCCL_HEAP_BYTES", 2 << 30),
+            heap_bytes=env_int("MINTCCL_HEAP_BYTES", 4 << 30),
             wait_timeout_ms=env_int("MINTCCL_WAIT_TIMEOUT_MS", 10000),
             heap_kind=env_str("MINTCCL_HEAP", "auto", ("vmm", "ipc", "auto")),
             nvls=env_str("MINTCCL_NVLS", "auto", ("on", "off", "auto")),

@@ -11,7 +11,7 @@
 #include <stdint.h>
 
 #define MT_MAX_RANKS 8
-#define MT_MAX_CHANNELS 32
+#define MT_MAX_CHANNELS 96
 #define MT_MAX_BAR_SLOTS 160   // one barrier slot per CTA of a direct/NVLS kernel (>= 148 SMs)
 
 // Protocol ids (index into per-protocol arrays of the layout).

@@ -130,7 +130,7 @@ void mt_reset_launch_count(void) { g_launches.store(0); }
 
 static int check_cfg(const MtConfig* cfg, int nranks) {
   if (nranks < 1 || nranks > MT_MAX_RANKS) return fail("nranks must be in [1, 8]");
-  if (cfg->nchannels < 1 || cfg->nchannels > MT_MAX_CHANNELS) return fail("nchannels must be in [1, 32]");
+  if (cfg->nchannels < 1 || cfg->nchannels > MT_MAX_CHANNELS) return fail("nchannels must be in [1, 96]");
   if (cfg->simple_slots < 1 || cfg->ll128_slots < 1) return fail("need at least one FIFO slot");
   if (cfg->simple_slot_bytes % 128 || cfg->ll128_slot_bytes % MT_LL128_WARP_WIRE || cfg->ll_bytes % MT_LL128_WARP_WIRE)
     return fail("slot sizes must be multiples of 128 (Simple) / 2048 (LL128, one-shot)");

@@ -68,7 +68,7 @@ class AllGatherGemm(_Fused):
 
     MODES = {"push": 0, "pull": 1, "push_st": 2}
 
-    def __init__(self, comm, M: int, N_: int, K: int, ncomm: int = 16, mode: str = "push", split: int = 1):
+    def __init__(self, comm, M: int, N_: int, K: int, ncomm: int = 24, mode: str = "push", split: int = 1):
         super().__init__(comm)
         self.mode = self.MODES[mode]
         self.split = max(1, min(split, ncomm))

@@ -360,7 +360,7 @@ class Communicator:
         return offs[0]
 
     def _ring_channels(self, nbytes: int, proto: int, nch: Optional[int]) -> int:
-        cap = self.cfg.num_blocks
+        cap = self.cfg.num_blocks or self.cfg.max_channels
         if self.world_size == 1:
             cap = 296  # local copies only: no FIFO limits the channel count, fill the 148 SMs twice
         if self.emulated:
@@ -406,7 +406,7 @@ class Communicator:
                                      len(chain or []), nch))
 
     def _launch_direct(self, dop, ins, outs, in_off, out_off, nbytes, dtype, root=0, variant=0, nvls=False, nctas=None):
-        nctas = self._direct_ctas(nbytes, nctas if nctas is not None or not nvls else min(64, self._direct_ctas(nbytes, None)))
+        nctas = self._direct_ctas(nbytes, nctas if nctas is not None or not nvls else min(self.cfg.nvls_ctas, self._direct_ctas(nbytes, None)))
         if nvls and (nbytes % 16 or (in_off or 0) % 16 or (out_off or 0) % 16
                      or any(t is not None and t.data_ptr() % 16 for t in list(ins) + list(outs))):
             raise ValueError("NVLS algorithms need 16-byte aligned buffers and a byte count that is a multiple of 16")
@@ -600,7 +600,11 @@ class Communicator:
         algo = self._algo(algo)
         off = self._symm_off_all(ts)
         if algo == "auto":
-            if off is not None and self._want_nvls(nbytes, ts):
+            ring_wide = (self.cfg.num_blocks or self.cfg.max_channels) >= 48
+            if self.world_size >= 4 and nbytes >= (32 << 20) and ring_wide:
+                algo = "ring"     # 48+ channels of the pipelined Simple chain fill the links (measured
+                                  # 631 GB/s at 1 GiB on 4 GPUs against 528 for the multicast variant)
+            elif off is not None and self._want_nvls(nbytes, ts):
                 algo = "nvls"
             elif off is not None and self.world_size == 2 and nbytes > (64 << 10):
                 algo = "direct"   # two ranks: the root pushes once, nothing to pipeline

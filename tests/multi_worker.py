@@ -27,7 +27,7 @@ def main():
     from mintccl_b200 import Config
     rank, n = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
-    cfg = Config.from_env(heap_bytes=3 << 30, wait_timeout_ms=5000)
+    cfg = Config.from_env(heap_bytes=4 << 30, wait_timeout_ms=5000)
     c = mintccl_b200.Communicator(config=cfg)
     print(f"[r{rank}] heap={c.heap_kind} nvls={c.nvls} ring={c.ring}", flush=True)
     dtypes = [torch.float32, torch.float16, torch.bfloat16]

@@ -25,7 +25,8 @@ def test_config_defaults_match_reference_knobs(monkeypatch):
         if k.startswith("MINTCCL_"):
             monkeypatch.delenv(k)
     c = m.Config.from_env()
-    assert (c.num_blocks, c.num_warps, c.buff_size, c.test_count) == (16, 16, 4194304, 67108864)
+    # MINTCCL_NUM_BLOCKS defaults to "automatic" (0) here; the reference always launches 16 CTAs
+    assert (c.num_blocks, c.num_warps, c.buff_size, c.test_count) == (0, 16, 4194304, 67108864)
     assert m.WARP_SIZE == 32 and m.VECTORIZED_BYTES == 16 and m.NULL == 0
     monkeypatch.setenv("MINTCCL_NUM_BLOCKS", "8")
     monkeypatch.setenv("MINTCCL_BUFFSIZE", "1M")
