@@ -385,6 +385,8 @@ class Communicator:
 
     def _pick_proto(self, nbytes: int, proto: Optional[str]) -> int:
         p = proto or self.cfg.proto
+        if self.world_size == 1:
+            return N.PROTO_SIMPLE  # a single rank only copies locally: no flags to carry
         if p == "simple":
             return N.PROTO_SIMPLE
         if p == "ll128":
