@@ -27,7 +27,7 @@ def main() -> None:
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--ffn", type=int, default=14336)
     ap.add_argument("--iters", type=int, default=20)
-    ap.add_argument("--ncomm", default="24", help="comma list of comm-CTA counts to try for the all-gather fusion")
+    ap.add_argument("--ncomm", default="0", help="comma list of comm-CTA counts to try for the all-gather fusion")
     ap.add_argument("--split", default="1", help="comma list: comm CTAs that share one 128-row chunk")
     ap.add_argument("--modes", default="push", help="comma list of all-gather transports: push, pull, push_st")
     a = ap.parse_args()
@@ -94,9 +94,10 @@ def main() -> None:
     h = torch.empty(T, F, device="cuda", dtype=torch.bfloat16)
     best = None
     for mode, nc, sp in [(m, int(v), int(q)) for m in a.modes.split(",") for v in a.ncomm.split(",") for q in a.split.split(",")]:
-        if sp > nc:
+        if nc and sp > nc:
             continue
-        plan = AllGatherGemm(comm, T, F, H, ncomm=nc, mode=mode, split=sp)
+        plan = AllGatherGemm(comm, T, F, H, ncomm=nc or None, mode=mode, split=sp)
+        nc = plan.ncomm
         us = timed(lambda: plan(x_shard, w_up, out=h))
         comm.check()
         out[f"up_fused_us_{mode}_ncomm{nc}_split{sp}"] = round(us, 1)

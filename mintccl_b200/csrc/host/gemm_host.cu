@@ -6,6 +6,7 @@
 #include <string>
 
 #include "../kernels/gemm_tc.h"
+#include "../kernels/mxfp8.h"
 #include "comm_internal.h"
 
 using mthost::fail;
@@ -169,6 +170,35 @@ int mt_gemm_rs(MtComm* c, void* stream, const void* const* A, const void* const*
   }
   cudaError_t e = mt::launch_gemm_tc(mt::MODE_GEMM_RS, maps, a, grid, c->nlocal, (cudaStream_t)stream);
   if (e != cudaSuccess) return fail(std::string("gemm_rs launch: ") + cudaGetErrorString(e));
+  return 0;
+}
+
+// Sum of MXFP8 tensors (e4m3 payload + ue8m0 scale per 32 elements) over all ranks.  op 0: all-reduce into
+// (data_out_off, scale_out_off) of every rank; op 1: reduce-scatter, shard `rank` into the local outputs.
+int mt_mxfp8_reduce(MtComm* c, void* stream, int op, uint64_t data_in_off, uint64_t scale_in_off,
+                    uint64_t data_out_off, uint64_t scale_out_off, void* const* data_out, void* const* scale_out,
+                    uint64_t nelems, int nctas) {
+  if (!c || !c->d_comms) return fail("communicator is not finalized");
+  if (nelems % 32) return fail("MXFP8 tensors hold whole blocks of 32 elements");
+  const uint64_t nblocks = nelems / 32;
+  if (op == mt::MX_REDUCESCATTER && nblocks % c->nranks) return fail("blocks must divide evenly over the ranks");
+  if ((data_in_off | data_out_off) & 15) return fail("MXFP8 payloads must be 16-byte aligned");
+  if (nctas < 1 || nctas > 148) return fail("nctas out of range");
+  if (c->emulated && nctas * c->nlocal > 148) nctas = 148 / c->nlocal;
+  mt::Mxfp8Args a;
+  memset(&a, 0, sizeof(a));
+  a.data_in_off = data_in_off;
+  a.scale_in_off = scale_in_off;
+  a.data_out_off = data_out_off;
+  a.scale_out_off = scale_out_off;
+  a.nblocks = nblocks;
+  a.op = op;
+  for (int lr = 0; lr < c->nlocal; ++lr) {
+    a.data_out[lr] = data_out ? data_out[lr] : nullptr;
+    a.scale_out[lr] = scale_out ? scale_out[lr] : nullptr;
+  }
+  cudaError_t e = mt::launch_mxfp8(c->d_comms, a, nctas, c->nlocal, (cudaStream_t)stream);
+  if (e != cudaSuccess) return fail(std::string("mxfp8 launch: ") + cudaGetErrorString(e));
   return 0;
 }
 

@@ -96,6 +96,10 @@ int mt_ag_gemm(MtComm* c, void* stream, const void* const* a_shard, const void* 
 int mt_gemm_rs(MtComm* c, void* stream, const void* const* A, const void* const* B, void* const* out,
                uint64_t stage_off, uint64_t flags_off, uint64_t epoch, int M, int N, int K, int nred, int nctas);
 
+int mt_mxfp8_reduce(MtComm* c, void* stream, int op, uint64_t data_in_off, uint64_t scale_in_off,
+                    uint64_t data_out_off, uint64_t scale_out_off, void* const* data_out, void* const* scale_out,
+                    uint64_t nelems, int nctas);
+
 // ---- device-wait self test: a wait nothing satisfies must time out and report, not hang -----------
 int mt_test_wait_timeout(MtComm* c, void* stream);
 

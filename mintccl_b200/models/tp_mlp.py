@@ -55,7 +55,7 @@ class _MLPFunction(torch.autograd.Function):
 class TensorParallelMLP(torch.nn.Module):
     """``tokens`` is the global token count of a step (fixed: the fused plans own buffers of that size)."""
 
-    def __init__(self, comm, tokens: int, hidden: int, ffn: int, ncomm: int = 24, seed: int = 0):
+    def __init__(self, comm, tokens: int, hidden: int, ffn: int, ncomm: Optional[int] = None, seed: int = 0):
         super().__init__()
         n = comm.world_size
         if ffn % n or tokens % n:

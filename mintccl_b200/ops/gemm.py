@@ -68,9 +68,11 @@ class AllGatherGemm(_Fused):
 
     MODES = {"push": 0, "pull": 1, "push_st": 2}
 
-    def __init__(self, comm, M: int, N_: int, K: int, ncomm: int = 24, mode: str = "push", split: int = 1):
+    def __init__(self, comm, M: int, N_: int, K: int, ncomm: Optional[int] = None, mode: str = "push", split: int = 1):
         super().__init__(comm)
         self.mode = self.MODES[mode]
+        if ncomm is None:
+            ncomm = self.pick_ncomm((M // BM) * (N_ // BN))
         self.split = max(1, min(split, ncomm))
         n = comm.world_size
         if M % (BM * n) or N_ % BN or K % BK:
@@ -80,6 +82,14 @@ class AllGatherGemm(_Fused):
         self.flags = comm.symm_zeros((n * (M // n // BM),), torch.int64)
         torch.cuda.synchronize()
         comm.control.barrier()
+
+    @staticmethod
+    def pick_ncomm(tiles: int, sms: int = 148, lo: int = 16, hi: int = 40) -> int:
+        """Comm CTAs for a problem of ``tiles`` output tiles: the GEMM takes ceil(tiles / (sms - ncomm)) waves,
+        so take the most comm CTAs (faster transfer) that do not add a wave over the fewest allowed."""
+        waves = lambda nc: -(-tiles // (sms - nc))  # noqa: E731
+        best = min(waves(nc) for nc in range(lo, hi + 1))
+        return max(nc for nc in range(lo, hi + 1) if waves(nc) == best)
 
     def __call__(self, a_shard: TensorOrList, w: TensorOrList, out: Optional[TensorOrList] = None, nctas: int = 0):
         c = self.comm

@@ -1,0 +1,87 @@
+"""MXFP8 (block-scaled fp8) tensors and their sum over ranks.
+
+Format: ``float8_e4m3fn`` payload, one ``ue8m0`` scale byte (a power of two, value ``2 ** (e - 127)``) per
+block of 32 consecutive elements.  The scale of a block is the smallest power of two that brings the
+block's largest magnitude to at most 448, the largest e4m3 value, so quantisation never saturates.
+
+``allreduce_mxfp8`` / ``reducescatter_mxfp8`` sum such tensors over the ranks with fp32 accumulation and a
+single requantisation (kernel: ``csrc/kernels/mxfp8.cu``).  The torch functions here are the oracle for the
+kernel and a convenience for callers.  fp8 reductions are on the reference's roadmap only (README.md:58-60).
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence, Tuple, Union
+
+import torch
+
+from .. import _native as N
+
+BLOCK = 32
+TensorOrList = Union[torch.Tensor, Sequence[torch.Tensor]]
+
+
+def scale_for_amax(amax: torch.Tensor) -> torch.Tensor:
+    """ue8m0 byte of the smallest power of two ``s`` with ``amax / s <= 448`` (fp32 in, uint8 out)."""
+    m, e = torch.frexp(amax.float())            # amax = m * 2**e, m in [0.5, 1)
+    s = e - 9 + (m * 2 > 1.75).to(e.dtype) + 127
+    s = torch.where(amax > 0, s, torch.full_like(s, 127 - 8))
+    return s.clamp(1, 254).to(torch.uint8)
+
+
+def scale_to_float(scale: torch.Tensor) -> torch.Tensor:
+    return torch.pow(2.0, scale.float() - 127.0)
+
+
+def quantize_mxfp8(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """fp32/bf16/fp16 tensor (numel a multiple of 32) -> (payload uint8 [numel], scales uint8 [numel / 32])."""
+    flat = x.detach().float().reshape(-1, BLOCK)
+    scale = scale_for_amax(flat.abs().amax(dim=1))
+    q = (flat / scale_to_float(scale)[:, None]).to(torch.float8_e4m3fn)
+    return q.view(torch.uint8).reshape(-1), scale
+
+
+def dequantize_mxfp8(data: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    return (data.view(torch.float8_e4m3fn).float().reshape(-1, BLOCK) * scale_to_float(scale)[:, None]).reshape(-1)
+
+
+def _lists(comm, t):
+    ts = [t] if isinstance(t, torch.Tensor) else list(t)
+    if len(ts) != comm.nlocal:
+        raise ValueError(f"expected {comm.nlocal} tensors")
+    return ts
+
+
+def _off(comm, ts, what):
+    offs = [comm.symm_offset(t, lr) for lr, t in enumerate(ts)]
+    if offs[0] is None or any(o != offs[0] for o in offs):
+        raise ValueError(f"{what} must come from the symmetric heap (same offset on every rank)")
+    return offs[0]
+
+
+def allreduce_mxfp8(comm, data: TensorOrList, scale: TensorOrList, out_data: Optional[TensorOrList] = None,
+                    out_scale: Optional[TensorOrList] = None, nctas: int = 64) -> None:
+    """Sum the MXFP8 tensors of all ranks; the result (requantised once) replaces ``data`` / ``scale`` on every
+    rank, or goes to ``out_data`` / ``out_scale``.  All tensors must be symmetric uint8 tensors."""
+    d, s = _lists(comm, data), _lists(comm, scale)
+    od = _lists(comm, out_data) if out_data is not None else d
+    os_ = _lists(comm, out_scale) if out_scale is not None else s
+    n_el = d[0].numel()
+    if s[0].numel() * BLOCK != n_el:
+        raise ValueError("one scale byte per 32 payload bytes")
+    rc = comm.lib.mt_mxfp8_reduce(comm._handle, comm._stream(), 0, _off(comm, d, "data"), _off(comm, s, "scale"),
+                                  _off(comm, od, "out_data"), _off(comm, os_, "out_scale"), None, None, n_el, nctas)
+    if rc < 0:
+        raise RuntimeError(f"mt_mxfp8_reduce: {N.last_error()}")
+
+
+def reducescatter_mxfp8(comm, data: TensorOrList, scale: TensorOrList, out_data: TensorOrList, out_scale: TensorOrList,
+                        nctas: int = 64) -> None:
+    """Shard ``rank`` (a contiguous 1/world of the blocks) of the sum lands in the local ``out_data`` / ``out_scale``."""
+    d, s = _lists(comm, data), _lists(comm, scale)
+    od, os_ = _lists(comm, out_data), _lists(comm, out_scale)
+    n_el = d[0].numel()
+    rc = comm.lib.mt_mxfp8_reduce(comm._handle, comm._stream(), 1, _off(comm, d, "data"), _off(comm, s, "scale"), 0, 0,
+                                  N.ptr_array([t.data_ptr() for t in od]), N.ptr_array([t.data_ptr() for t in os_]),
+                                  n_el, nctas)
+    if rc < 0:
+        raise RuntimeError(f"mt_mxfp8_reduce: {N.last_error()}")

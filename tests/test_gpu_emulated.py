@@ -292,3 +292,38 @@ def test_bounded_wait_reports_instead_of_hanging():
     x = torch.ones(8, device="cuda")
     assert float((x + 1).sum()) == 16.0  # the CUDA context still works
     w.close()
+
+
+@pytest.mark.parametrize("n", [2, 4, 8])
+def test_mxfp8_block_scaled_reductions(n):
+    """Block-scaled fp8 sum: fp32 accumulation over all ranks, one requantisation."""
+    from mintccl_b200.ops import mxfp8 as mx
+    w = world(n)
+    numel = 32 * n * 50 + 32 * n * 3
+    xs = [t * (10.0 ** (r % 3 - 1)) for r, t in enumerate(rand(n, numel, torch.float32, seed0=77))]
+    q = [mx.quantize_mxfp8(x) for x in xs]
+    # the torch quantiser round-trips within fp8 precision
+    torch.testing.assert_close(mx.dequantize_mxfp8(*q[0]), xs[0], rtol=0.07, atol=1e-3)
+    data, scale = w.symm_empty(numel, torch.uint8), w.symm_empty(numel // 32, torch.uint8)
+    od, os_ = w.symm_empty(numel, torch.uint8), w.symm_empty(numel // 32, torch.uint8)
+    for r in range(n):
+        data[r].copy_(q[r][0])
+        scale[r].copy_(q[r][1])
+    ref = sum(mx.dequantize_mxfp8(*q[r]) for r in range(n))          # fp32 sum of the dequantised inputs
+    ref_q = mx.dequantize_mxfp8(*mx.quantize_mxfp8(ref))               # ... quantised once
+    mx.allreduce_mxfp8(w, data, scale, od, os_)
+    w.check()
+    for r in range(n):
+        got = mx.dequantize_mxfp8(od[r], os_[r])
+        torch.testing.assert_close(got, ref_q, rtol=0.07, atol=2e-3)
+        assert torch.equal(od[r], od[0]) and torch.equal(os_[r], os_[0])
+        assert torch.equal(os_[r], mx.quantize_mxfp8(ref)[1])         # identical block scales
+    sd = [torch.empty(numel // n, device="cuda", dtype=torch.uint8) for _ in range(n)]
+    ss = [torch.empty(numel // n // 32, device="cuda", dtype=torch.uint8) for _ in range(n)]
+    mx.reducescatter_mxfp8(w, data, scale, sd, ss)
+    w.check()
+    per = numel // n
+    for r in range(n):
+        torch.testing.assert_close(mx.dequantize_mxfp8(sd[r], ss[r]), ref_q[r * per:(r + 1) * per], rtol=0.07, atol=2e-3)
+    for t in (data, scale, od, os_):
+        w.symm_free(t)
