@@ -42,6 +42,9 @@ def main() -> None:
     ap.add_argument("--algos", default="auto", help="comma list for mintccl: auto,ring,direct,nvls,ll,oneshot")
     ap.add_argument("--iters", type=int, default=0, help="0 = by size")
     ap.add_argument("--ctas", default="", help="comma list of CTA / channel counts to try for mintccl (default: automatic)")
+    ap.add_argument("--sync", action="store_true",
+                    help="follow every call with an 8-byte all-reduce of this library (a cross-rank fence), so that "
+                         "pipelined algorithms cannot overlap consecutive calls; the fence's own time is subtracted")
     ap.add_argument("--out", default="")
     a = ap.parse_args()
 
@@ -103,6 +106,12 @@ def main() -> None:
         k = max(1, nbytes // esz)
         return [(sym_in[j * ne: j * ne + k], sym_out[j * ne: j * ne + k]) for j in range(cnt)]
 
+    fence_in = comm.symm_empty(4, torch.float16)
+    fence_in.fill_(1.0)
+    fence_out = torch.empty(4, device="cuda", dtype=torch.float16)
+    fence = (lambda: comm.allreduce(fence_in, out=fence_out, algo="ll")) if (a.sync and n > 1) else None
+    fence_ms = timed(fence, 200) if fence else 0.0
+
     for coll in a.collectives.split(","):
         for size in sizes:
             numel = max(1, size // esz)
@@ -148,7 +157,13 @@ def main() -> None:
                             elif coll == "alltoall":
                                 dist.all_to_all_single(o, i)
                     try:
-                        ms = timed(call, iters)
+                        if fence:
+                            def call_f(call=call):
+                                call()
+                                fence()
+                            ms = max(timed(call_f, iters) - fence_ms, 1e-4)
+                        else:
+                            ms = timed(call, iters)
                         if impl == "mintccl":
                             comm.check()
                     except (ValueError, RuntimeError) as e:
@@ -158,7 +173,7 @@ def main() -> None:
                     bus = busbw_factor(coll, n) * nbytes / (ms * 1e-3) / 1e9
                     row = {"collective": coll, "bytes": nbytes, "impl": impl, "algo": algo, "ctas": ctas, "us": round(ms * 1e3, 2),
                            "algbw_GBps": round(nbytes / (ms * 1e-3) / 1e9, 3), "busbw_GBps": round(bus, 3), "n": n,
-                           "dtype": a.dtype}
+                           "dtype": a.dtype, "sync": bool(fence)}
                     results.append(row)
                     if rank == 0:
                         print(json.dumps(row), flush=True)

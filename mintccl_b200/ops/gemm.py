@@ -84,7 +84,7 @@ class AllGatherGemm(_Fused):
         comm.control.barrier()
 
     @staticmethod
-    def pick_ncomm(tiles: int, sms: int = 148, lo: int = 16, hi: int = 40) -> int:
+    def pick_ncomm(tiles: int, sms: int = 148, lo: int = 16, hi: int = 24) -> int:
         """Comm CTAs for a problem of ``tiles`` output tiles: the GEMM takes ceil(tiles / (sms - ncomm)) waves,
         so take the most comm CTAs (faster transfer) that do not add a wave over the fewest allowed."""
         waves = lambda nc: -(-tiles // (sms - nc))  # noqa: E731

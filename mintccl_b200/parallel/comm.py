@@ -602,11 +602,11 @@ class Communicator:
         algo = self._algo(algo)
         off = self._symm_off_all(ts)
         if algo == "auto":
-            ring_wide = (self.cfg.num_blocks or self.cfg.max_channels) >= 48
-            if self.world_size >= 4 and nbytes >= (32 << 20) and ring_wide:
-                algo = "ring"     # 48+ channels of the pipelined Simple chain fill the links (measured
-                                  # 631 GB/s at 1 GiB on 4 GPUs against 528 for the multicast variant)
-            elif off is not None and self._want_nvls(nbytes, ts):
+            # A wide pipelined ring (algo="ring", 48+ channels) moves more bytes per second when broadcasts
+            # follow each other back to back (631 against 528 GB/s at 1 GiB on 4 GPUs), but a single broadcast
+            # then pays the fill time of the chain before the last rank has its data.  The multicast variant
+            # finishes on every rank at the same time, so it is the default.
+            if off is not None and self._want_nvls(nbytes, ts):
                 algo = "nvls"
             elif off is not None and self.world_size == 2 and nbytes > (64 << 10):
                 algo = "direct"   # two ranks: the root pushes once, nothing to pipeline
