@@ -110,6 +110,7 @@ def lib():
     sig("mt_ll_capacity", u64, vp)
     sig("mt_p2p", i32, vp, vp, i32, i32, vp, vp, u64, i32, i32)
     sig("mt_gemm", i32, vp, vp, vp, vp, i32, i32, i32, i32, i32)
+    sig("mt_gemm_mxfp8", i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32)
     sig("mt_ag_gemm", i32, vp, vp, pp, pp, pp, u64, u64, u64, i32, i32, i32, i32, i32, i32, i32, u64, i32)
     sig("mt_gemm_rs", i32, vp, vp, pp, pp, pp, u64, u64, u64, i32, i32, i32, i32, i32)
     sig("mt_mxfp8_reduce", i32, vp, vp, i32, u64, u64, u64, u64, pp, pp, u64, i32)

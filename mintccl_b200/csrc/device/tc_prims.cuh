@@ -111,5 +111,41 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+// ---- block-scaled fp8 (MXFP8: e4m3 operands, one ue8m0 scale per 32 elements along K) ------------------
+// D[tmem] (+)= (A * SFA)[smem] * (B * SFB)[smem]^T.  Scale factors sit in TMEM: for operand row r (an output
+// row for A, an output column for B) and K block k (of 32 elements) the scale byte is at lane r % 32,
+// column base + r / 32, byte k % 4; the instruction descriptor names the byte (a_sf_id / b_sf_id).
+__device__ __forceinline__ void umma_mxfp8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                           uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+      : "memory");
+}
+// e4m3 x e4m3 -> fp32, ue8m0 scales, both operands K-major; sf ids select the scale byte of this K block.
+__host__ __device__ constexpr uint32_t make_idesc_mxfp8(int m, int n, uint32_t a_sf_id, uint32_t b_sf_id) {
+  return (b_sf_id << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(n >> 3) << 17) | (1u << 23) | ((uint32_t)(m >> 4) << 24) |
+         (a_sf_id << 29);
+}
+// Shared-memory descriptor of one scale-factor atom: 512 contiguous bytes = 32 rows of 16 bytes, no swizzle
+// (8-row groups 128 bytes apart).  Byte (r % 32) * 16 + (r / 32) * 4 + k holds the scale of row r, K block k.
+__device__ __forceinline__ uint64_t make_smem_desc_sf(const void* smem_atom) {
+  const uint64_t addr = (uint64_t)(smem_u32(smem_atom) >> 4) & 0x3fffull;
+  return addr | (0ull << 16) | (8ull << 32) | (1ull << 46);
+}
+// Copy one atom from shared memory into 4 TMEM columns, replicated to the four 32-lane quarters.
+__device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint64_t smem_desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
+}
+// 1-D bulk copy global -> shared, completion counted on an mbarrier (sizes and addresses multiples of 16).
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
 }  // namespace tc
 }  // namespace mt

@@ -20,15 +20,16 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 // [rows, K] bf16 row-major, tiles of box_rows x 64 elements, 128-byte swizzle.
-int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K, uint32_t box_rows) {
+int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K, uint32_t box_rows, bool fp8 = false) {
   static EncodeTiledFn enc = (EncodeTiledFn)mthost::driver_entry("cuTensorMapEncodeTiled");
   if (!enc) return fail("cuTensorMapEncodeTiled not available");
-  if (((uintptr_t)base & 15) || (K * 2) % 16) return fail("GEMM operands must be 16-byte aligned with K a multiple of 8");
+  const uint64_t esz = fp8 ? 1 : 2;
+  if (((uintptr_t)base & 15) || (K * esz) % 16) return fail("GEMM operands must be 16-byte aligned with rows a multiple of 16 bytes");
   cuuint64_t dims[2] = {K, rows};
-  cuuint64_t strides[1] = {K * 2};
-  cuuint32_t box[2] = {(cuuint32_t)kBK, box_rows};
+  cuuint64_t strides[1] = {K * esz};
+  cuuint32_t box[2] = {(cuuint32_t)(fp8 ? 128 : kBK), box_rows};  // 128 bytes per row either way
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)base, dims, strides, box, estr,
+  CUresult r = enc(map, fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)base, dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled failed: CUresult " + std::to_string((int)r));
@@ -82,6 +83,40 @@ int mt_gemm(void* stream, const void* A, const void* B, void* C, int M, int N, i
   if (grid > tiles) grid = tiles;
   cudaError_t e = mt::launch_gemm_tc(mt::MODE_PLAIN, maps, a, grid, 1, (cudaStream_t)stream);
   if (e != cudaSuccess) return fail(std::string("gemm launch: ") + cudaGetErrorString(e));
+  return 0;
+}
+
+// C[M, ldc] (bf16) = (A * SFA)[M, K] * (B * SFB)[N, K]^T for MXFP8 operands: e4m3 payload, ue8m0 scales per 32
+// elements along K.  The scales are given in the tiled layout the tensor core reads: [rows / 128][K / 128][512]
+// with byte (r % 32) * 16 + ((r % 128) / 32) * 4 + (k / 32) % 4 for row r and element k
+// (mintccl_b200.ops.mxfp8.tile_scales builds it).  K must be a multiple of 128.
+int mt_gemm_mxfp8(void* stream, const void* A, const void* sfa, const void* B, const void* sfb, void* C, int M, int N,
+                  int K, int ldc, int nctas) {
+  if (check_shape(M, N, K, 1) || K % 128) return fail("MXFP8 GEMM: M multiple of 128, N of 256, K of 128");
+  if (ldc < N || ldc % 8 || ((uintptr_t)C & 15)) return fail("C must be 16-byte aligned with ldc >= N, ldc % 8 == 0");
+  if (((uintptr_t)sfa | (uintptr_t)sfb) & 15) return fail("scale tensors must be 16-byte aligned");
+  int dev = 0;
+  cudaGetDevice(&dev);
+  mt::GemmMaps maps;
+  memset(&maps, 0, sizeof(maps));
+  if (make_map(&maps.a[0], A, M, K, kBM, true) || make_map(&maps.b[0], B, N, K, kBN, true)) return -1;
+  maps.a2[0] = maps.a[0];
+  mt::GemmArgs a;
+  memset(&a, 0, sizeof(a));
+  a.c[0] = C;
+  a.sfa[0] = sfa;
+  a.sfb[0] = sfb;
+  a.M = M;
+  a.N = N;
+  a.K = K;
+  a.ldc = ldc;
+  a.nranks = 1;
+  a.timeout_ns = 4000000000ull;
+  const int tiles = (M / kBM) * (N / kBN);
+  int grid = nctas > 0 ? nctas : sm_count(dev);
+  if (grid > tiles) grid = tiles;
+  cudaError_t e = mt::launch_gemm_tc(mt::MODE_PLAIN, maps, a, grid, 1, (cudaStream_t)stream, true);
+  if (e != cudaSuccess) return fail(std::string("mxfp8 gemm launch: ") + cudaGetErrorString(e));
   return 0;
 }
 

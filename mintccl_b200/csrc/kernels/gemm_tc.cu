@@ -39,7 +39,8 @@ constexpr uint32_t A_TILE_BYTES = BM * BK * 2, B_TILE_BYTES = BN * BK * 2;
 constexpr uint32_t STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
 constexpr int EPI_PITCH = 144;                      // bytes per staged row: 64 bf16 + 16 bytes of padding
 constexpr uint32_t EPI_BYTES = 4 * 32 * EPI_PITCH;  // 4 epilogue warps x 32 rows
-constexpr uint32_t SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + 256;
+constexpr uint32_t SF_STAGE_BYTES = 1536;  // MXFP8: one 512-byte scale atom for A, two for B, per stage
+constexpr uint32_t SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + 256 + STAGES * SF_STAGE_BYTES;
 constexpr uint32_t TMEM_COLS = 512;
 
 // comm CTAs: ring of COMM_SLOTS pieces in shared memory, loads run COMM_LAG pieces ahead of stores
@@ -213,7 +214,7 @@ __device__ void rs_reduce_loop(const GemmArgs& a, int lr) {
   }
 }
 
-template <int MODE>
+template <int MODE, bool FP8>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_constant__ GemmMaps maps, GemmArgs a) {
   extern __shared__ uint8_t smem_raw[];
   const int lr = blockIdx.y;
@@ -223,6 +224,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_c
   uint8_t* sB = smem + STAGES * A_TILE_BYTES;
   uint8_t* sEpi = smem + STAGES * STAGE_BYTES;
   SharedCtl* ctl = (SharedCtl*)(sEpi + EPI_BYTES);
+  uint8_t* sSF = sEpi + EPI_BYTES + 256;            // MXFP8 scale atoms, SF_STAGE_BYTES per stage
+  constexpr int BKE = FP8 ? 128 : 64;                // K elements per stage (128 bytes per row either way)
+  constexpr uint32_t ACC = FP8 ? 1 : 2;              // accumulator buffers (MXFP8 needs TMEM columns for scales)
   const int ncomm = MODE == MODE_PLAIN ? 0 : a.ncomm;  // AG: data movers, RS: dedicated reducers
   const int ngemm = gridDim.x - ncomm;
   const uint64_t timeout_ns = a.timeout_ns;
@@ -402,7 +406,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_c
   volatile int* abort_flag = &ctl->abort;
 
   const int total_tiles = (a.M / BM) * (a.N / BN);
-  const int kblocks = a.K / BK;
+  const int kblocks = a.K / BKE;
   const int first = blockIdx.x;
 
   if (warp == 0) {
@@ -442,9 +446,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_c
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
           if (!mbar_wait(&ctl->empty[s], ph ^ 1, abort_flag, timeout_ns)) break;
-          mbar_expect_tx(&ctl->full[s], STAGE_BYTES);
-          tma_load_2d(sA + s * A_TILE_BYTES, amap, kb * BK, arow, &ctl->full[s]);
-          tma_load_2d(sB + s * B_TILE_BYTES, &maps.b[lr], kb * BK, tc_.nb * BN, &ctl->full[s]);
+          mbar_expect_tx(&ctl->full[s], STAGE_BYTES + (FP8 ? SF_STAGE_BYTES : 0));
+          tma_load_2d(sA + s * A_TILE_BYTES, amap, kb * BKE, arow, &ctl->full[s]);
+          tma_load_2d(sB + s * B_TILE_BYTES, &maps.b[lr], kb * BKE, tc_.nb * BN, &ctl->full[s]);
+          if (FP8) {
+            const uint8_t* fa = (const uint8_t*)a.sfa[lr] + ((uint64_t)tc_.mb * kblocks + kb) * 512;
+            const uint8_t* fb = (const uint8_t*)a.sfb[lr] + ((uint64_t)(tc_.nb * 2) * kblocks + kb) * 512;
+            uint8_t* sf = sSF + s * SF_STAGE_BYTES;
+            bulk_load_1d(sf, fa, 512, &ctl->full[s]);
+            bulk_load_1d(sf + 512, fb, 512, &ctl->full[s]);
+            bulk_load_1d(sf + 1024, fb + (uint64_t)kblocks * 512, 512, &ctl->full[s]);
+          }
         }
       }
       if (*abort_flag) {
@@ -459,7 +471,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_c
       constexpr uint32_t idesc = make_idesc_bf16(BM, BN);
       uint32_t it = 0, tile_i = 0;
       for (int t = first; t < total_tiles && !*abort_flag; t += ngemm, ++tile_i) {
-        const uint32_t as = tile_i & 1, aph = (tile_i >> 1) & 1;
+        const uint32_t as = tile_i % ACC, aph = (tile_i / ACC) & 1;
         if (!mbar_wait(&ctl->acc_empty[as], aph ^ 1, abort_flag, timeout_ns)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + as * BN;
@@ -473,9 +485,23 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_c
           tc_fence_after();
           const uint64_t da = make_smem_desc_sw128(sA + s * A_TILE_BYTES);
           const uint64_t db = make_smem_desc_sw128(sB + s * B_TILE_BYTES);
+          if (FP8) {
+            // scales of this stage -> TMEM (the tensor pipe runs copies and MMAs in issue order, so the
+            // same columns serve every stage), then one MMA per 32-element K block with its scale byte
+            const uint32_t tsfa = tmem_base + 256, tsfb = tmem_base + 260;
+            const uint8_t* sf = sSF + s * SF_STAGE_BYTES;
+            tmem_cp_sf(tsfa, make_smem_desc_sf(sf));
+            tmem_cp_sf(tsfb, make_smem_desc_sf(sf + 512));
+            tmem_cp_sf(tsfb + 4, make_smem_desc_sf(sf + 1024));
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k)
-            umma_bf16(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < 4; ++k)
+              umma_mxfp8(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), make_idesc_mxfp8(BM, BN, k, k), tsfa, tsfb,
+                         (kb > 0 || k > 0) ? 1u : 0u);
+          } else {
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k)
+              umma_bf16(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
           umma_commit(&ctl->empty[s]);  // the stage is free once these MMAs have read it
         }
         if (!ok) break;
@@ -491,7 +517,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_c
     uint8_t* stg = sEpi + (warp - 2) * 32 * EPI_PITCH;
     uint32_t tile_i = 0;
     for (int t = first; t < total_tiles; t += ngemm, ++tile_i) {
-      const uint32_t as = tile_i & 1, aph = (tile_i >> 1) & 1;
+      const uint32_t as = tile_i % ACC, aph = (tile_i / ACC) & 1;
       if (!mbar_wait(&ctl->acc_full[as], aph, abort_flag, timeout_ns)) break;
       tc_fence_after();
       const TileCoord tc_ = tile_coord<MODE>(a, lr, t);
@@ -595,10 +621,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_c
   }
 }
 
-template <int MODE>
+template <int MODE, bool FP8>
 static cudaError_t launch_mode(const GemmMaps& maps, const GemmArgs& a, int nctas, int nlocal, cudaStream_t s) {
   static bool attr_set = false;
-  const void* fn = (const void*)gemm_tc_kernel<MODE>;
+  const void* fn = (const void*)gemm_tc_kernel<MODE, FP8>;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return e;
@@ -612,11 +638,19 @@ static cudaError_t launch_mode(const GemmMaps& maps, const GemmArgs& a, int ncta
   return cudaLaunchKernel(fn, dim3(nctas, nlocal), dim3(kGemmThreads), p, SMEM_BYTES, s);
 }
 
-cudaError_t launch_gemm_tc(int mode, const GemmMaps& maps, const GemmArgs& a, int nctas, int nlocal, cudaStream_t s) {
+cudaError_t launch_gemm_tc(int mode, const GemmMaps& maps, const GemmArgs& a, int nctas, int nlocal, cudaStream_t s,
+                           bool fp8) {
+  if (fp8) {
+    switch (mode) {
+      case MODE_PLAIN: return launch_mode<MODE_PLAIN, true>(maps, a, nctas, nlocal, s);
+      case MODE_GEMM_RS: return launch_mode<MODE_GEMM_RS, true>(maps, a, nctas, nlocal, s);
+      default: return cudaErrorInvalidValue;  // the all-gather fusion would also have to gather the scales
+    }
+  }
   switch (mode) {
-    case MODE_PLAIN: return launch_mode<MODE_PLAIN>(maps, a, nctas, nlocal, s);
-    case MODE_AG_GEMM: return launch_mode<MODE_AG_GEMM>(maps, a, nctas, nlocal, s);
-    case MODE_GEMM_RS: return launch_mode<MODE_GEMM_RS>(maps, a, nctas, nlocal, s);
+    case MODE_PLAIN: return launch_mode<MODE_PLAIN, false>(maps, a, nctas, nlocal, s);
+    case MODE_AG_GEMM: return launch_mode<MODE_AG_GEMM, false>(maps, a, nctas, nlocal, s);
+    case MODE_GEMM_RS: return launch_mode<MODE_GEMM_RS, false>(maps, a, nctas, nlocal, s);
     default: return cudaErrorInvalidValue;
   }
 }

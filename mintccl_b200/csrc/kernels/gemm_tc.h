@@ -21,6 +21,8 @@ struct GemmArgs {
   const void* a_local[MT_MAX_RANKS];   // AG_GEMM: own rows, pushed to the peers by the comm CTAs
   const void* flags_local[MT_MAX_RANKS];  // AG_GEMM: this rank's arrival counters (local view)
   void* status[MT_MAX_RANKS];          // MtStatus of the rank (or null)
+  const void* sfa[MT_MAX_RANKS];       // MXFP8: scales of A, tiled [M / 128][K / 128][512 bytes]
+  const void* sfb[MT_MAX_RANKS];       // MXFP8: scales of B, tiled [N / 128][K / 128][512 bytes]
   const MtDevComm* comms;              // device descriptors (fused modes)
   int32_t rank[MT_MAX_RANKS];
   int32_t M, N, K, ldc;
@@ -36,6 +38,7 @@ struct GemmArgs {
   uint64_t timeout_ns;
 };
 
-cudaError_t launch_gemm_tc(int mode, const GemmMaps& maps, const GemmArgs& a, int nctas, int nlocal, cudaStream_t s);
+cudaError_t launch_gemm_tc(int mode, const GemmMaps& maps, const GemmArgs& a, int nctas, int nlocal, cudaStream_t s,
+                           bool fp8 = false);
 
 }  // namespace mt

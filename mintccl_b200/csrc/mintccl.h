@@ -90,6 +90,8 @@ int mt_p2p(MtComm* c, void* stream, int src_rank, int dst_rank, const void* src_
 
 // ---- tcgen05 GEMM and its fusions with collectives (bf16, fp32 accumulate; B is [N, K] like nn.Linear) ----
 int mt_gemm(void* stream, const void* A, const void* B, void* C, int M, int N, int K, int ldc, int nctas);
+int mt_gemm_mxfp8(void* stream, const void* A, const void* sfa, const void* B, const void* sfb, void* C, int M, int N,
+                  int K, int ldc, int nctas);
 int mt_ag_gemm(MtComm* c, void* stream, const void* const* a_shard, const void* const* B, void* const* C,
                uint64_t gather_off, uint64_t flags_off, uint64_t epoch, int M, int N, int K, int ldc, int ncomm,
                int nctas, int comm_mode, uint64_t shard_off, int comm_split);

@@ -85,3 +85,38 @@ def reducescatter_mxfp8(comm, data: TensorOrList, scale: TensorOrList, out_data:
                                   n_el, nctas)
     if rc < 0:
         raise RuntimeError(f"mt_mxfp8_reduce: {N.last_error()}")
+
+
+# ---- MXFP8 GEMM operands -------------------------------------------------------------------------------------
+def quantize_rows_mxfp8(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``[rows, K]`` -> (payload uint8 ``[rows, K]``, scales uint8 ``[rows, K / 32]``): blocks of 32 along K."""
+    rows, K = x.shape
+    data, scale = quantize_mxfp8(x.contiguous())
+    return data.view(rows, K), scale.view(rows, K // BLOCK)
+
+
+def tile_scales(scale: torch.Tensor) -> torch.Tensor:
+    """Row-major scales ``[rows, K / 32]`` -> the layout the tensor core reads: ``[rows / 128][K / 128][512]`` bytes
+    with byte ``(r % 32) * 16 + ((r % 128) / 32) * 4 + kb % 4`` for row ``r`` and 32-element block ``kb``."""
+    rows, kb = scale.shape
+    if rows % 128 or kb % 4:
+        raise ValueError("rows must be a multiple of 128 and K of 128")
+    t = scale.view(rows // 128, 4, 32, kb // 4, 4)       # [R, r/32, r%32, KB, kb%4]
+    return t.permute(0, 3, 2, 1, 4).contiguous().view(-1)  # [R, KB, r%32, r/32, kb%4]
+
+
+def gemm_mxfp8(a_data: torch.Tensor, a_scale: torch.Tensor, w_data: torch.Tensor, w_scale: torch.Tensor,
+               out: Optional[torch.Tensor] = None, nctas: int = 0) -> torch.Tensor:
+    """``dequant(a) [M, K] @ dequant(w)[N, K].T -> bf16 [M, N]`` on the block-scaled tensor cores
+    (``tcgen05.mma.kind::mxf8f6f4.block_scale``).  ``a_scale`` / ``w_scale`` are row-major ``[rows, K / 32]``."""
+    M, K = a_data.shape
+    Nn = w_data.shape[0]
+    if out is None:
+        out = torch.empty(M, Nn, device=a_data.device, dtype=torch.bfloat16)
+    sfa, sfb = tile_scales(a_scale), tile_scales(w_scale)
+    stream = torch.cuda.current_stream(a_data.device).cuda_stream
+    rc = N.lib().mt_gemm_mxfp8(stream, a_data.data_ptr(), sfa.data_ptr(), w_data.data_ptr(), sfb.data_ptr(),
+                               out.data_ptr(), M, Nn, K, out.stride(0), nctas)
+    if rc < 0:
+        raise RuntimeError(f"mt_gemm_mxfp8: {N.last_error()}")
+    return out

@@ -81,3 +81,24 @@ def test_gemm_rs_emulated(n):
 def test_tp_mlp_forward_backward_single_rank():
     from mintccl_b200.models.tp_mlp import smoke_mlp
     smoke_mlp()
+
+
+@pytest.mark.parametrize("shape", [(128, 256, 128), (256, 512, 512), (1024, 1792, 4096)])
+def test_mxfp8_gemm_matches_dequantised_reference(shape):
+    """Block-scaled fp8 GEMM against the fp32 product of the dequantised operands (the quantisation error is in
+    both; what is compared is the tensor-core arithmetic and the scale plumbing)."""
+    from mintccl_b200.ops import mxfp8 as mx
+    M, N, K = shape
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    a = torch.randn(M, K, generator=g, device="cuda") * torch.logspace(-2, 2, M, device="cuda")[:, None]
+    w = torch.randn(N, K, generator=g, device="cuda") * 0.02
+    ad, asc = mx.quantize_rows_mxfp8(a)
+    wd, wsc = mx.quantize_rows_mxfp8(w)
+    out = mx.gemm_mxfp8(ad, asc, wd, wsc)
+    torch.cuda.synchronize()
+    a_dq = mx.dequantize_mxfp8(ad.reshape(-1), asc.reshape(-1)).view(M, K)
+    w_dq = mx.dequantize_mxfp8(wd.reshape(-1), wsc.reshape(-1)).view(N, K)
+    ref = a_dq @ w_dq.t()
+    err = (out.float() - ref).abs()
+    tol = 1.6e-2 * ref.abs() + 2e-3 * (a_dq.abs().amax(dim=1, keepdim=True) * (K ** 0.5) * 0.02)
+    assert bool((err <= tol).all()), f"max err {err.max().item()} worst ratio {(err / tol).max().item()}"
