@@ -113,6 +113,8 @@ def lib():
     sig("mt_gemm_mxfp8", i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32)
     sig("mt_ag_gemm", i32, vp, vp, pp, pp, pp, u64, u64, u64, i32, i32, i32, i32, i32, i32, i32, u64, i32)
     sig("mt_gemm_rs", i32, vp, vp, pp, pp, pp, u64, u64, u64, i32, i32, i32, i32, i32)
+    sig("mt_ag_gemm_mxfp8", i32, vp, vp, pp, pp, pp, pp, pp, u64, u64, u64, i32, i32, i32, i32, i32, i32)
+    sig("mt_gemm_rs_mxfp8", i32, vp, vp, pp, pp, pp, pp, pp, u64, u64, u64, i32, i32, i32, i32, i32)
     sig("mt_mxfp8_reduce", i32, vp, vp, i32, u64, u64, u64, u64, pp, pp, u64, i32)
     sig("mt_test_wait_timeout", i32, vp, vp)
     sig("mt_find_ring", i32, C.POINTER(C.c_double), i32, ip)

@@ -143,10 +143,12 @@ static int fused_common(MtComm* c, mt::GemmArgs& a, int M, int N, int K, uint64_
 // C[M, ldc] = allgather(a_shard)[M, K] * B[N, K]^T.  `gather_off`: symmetric buffer of M * K bf16;
 // `flags_off`: symmetric u64 counters [ranks][M / ranks / 128], zero before the first call; `epoch`: 1 on the
 // first call on these counters, then 2, 3, ...; `ncomm` must not change between calls on the same counters.
-int mt_ag_gemm(MtComm* c, void* stream, const void* const* a_shard, const void* const* B, void* const* C,
-               uint64_t gather_off, uint64_t flags_off, uint64_t epoch, int M, int N, int K, int ldc, int ncomm,
-               int nctas, int comm_mode, uint64_t shard_off, int comm_split) {
+static int ag_gemm_impl(MtComm* c, void* stream, const void* const* a_shard, const void* const* B, void* const* C,
+                        uint64_t gather_off, uint64_t flags_off, uint64_t epoch, int M, int N, int K, int ldc, int ncomm,
+                        int nctas, int comm_mode, uint64_t shard_off, int comm_split, bool fp8, const void* const* sfa,
+                        const void* const* sfb) {
   mt::GemmArgs a;
+  if (fp8 && K % 128) return fail("MXFP8: K must be a multiple of 128");
   if (fused_common(c, a, M, N, K, flags_off, epoch)) return -1;
   if (ldc < N || ldc % 8) return fail("ldc must be >= N and a multiple of 8");
   const int n = c->nranks;
@@ -171,23 +173,44 @@ int mt_ag_gemm(MtComm* c, void* stream, const void* const* a_shard, const void* 
     a.c[lr] = C[lr];
     a.a_local[lr] = a_shard[lr];
     a.flags_local[lr] = c->heap[lr][r] + flags_off;
-    if (make_map(&maps.a[lr], c->heap[lr][r] + gather_off, M, K, kBM) || make_map(&maps.b[lr], B[lr], N, K, kBN) ||
-        make_map(&maps.a2[lr], a_shard[lr], M / n, K, kBM))
+    if (make_map(&maps.a[lr], c->heap[lr][r] + gather_off, M, K, kBM, fp8) || make_map(&maps.b[lr], B[lr], N, K, kBN, fp8) ||
+        make_map(&maps.a2[lr], a_shard[lr], M / n, K, kBM, fp8))
       return -1;
     if ((uintptr_t)C[lr] & 15) return fail("C must be 16-byte aligned");
+    if (fp8) {
+      a.sfa[lr] = sfa[lr];
+      a.sfb[lr] = sfb[lr];
+    }
   }
-  cudaError_t e = mt::launch_gemm_tc(mt::MODE_AG_GEMM, maps, a, grid, c->nlocal, (cudaStream_t)stream);
+  cudaError_t e = mt::launch_gemm_tc(mt::MODE_AG_GEMM, maps, a, grid, c->nlocal, (cudaStream_t)stream, fp8);
   if (e != cudaSuccess) return fail(std::string("ag_gemm launch: ") + cudaGetErrorString(e));
   return 0;
+}
+
+int mt_ag_gemm(MtComm* c, void* stream, const void* const* a_shard, const void* const* B, void* const* C,
+               uint64_t gather_off, uint64_t flags_off, uint64_t epoch, int M, int N, int K, int ldc, int ncomm,
+               int nctas, int comm_mode, uint64_t shard_off, int comm_split) {
+  return ag_gemm_impl(c, stream, a_shard, B, C, gather_off, flags_off, epoch, M, N, K, ldc, ncomm, nctas, comm_mode,
+                      shard_off, comm_split, false, nullptr, nullptr);
+}
+// MXFP8 variant: payloads are e4m3 bytes; `sfa` is the tiled scale tensor of the GATHERED A (every rank must
+// hold all of it before the call, e.g. through an all-gather of the small scale tensors), `sfb` that of B.
+int mt_ag_gemm_mxfp8(MtComm* c, void* stream, const void* const* a_shard, const void* const* sfa, const void* const* B,
+                     const void* const* sfb, void* const* C, uint64_t gather_off, uint64_t flags_off, uint64_t epoch,
+                     int M, int N, int K, int ldc, int ncomm, int nctas) {
+  return ag_gemm_impl(c, stream, a_shard, B, C, gather_off, flags_off, epoch, M, N, K, ldc, ncomm, nctas, 0, 0, 1, true,
+                      sfa, sfb);
 }
 
 // out[M / ranks, N] = reduce_scatter over rows of (A[M, K] * B[N, K]^T), K being this rank's slice of the
 // contraction.  `stage_off`: symmetric buffer of ranks * (M / ranks) * N bf16 partial tiles;
 // `flags_off`: symmetric u64 counters [ranks][M / ranks / 128][N / 256] followed by two ticket words, all zero
 // before the first call.  `nred`: CTAs that only reduce (the others join them when their tiles are done).
-int mt_gemm_rs(MtComm* c, void* stream, const void* const* A, const void* const* B, void* const* out,
-               uint64_t stage_off, uint64_t flags_off, uint64_t epoch, int M, int N, int K, int nred, int nctas) {
+static int gemm_rs_impl(MtComm* c, void* stream, const void* const* A, const void* const* B, void* const* out,
+                        uint64_t stage_off, uint64_t flags_off, uint64_t epoch, int M, int N, int K, int nred, int nctas,
+                        bool fp8, const void* const* sfa, const void* const* sfb) {
   mt::GemmArgs a;
+  if (fp8 && K % 128) return fail("MXFP8: K must be a multiple of 128");
   if (fused_common(c, a, M, N, K, flags_off, epoch)) return -1;
   int grid = nctas > 0 ? nctas : sm_count(c->device);
   if (c->emulated && grid * c->nlocal > sm_count(c->device)) grid = sm_count(c->device) / c->nlocal;
@@ -199,13 +222,27 @@ int mt_gemm_rs(MtComm* c, void* stream, const void* const* A, const void* const*
   memset(&maps, 0, sizeof(maps));
   for (int lr = 0; lr < c->nlocal; ++lr) {
     a.c[lr] = out[lr];
-    if (make_map(&maps.a[lr], A[lr], M, K, kBM) || make_map(&maps.b[lr], B[lr], N, K, kBN)) return -1;
+    if (make_map(&maps.a[lr], A[lr], M, K, kBM, fp8) || make_map(&maps.b[lr], B[lr], N, K, kBN, fp8)) return -1;
     maps.a2[lr] = maps.a[lr];
     if ((uintptr_t)out[lr] & 15) return fail("out must be 16-byte aligned");
+    if (fp8) {
+      a.sfa[lr] = sfa[lr];
+      a.sfb[lr] = sfb[lr];
+    }
   }
-  cudaError_t e = mt::launch_gemm_tc(mt::MODE_GEMM_RS, maps, a, grid, c->nlocal, (cudaStream_t)stream);
+  cudaError_t e = mt::launch_gemm_tc(mt::MODE_GEMM_RS, maps, a, grid, c->nlocal, (cudaStream_t)stream, fp8);
   if (e != cudaSuccess) return fail(std::string("gemm_rs launch: ") + cudaGetErrorString(e));
   return 0;
+}
+
+int mt_gemm_rs(MtComm* c, void* stream, const void* const* A, const void* const* B, void* const* out,
+               uint64_t stage_off, uint64_t flags_off, uint64_t epoch, int M, int N, int K, int nred, int nctas) {
+  return gemm_rs_impl(c, stream, A, B, out, stage_off, flags_off, epoch, M, N, K, nred, nctas, false, nullptr, nullptr);
+}
+int mt_gemm_rs_mxfp8(MtComm* c, void* stream, const void* const* A, const void* const* sfa, const void* const* B,
+                     const void* const* sfb, void* const* out, uint64_t stage_off, uint64_t flags_off, uint64_t epoch,
+                     int M, int N, int K, int nred, int nctas) {
+  return gemm_rs_impl(c, stream, A, B, out, stage_off, flags_off, epoch, M, N, K, nred, nctas, true, sfa, sfb);
 }
 
 // Sum of MXFP8 tensors (e4m3 payload + ue8m0 scale per 32 elements) over all ranks.  op 0: all-reduce into

@@ -239,7 +239,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_c
     // every rank has entered this call, so nobody still reads last call's gathered rows
     if (!rank_barrier(c, cc, &s_fail)) return;
     const int n = c.nranks, me = c.rank;
-    const uint64_t row_bytes = (uint64_t)a.K * 2;
+    const uint64_t row_bytes = (uint64_t)a.K * (FP8 ? 1 : 2);
     const uint64_t shard_rows = a.M / n;
     const int chunks = (int)(shard_rows / BM);
     const uint8_t* src = (const uint8_t*)a.a_local[lr];
@@ -643,8 +643,9 @@ cudaError_t launch_gemm_tc(int mode, const GemmMaps& maps, const GemmArgs& a, in
   if (fp8) {
     switch (mode) {
       case MODE_PLAIN: return launch_mode<MODE_PLAIN, true>(maps, a, nctas, nlocal, s);
+      case MODE_AG_GEMM: return launch_mode<MODE_AG_GEMM, true>(maps, a, nctas, nlocal, s);
       case MODE_GEMM_RS: return launch_mode<MODE_GEMM_RS, true>(maps, a, nctas, nlocal, s);
-      default: return cudaErrorInvalidValue;  // the all-gather fusion would also have to gather the scales
+      default: return cudaErrorInvalidValue;
     }
   }
   switch (mode) {

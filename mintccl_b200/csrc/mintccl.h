@@ -98,6 +98,12 @@ int mt_ag_gemm(MtComm* c, void* stream, const void* const* a_shard, const void* 
 int mt_gemm_rs(MtComm* c, void* stream, const void* const* A, const void* const* B, void* const* out,
                uint64_t stage_off, uint64_t flags_off, uint64_t epoch, int M, int N, int K, int nred, int nctas);
 
+int mt_ag_gemm_mxfp8(MtComm* c, void* stream, const void* const* a_shard, const void* const* sfa, const void* const* B,
+                     const void* const* sfb, void* const* C, uint64_t gather_off, uint64_t flags_off, uint64_t epoch,
+                     int M, int N, int K, int ldc, int ncomm, int nctas);
+int mt_gemm_rs_mxfp8(MtComm* c, void* stream, const void* const* A, const void* const* sfa, const void* const* B,
+                     const void* const* sfb, void* const* out, uint64_t stage_off, uint64_t flags_off, uint64_t epoch,
+                     int M, int N, int K, int nred, int nctas);
 int mt_mxfp8_reduce(MtComm* c, void* stream, int op, uint64_t data_in_off, uint64_t scale_in_off,
                     uint64_t data_out_off, uint64_t scale_out_off, void* const* data_out, void* const* scale_out,
                     uint64_t nelems, int nctas);

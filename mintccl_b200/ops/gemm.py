@@ -68,9 +68,11 @@ class AllGatherGemm(_Fused):
 
     MODES = {"push": 0, "pull": 1, "push_st": 2}
 
-    def __init__(self, comm, M: int, N_: int, K: int, ncomm: Optional[int] = None, mode: str = "push", split: int = 1):
+    def __init__(self, comm, M: int, N_: int, K: int, ncomm: Optional[int] = None, mode: str = "push", split: int = 1,
+                 fp8: bool = False):
         super().__init__(comm)
         self.mode = self.MODES[mode]
+        self.fp8 = fp8
         if ncomm is None:
             ncomm = self.pick_ncomm((M // BM) * (N_ // BN))
         self.split = max(1, min(split, ncomm))
@@ -78,10 +80,43 @@ class AllGatherGemm(_Fused):
         if M % (BM * n) or N_ % BN or K % BK:
             raise ValueError("M must be a multiple of 128 x world, N of 256, K of 64")
         self.M, self.N, self.K, self.ncomm = M, N_, K, ncomm
-        self.gathered = comm.symm_empty((M, K), torch.bfloat16)
+        if fp8 and K % 128:
+            raise ValueError("MXFP8: K must be a multiple of 128")
+        self.gathered = comm.symm_empty((M, K), torch.uint8 if fp8 else torch.bfloat16)
+        # MXFP8: the tiled scales of all ranks' rows, gathered by a small all-gather before the fused kernel
+        self.sfa_all = comm.symm_empty((n, (M // n // 128) * (K // 128) * 512), torch.uint8) if fp8 else None
         self.flags = comm.symm_zeros((n * (M // n // BM),), torch.int64)
         torch.cuda.synchronize()
         comm.control.barrier()
+
+    def call_mxfp8(self, a_data: TensorOrList, a_scale: TensorOrList, w_data: TensorOrList, w_scale: TensorOrList,
+                   out: Optional[TensorOrList] = None, nctas: int = 0):
+        """MXFP8 operands: ``a_data`` uint8 ``[M / n, K]`` (e4m3) with row-major scales ``[M / n, K / 32]``, ``w_data``
+        ``[N, K]`` with scales ``[N, K / 32]``; bf16 result.  The payload rows are gathered inside the fused kernel,
+        the (32 x smaller) scales by an all-gather of this library just before it."""
+        from . import mxfp8 as mx
+        if not self.fp8:
+            raise ValueError("create the plan with fp8=True")
+        c = self.comm
+        a_s, ws = self._lists(a_data), self._lists(w_data)
+        a_sc, w_sc = self._lists(a_scale), self._lists(w_scale)
+        outs = self._lists(out) if out is not None else [torch.empty(self.M, self.N, device=a_s[0].device, dtype=torch.bfloat16) for _ in a_s]
+        ranks = range(c.world_size) if c.emulated else [c.rank]
+        sfa_all = self.sfa_all if c.emulated else [self.sfa_all]
+        for lr, r in enumerate(ranks):
+            sfa_all[lr][r].copy_(mx.tile_scales(a_sc[lr]))
+        c.allgather(self.sfa_all)
+        sfb = [mx.tile_scales(t) for t in w_sc]
+        self.epoch += 1
+        rc = c.lib.mt_ag_gemm_mxfp8(c._handle, c._stream(), N.ptr_array([t.data_ptr() for t in a_s]),
+                                    N.ptr_array([t.data_ptr() for t in sfa_all]), N.ptr_array([t.data_ptr() for t in ws]),
+                                    N.ptr_array([t.data_ptr() for t in sfb]), N.ptr_array([t.data_ptr() for t in outs]),
+                                    self._off(self.gathered), self._off(self.flags), self.epoch, self.M, self.N, self.K,
+                                    outs[0].stride(0), self.ncomm, nctas)
+        if rc < 0:
+            raise RuntimeError(f"mt_ag_gemm_mxfp8: {N.last_error()}")
+        self._keep = sfb  # the kernel reads them asynchronously
+        return outs if c.emulated else outs[0]
 
     @staticmethod
     def pick_ncomm(tiles: int, sms: int = 148, lo: int = 16, hi: int = 24) -> int:
@@ -153,4 +188,26 @@ class GemmReduceScatter(_Fused):
                               min(self.nred, 148 // c.nlocal - 1) if c.emulated else self.nred, nctas)
         if rc < 0:
             raise RuntimeError(f"mt_gemm_rs: {N.last_error()}")
+        return outs if c.emulated else outs[0]
+
+    def call_mxfp8(self, a_data: TensorOrList, a_scale: TensorOrList, w_data: TensorOrList, w_scale: TensorOrList,
+                   out: Optional[TensorOrList] = None, nctas: int = 0):
+        """MXFP8 operands (e4m3 payloads, row-major ue8m0 scales per 32 elements along K); bf16 partial tiles and
+        result, fp32 accumulation in the tensor core and in the cross-rank sum."""
+        from . import mxfp8 as mx
+        c = self.comm
+        a_s, ws = self._lists(a_data), self._lists(w_data)
+        rows = self.M // c.world_size
+        outs = self._lists(out) if out is not None else [torch.empty(rows, self.N, device=a_s[0].device, dtype=torch.bfloat16) for _ in a_s]
+        sfa = [mx.tile_scales(t) for t in self._lists(a_scale)]
+        sfb = [mx.tile_scales(t) for t in self._lists(w_scale)]
+        self.epoch += 1
+        rc = c.lib.mt_gemm_rs_mxfp8(c._handle, c._stream(), N.ptr_array([t.data_ptr() for t in a_s]),
+                                    N.ptr_array([t.data_ptr() for t in sfa]), N.ptr_array([t.data_ptr() for t in ws]),
+                                    N.ptr_array([t.data_ptr() for t in sfb]), N.ptr_array([t.data_ptr() for t in outs]),
+                                    self._off(self.stage), self._off(self.flags), self.epoch, self.M, self.N, self.K,
+                                    min(self.nred, 148 // c.nlocal - 1) if c.emulated else self.nred, nctas)
+        if rc < 0:
+            raise RuntimeError(f"mt_gemm_rs_mxfp8: {N.last_error()}")
+        self._keep = (sfa, sfb)
         return outs if c.emulated else outs[0]

@@ -102,3 +102,37 @@ def test_mxfp8_gemm_matches_dequantised_reference(shape):
     err = (out.float() - ref).abs()
     tol = 1.6e-2 * ref.abs() + 2e-3 * (a_dq.abs().amax(dim=1, keepdim=True) * (K ** 0.5) * 0.02)
     assert bool((err <= tol).all()), f"max err {err.max().item()} worst ratio {(err / tol).max().item()}"
+
+
+@pytest.mark.parametrize("n", [1, 2, 4])
+def test_fused_kernels_mxfp8_emulated(n):
+    from mintccl_b200.ops import mxfp8 as mx
+    from mintccl_b200.ops.gemm import AllGatherGemm, GemmReduceScatter
+    w_ = world(n)
+    M, N, K = 128 * n * 2, 512, 256
+    g = torch.Generator(device="cuda").manual_seed(5)
+    ag = AllGatherGemm(w_, M, N, K, ncomm=4, fp8=True)
+    rs = GemmReduceScatter(w_, M, N, K)
+    for it in range(2):
+        shards = [torch.randn(M // n, K, generator=g, device="cuda") * (r + 1) for r in range(n)]
+        ws = [torch.randn(N, K, generator=g, device="cuda") * 0.05 for _ in range(n)]
+        qa = [mx.quantize_rows_mxfp8(t) for t in shards]
+        qw = [mx.quantize_rows_mxfp8(t) for t in ws]
+        outs = ag.call_mxfp8([q[0] for q in qa], [q[1] for q in qa], [q[0] for q in qw], [q[1] for q in qw])
+        w_.check()
+        a_dq = torch.cat([mx.dequantize_mxfp8(d.reshape(-1), s.reshape(-1)).view(M // n, K) for d, s in qa], 0)
+        for r in range(n):
+            w_dq = mx.dequantize_mxfp8(qw[r][0].reshape(-1), qw[r][1].reshape(-1)).view(N, K)
+            torch.testing.assert_close(outs[r].float(), a_dq @ w_dq.t(), rtol=2e-2, atol=5e-2)
+        As = [torch.randn(M, K, generator=g, device="cuda") for _ in range(n)]
+        qA = [mx.quantize_rows_mxfp8(t) for t in As]
+        ys = rs.call_mxfp8([q[0] for q in qA], [q[1] for q in qA], [q[0] for q in qw], [q[1] for q in qw])
+        w_.check()
+        ref = 0
+        for r in range(n):
+            A_dq = mx.dequantize_mxfp8(qA[r][0].reshape(-1), qA[r][1].reshape(-1)).view(M, K)
+            w_dq = mx.dequantize_mxfp8(qw[r][0].reshape(-1), qw[r][1].reshape(-1)).view(N, K)
+            ref = ref + (A_dq @ w_dq.t()).to(torch.bfloat16).float()
+        rows = M // n
+        for r in range(n):
+            torch.testing.assert_close(ys[r].float(), ref[r * rows:(r + 1) * rows], rtol=2e-2, atol=6e-2)
