@@ -57,6 +57,15 @@ int make_bf16_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K,
 }
 }  // namespace mthost
 
+// Row blocks per group of the plain GEMM's tile order.  Row-major order streams the whole of B through the
+// L2 once per wave of CTAs; when B does not fit beside A's rows (large N x K) a grouped order keeps a wave's
+// operands resident.  MINTCCL_GEMM_RASTER overrides (for tuning).
+static int raster_for(int M, int N, int K, int elem_bytes) {
+  if (const char* e = getenv("MINTCCL_GEMM_RASTER")) return atoi(e);
+  const double b_bytes = (double)N * K * elem_bytes;
+  return b_bytes > 48e6 ? 16 : 1;
+}
+
 extern "C" {
 
 // C[M, ldc] = A[M, K] * B[N, K]^T in bf16 with fp32 accumulation, on the current device.
@@ -77,6 +86,7 @@ int mt_gemm(void* stream, const void* A, const void* B, void* C, int M, int N, i
   a.K = K;
   a.ldc = ldc;
   a.nranks = 1;
+  a.raster = raster_for(M, N, K, 2);
   a.timeout_ns = 4000000000ull;
   const int tiles = (M / kBM) * (N / kBN);
   int grid = nctas > 0 ? nctas : sm_count(dev);
@@ -111,6 +121,7 @@ int mt_gemm_mxfp8(void* stream, const void* A, const void* sfa, const void* B, c
   a.K = K;
   a.ldc = ldc;
   a.nranks = 1;
+  a.raster = raster_for(M, N, K, 1);
   a.timeout_ns = 4000000000ull;
   const int tiles = (M / kBM) * (N / kBN);
   int grid = nctas > 0 ? nctas : sm_count(dev);

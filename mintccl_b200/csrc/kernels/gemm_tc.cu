@@ -96,12 +96,24 @@ template <int MODE>
 __device__ __forceinline__ TileCoord tile_coord(const GemmArgs& a, int lr, int t) {
   const int nbs = a.N / BN;
   TileCoord c;
+  if (MODE == MODE_PLAIN) {
+    // Groups of a.raster row blocks, row block fastest inside a group: the tiles in flight at any time
+    // (one per CTA, consecutive t) then span about as many rows of A as of B, which keeps the operands of
+    // a wave, and of the next wave, inside the L2 for large problems.
+    const int mbs = a.M / BM;
+    const int G = a.raster > 1 ? a.raster : 1;
+    const int per_group = G * nbs;
+    const int g0 = (t / per_group) * G;
+    const int gsz = (mbs - g0) < G ? (mbs - g0) : G;
+    const int r = t % per_group;
+    c.mb = g0 + r % gsz;
+    c.nb = r / gsz;
+    c.owner = 0;
+    return c;
+  }
   c.nb = t % nbs;
   int mi = t / nbs;
-  if (MODE == MODE_PLAIN) {
-    c.mb = mi;
-    c.owner = 0;
-  } else {
+  {
     const int per = (a.M / a.nranks) / BM;  // row blocks per rank
     int d, j;
     if (MODE == MODE_AG_GEMM) {
@@ -540,36 +552,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_c
       }
       dst += (uint64_t)(q * 32) * ld_bytes;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + as * BN;
-#pragma unroll 1
-      for (int cb = 0; cb < BN / 64; ++cb) {
-        uint32_t r0[32], r1[32];
-        tmem_ld_32x32(taddr + cb * 64, r0);
-        tmem_ld_32x32(taddr + cb * 64 + 32, r1);
-        tmem_ld_wait();
-        // fp32 -> bf16, row `lane` of the staging tile (conflict-free: pitch 144 bytes)
-        uint4* row = (uint4*)(stg + lane * EPI_PITCH);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint4 o;
-          __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r0[8 * j + 0]), __uint_as_float(r0[8 * j + 1]));
-          __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r0[8 * j + 2]), __uint_as_float(r0[8 * j + 3]));
-          __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r0[8 * j + 4]), __uint_as_float(r0[8 * j + 5]));
-          __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r0[8 * j + 6]), __uint_as_float(r0[8 * j + 7]));
-          o.x = *(uint32_t*)&p0; o.y = *(uint32_t*)&p1; o.z = *(uint32_t*)&p2; o.w = *(uint32_t*)&p3;
-          row[j] = o;
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint4 o;
-          __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r1[8 * j + 0]), __uint_as_float(r1[8 * j + 1]));
-          __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r1[8 * j + 2]), __uint_as_float(r1[8 * j + 3]));
-          __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r1[8 * j + 4]), __uint_as_float(r1[8 * j + 5]));
-          __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r1[8 * j + 6]), __uint_as_float(r1[8 * j + 7]));
-          o.x = *(uint32_t*)&p0; o.y = *(uint32_t*)&p1; o.z = *(uint32_t*)&p2; o.w = *(uint32_t*)&p3;
-          row[4 + j] = o;
-        }
-        __syncwarp();
-        // 8 lanes cover one 128-byte row segment: 4 rows per pass, full lines on the wire
+      // 4 rows per pass of 8 lanes x 16 bytes: full 128-byte lines on the wire
+      auto store_block = [&](int cb) {
 #pragma unroll
         for (int p = 0; p < 8; ++p) {
           const int rr = p * 4 + (lane >> 3), c16 = lane & 7;
@@ -584,12 +568,77 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_c
             *(uint4*)g = v;
           }
         }
+      };
+      if constexpr (FP8) {
+        // One accumulator only (the scales take TMEM columns), so the MMA warp waits for this drain: pull
+        // the whole row into registers as packed bf16 first, hand the accumulator back, and only then go
+        // through shared memory to global memory, which overlaps the next tile's MMAs.
+        uint32_t pk[BN / 2];
+#pragma unroll
+        for (int cb = 0; cb < BN / 64; ++cb) {
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32(taddr + cb * 64, r0);
+          tmem_ld_32x32(taddr + cb * 64 + 32, r1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]));
+            __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
+            pk[cb * 32 + j] = *(uint32_t*)&p0;
+            pk[cb * 32 + 16 + j] = *(uint32_t*)&p1;
+          }
+        }
+        tc_fence_before();
         __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl->acc_empty[as]);
+#pragma unroll
+        for (int cb = 0; cb < BN / 64; ++cb) {
+          uint4* row = (uint4*)(stg + lane * EPI_PITCH);
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            row[j] = make_uint4(pk[cb * 32 + 4 * j], pk[cb * 32 + 4 * j + 1], pk[cb * 32 + 4 * j + 2], pk[cb * 32 + 4 * j + 3]);
+          __syncwarp();
+          store_block(cb);
+          __syncwarp();
+        }
+      } else {
+#pragma unroll 1
+        for (int cb = 0; cb < BN / 64; ++cb) {
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32(taddr + cb * 64, r0);
+          tmem_ld_32x32(taddr + cb * 64 + 32, r1);
+          tmem_ld_wait();
+          // fp32 -> bf16, row `lane` of the staging tile (conflict-free: pitch 144 bytes)
+          uint4* row = (uint4*)(stg + lane * EPI_PITCH);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 o;
+            __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r0[8 * j + 0]), __uint_as_float(r0[8 * j + 1]));
+            __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r0[8 * j + 2]), __uint_as_float(r0[8 * j + 3]));
+            __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r0[8 * j + 4]), __uint_as_float(r0[8 * j + 5]));
+            __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r0[8 * j + 6]), __uint_as_float(r0[8 * j + 7]));
+            o.x = *(uint32_t*)&p0; o.y = *(uint32_t*)&p1; o.z = *(uint32_t*)&p2; o.w = *(uint32_t*)&p3;
+            row[j] = o;
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 o;
+            __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r1[8 * j + 0]), __uint_as_float(r1[8 * j + 1]));
+            __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r1[8 * j + 2]), __uint_as_float(r1[8 * j + 3]));
+            __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r1[8 * j + 4]), __uint_as_float(r1[8 * j + 5]));
+            __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r1[8 * j + 6]), __uint_as_float(r1[8 * j + 7]));
+            o.x = *(uint32_t*)&p0; o.y = *(uint32_t*)&p1; o.z = *(uint32_t*)&p2; o.w = *(uint32_t*)&p3;
+            row[4 + j] = o;
+          }
+          __syncwarp();
+          store_block(cb);
+          __syncwarp();
+        }
+        // accumulator drained: hand it back to the MMA warp
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl->acc_empty[as]);
       }
-      // accumulator drained: hand it back to the MMA warp
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&ctl->acc_empty[as]);
       if (MODE == MODE_GEMM_RS) {
         // count this warp's quarter of the tile on the owner (release: the stores above come first)
         if (lane == 0) {

@@ -30,6 +30,7 @@ struct GemmArgs {
   int32_t ncomm;                       // AG_GEMM: CTAs that move data instead of computing; GEMM_RS: reducers
   int32_t comm_mode;                   // AG_GEMM: 0 copy-engine push, 1 copy-engine pull, 2 push with plain stores
   int32_t comm_split;                  // AG_GEMM: comm CTAs that share one 128-row chunk
+  int32_t raster;                      // plain GEMM: row blocks per group of the tile order (<= 1: row-major)
   uint64_t shard_off;                  // AG_GEMM pull: heap offset of every rank's own rows
   uint64_t gather_off;                 // AG_GEMM: heap offset of the gathered A buffer [M, K]
   uint64_t flags_off;                  // heap offset of the arrival counters

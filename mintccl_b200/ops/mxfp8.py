@@ -106,14 +106,15 @@ def tile_scales(scale: torch.Tensor) -> torch.Tensor:
 
 
 def gemm_mxfp8(a_data: torch.Tensor, a_scale: torch.Tensor, w_data: torch.Tensor, w_scale: torch.Tensor,
-               out: Optional[torch.Tensor] = None, nctas: int = 0) -> torch.Tensor:
+               out: Optional[torch.Tensor] = None, nctas: int = 0, scales_tiled: bool = False) -> torch.Tensor:
     """``dequant(a) [M, K] @ dequant(w)[N, K].T -> bf16 [M, N]`` on the block-scaled tensor cores
-    (``tcgen05.mma.kind::mxf8f6f4.block_scale``).  ``a_scale`` / ``w_scale`` are row-major ``[rows, K / 32]``."""
+    (``tcgen05.mma.kind::mxf8f6f4.block_scale``).  ``a_scale`` / ``w_scale`` are row-major ``[rows, K / 32]``,
+    or already in the tensor-core layout of ``tile_scales`` (``scales_tiled``: weights are tiled once, not per call)."""
     M, K = a_data.shape
     Nn = w_data.shape[0]
     if out is None:
         out = torch.empty(M, Nn, device=a_data.device, dtype=torch.bfloat16)
-    sfa, sfb = tile_scales(a_scale), tile_scales(w_scale)
+    sfa, sfb = (a_scale, w_scale) if scales_tiled else (tile_scales(a_scale), tile_scales(w_scale))
     stream = torch.cuda.current_stream(a_data.device).cuda_stream
     rc = N.lib().mt_gemm_mxfp8(stream, a_data.data_ptr(), sfa.data_ptr(), w_data.data_ptr(), sfb.data_ptr(),
                                out.data_ptr(), M, Nn, K, out.stride(0), nctas)

@@ -142,6 +142,23 @@ def main():
         ref = sum((a_.float() @ w_.float().t()).to(torch.bfloat16).float() for a_, w_ in zip(As, Ws))
         rows = M // n
         torch.testing.assert_close(y.float(), ref[rank * rows:(rank + 1) * rows], rtol=2e-2, atol=4e-2)
+    # the same two fusions on MXFP8 operands against the dequantised fp32 product
+    from mintccl_b200.ops import mxfp8 as mx
+    ag8 = AllGatherGemm(c, M, Nn, K, ncomm=4, fp8=True)
+    deq = lambda q, r_, k_: mx.dequantize_mxfp8(q[0].reshape(-1), q[1].reshape(-1)).view(r_, k_)
+    for it in range(2):
+        qs = [mx.quantize_rows_mxfp8(gen(r, (M // n) * K, torch.float32, seed0=90 + it).view(M // n, K)) for r in range(n)]
+        qw = [mx.quantize_rows_mxfp8(gen(r, Nn * K, torch.float32, seed0=95 + it).view(Nn, K) * 0.05) for r in range(n)]
+        out = ag8.call_mxfp8(qs[rank][0], qs[rank][1], qw[rank][0], qw[rank][1])
+        c.check()
+        ref = torch.cat([deq(q, M // n, K) for q in qs], 0) @ deq(qw[rank], Nn, K).t()
+        torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=5e-2)
+        qA = [mx.quantize_rows_mxfp8(gen(r, M * K, torch.float32, seed0=100 + it).view(M, K)) for r in range(n)]
+        y = rs.call_mxfp8(qA[rank][0], qA[rank][1], qw[rank][0], qw[rank][1])
+        c.check()
+        ref = sum((deq(qA[r], M, K) @ deq(qw[r], Nn, K).t()).to(torch.bfloat16).float() for r in range(n))
+        rows = M // n
+        torch.testing.assert_close(y.float(), ref[rank * rows:(rank + 1) * rows], rtol=2e-2, atol=6e-2)
     c.control.barrier()
     # point to point: deferred API over a multi-hop ring route, direct pull and push, registered tensor
     os.environ["MINTCCL_ROUTE"] = "ring"
