@@ -14,6 +14,7 @@ using mthost::fail;
 namespace {
 
 constexpr int kBM = 128, kBN = 256, kBK = 64;
+constexpr int kPairDefault = 1;  // plain GEMMs on CTA pairs unless MINTCCL_GEMM_PAIR says otherwise
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -33,6 +34,21 @@ int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K, uint
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled failed: CUresult " + std::to_string((int)r));
+  return 0;
+}
+
+// Tiled MXFP8 scales as a [atoms, 128] tensor of 32-bit words: one box = one 512-byte atom.
+int make_sf_map(CUtensorMap* map, const void* base, uint64_t atoms) {
+  static EncodeTiledFn enc = (EncodeTiledFn)mthost::driver_entry("cuTensorMapEncodeTiled");
+  if (!enc) return fail("cuTensorMapEncodeTiled not available");
+  if ((uintptr_t)base & 15) return fail("scale tensors must be 16-byte aligned");
+  cuuint64_t dims[2] = {128, atoms};
+  cuuint64_t strides[1] = {512};
+  cuuint32_t box[2] = {128, 1};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled (scales) failed: CUresult " + std::to_string((int)r));
   return 0;
 }
 
@@ -66,12 +82,59 @@ static int raster_for(int M, int N, int K, int elem_bytes) {
   return b_bytes > 48e6 ? 16 : 1;
 }
 
+// The plain GEMM runs on CTA pairs (one 256 x 256 tile per cluster of two CTAs, gemm_tc2.cu) when M allows
+// it; MINTCCL_GEMM_PAIR=0 selects the single-CTA kernel.
+static int g_pair_mode = -1;
+static bool use_pair(int M) {
+  if (g_pair_mode < 0) {
+    const char* e = getenv("MINTCCL_GEMM_PAIR");
+    g_pair_mode = e ? atoi(e) : kPairDefault;
+  }
+  return g_pair_mode != 0 && M % 256 == 0;
+}
+
+static int gemm_pair(void* stream, const void* A, const void* sfa, const void* B, const void* sfb, void* C, int M, int N,
+                     int K, int ldc, int nctas, bool fp8) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  mt::Gemm2Maps maps;
+  memset(&maps, 0, sizeof(maps));
+  if (make_map(&maps.a, A, M, K, 128, fp8) || make_map(&maps.b, B, N, K, 128, fp8)) return -1;
+  if (fp8) {
+    if (make_sf_map(&maps.sfa, sfa, (uint64_t)(M / 128) * (K / 128)) ||
+        make_sf_map(&maps.sfb, sfb, (uint64_t)(N / 128) * (K / 128)))
+      return -1;
+  }
+  mt::Gemm2Args a;
+  memset(&a, 0, sizeof(a));
+  a.c = C;
+  a.M = M;
+  a.N = N;
+  a.K = K;
+  a.ldc = ldc;
+  a.raster = raster_for(M, N, K, fp8 ? 1 : 2) / 2;
+  a.timeout_ns = 4000000000ull;
+  const int tiles = (M / 256) * (N / kBN);
+  int nclusters = (nctas > 0 ? nctas : sm_count(dev)) / 2;
+  if (nclusters > tiles) nclusters = tiles;
+  if (nclusters < 1) nclusters = 1;
+  cudaError_t e = mt::launch_gemm_pair(maps, a, nclusters, (cudaStream_t)stream, fp8);
+  if (e != cudaSuccess) return fail(std::string("pair gemm launch: ") + cudaGetErrorString(e));
+  return 0;
+}
+
 extern "C" {
+
+// 1 after a bounded wait of the CTA-pair GEMM expired (the result of that call is then invalid), 0 otherwise.
+int mt_gemm_pair_error(void) { return mt::gemm_pair_error(); }
+// 1: plain GEMMs use CTA pairs where the shape allows, 0: single-CTA kernel, -1: back to the environment / default.
+void mt_gemm_set_pair(int mode) { g_pair_mode = mode; }
 
 // C[M, ldc] = A[M, K] * B[N, K]^T in bf16 with fp32 accumulation, on the current device.
 int mt_gemm(void* stream, const void* A, const void* B, void* C, int M, int N, int K, int ldc, int nctas) {
   if (check_shape(M, N, K, 1)) return -1;
   if (ldc < N || ldc % 8 || ((uintptr_t)C & 15)) return fail("C must be 16-byte aligned with ldc >= N, ldc % 8 == 0");
+  if (use_pair(M)) return gemm_pair(stream, A, nullptr, B, nullptr, C, M, N, K, ldc, nctas, false);
   int dev = 0;
   cudaGetDevice(&dev);
   mt::GemmMaps maps;
@@ -105,6 +168,7 @@ int mt_gemm_mxfp8(void* stream, const void* A, const void* sfa, const void* B, c
   if (check_shape(M, N, K, 1) || K % 128) return fail("MXFP8 GEMM: M multiple of 128, N of 256, K of 128");
   if (ldc < N || ldc % 8 || ((uintptr_t)C & 15)) return fail("C must be 16-byte aligned with ldc >= N, ldc % 8 == 0");
   if (((uintptr_t)sfa | (uintptr_t)sfb) & 15) return fail("scale tensors must be 16-byte aligned");
+  if (use_pair(M)) return gemm_pair(stream, A, sfa, B, sfb, C, M, N, K, ldc, nctas, true);
   int dev = 0;
   cudaGetDevice(&dev);
   mt::GemmMaps maps;

@@ -92,6 +92,10 @@ int mt_p2p(MtComm* c, void* stream, int src_rank, int dst_rank, const void* src_
 int mt_gemm(void* stream, const void* A, const void* B, void* C, int M, int N, int K, int ldc, int nctas);
 int mt_gemm_mxfp8(void* stream, const void* A, const void* sfa, const void* B, const void* sfb, void* C, int M, int N,
                   int K, int ldc, int nctas);
+// Plain GEMMs with M % 256 == 0 run on CTA pairs (tcgen05 cta_group::2) when MINTCCL_GEMM_PAIR is not 0; a wait
+// of that kernel that expired leaves 1 here (synchronises the device).
+int mt_gemm_pair_error(void);
+void mt_gemm_set_pair(int mode);                          // 1 pairs, 0 single CTA, -1 environment / default
 int mt_ag_gemm(MtComm* c, void* stream, const void* const* a_shard, const void* const* B, void* const* C,
                uint64_t gather_off, uint64_t flags_off, uint64_t epoch, int M, int N, int K, int ldc, int ncomm,
                int nctas, int comm_mode, uint64_t shard_off, int comm_split);

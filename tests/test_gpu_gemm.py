@@ -14,8 +14,20 @@ def close(got, ref32, k):
     torch.testing.assert_close(got.float(), ref32, rtol=1.6e-2, atol=2e-2 * (k ** 0.5) * 0.05 + 1e-2)
 
 
-@pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 128), (384, 256, 1024), (1024, 1792, 4096), (2048, 4096, 1792)])
-def test_gemm_matches_fp32_reference(shape):
+@pytest.fixture(params=[1, 0], ids=["cta_pair", "single_cta"])
+def gemm_kernel(request):
+    """Plain GEMMs run on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles) when M % 256 == 0, else on the
+    single-CTA kernel (128 x 256 tiles); both are tested on every shape."""
+    from mintccl_b200 import _native as N
+    N.lib().mt_gemm_set_pair(request.param)
+    yield request.param
+    assert N.lib().mt_gemm_pair_error() == 0, "a bounded wait of the CTA-pair GEMM expired"
+    N.lib().mt_gemm_set_pair(-1)
+
+
+@pytest.mark.parametrize("shape", [(128, 256, 64), (256, 256, 64), (256, 512, 128), (384, 256, 1024), (1024, 1792, 4096),
+                                   (2048, 4096, 1792), (4096, 2048, 512)])
+def test_gemm_matches_fp32_reference(shape, gemm_kernel):
     from mintccl_b200.ops.gemm import gemm
     M, N, K = shape
     g = torch.Generator(device="cuda").manual_seed(M + N + K)
@@ -83,8 +95,8 @@ def test_tp_mlp_forward_backward_single_rank():
     smoke_mlp()
 
 
-@pytest.mark.parametrize("shape", [(128, 256, 128), (256, 512, 512), (1024, 1792, 4096)])
-def test_mxfp8_gemm_matches_dequantised_reference(shape):
+@pytest.mark.parametrize("shape", [(128, 256, 128), (256, 256, 128), (256, 512, 512), (1024, 1792, 4096), (2048, 1024, 1024)])
+def test_mxfp8_gemm_matches_dequantised_reference(shape, gemm_kernel):
     """Block-scaled fp8 GEMM against the fp32 product of the dequantised operands (the quantisation error is in
     both; what is compared is the tensor-core arithmetic and the scale plumbing)."""
     from mintccl_b200.ops import mxfp8 as mx
