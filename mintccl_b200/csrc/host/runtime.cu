@@ -484,6 +484,17 @@ int mt_ring(MtComm* c, void* stream, int proto, int dtype, int op, const void* c
   if (nchannels < 1 || nchannels > max_ch) return fail("nchannels out of range");
   if (chain_len > MT_MAX_RANKS + 1) return fail("route too long");
   if (c->emulated && nchannels * c->nlocal > 148) return fail("emulated world: channels * ranks must be <= 148");
+  if (c->nranks == 1 && !c->emulated && in && out && getenv("MINTCCL_NO_LOCAL_COPY") == nullptr) {
+    // the only rank's contribution is the result: nothing to do in place, else one copy at HBM speed
+    if (nbytes % mt::dtype_size(dtype)) return fail("byte count is not a multiple of the element size");
+    if (in[0] == out[0] || nbytes == 0) return 0;
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, c->device);
+    cudaError_t e = mt::launch_local_copy(out[0], in[0], nbytes, sms, (cudaStream_t)stream);
+    if (e == cudaSuccess) return 0;
+    if (e != cudaErrorInvalidValue) return fail(std::string("local copy launch: ") + cudaGetErrorString(e));
+    cudaGetLastError();  // pointers not co-aligned: the ring kernel copies any alignment
+  }
   mt::RingArgs a;
   memset(&a, 0, sizeof(a));
   for (int lr = 0; lr < c->nlocal; ++lr) {

@@ -24,5 +24,7 @@ cudaError_t launch_ring_ll128(int dtype, const MtDevComm* comms, const RingArgs&
 cudaError_t launch_direct(int dtype, const MtDevComm* comms, const DirectArgs& a, int nctas, int nlocal, cudaStream_t s);
 cudaError_t launch_p2p(const MtDevComm* comms, const P2pArgs& a, int nctas, int nlocal, cudaStream_t s);
 cudaError_t launch_ll_allreduce(int dtype, const MtDevComm* comms, const LLArgs& a, int nctas, int nlocal, cudaStream_t s);
+// one-rank communicators: every collective is this copy (invalid value: pointers not co-aligned, use the ring kernel)
+cudaError_t launch_local_copy(void* dst, const void* src, uint64_t nbytes, int sms, cudaStream_t s);
 cudaError_t launch_wait_timeout_test(const MtDevComm* comms, int nlocal, cudaStream_t s);
 }  // namespace mt

@@ -327,3 +327,35 @@ def test_mxfp8_block_scaled_reductions(n):
         torch.testing.assert_close(mx.dequantize_mxfp8(sd[r], ss[r]), ref_q[r * per:(r + 1) * per], rtol=0.07, atol=2e-3)
     for t in (data, scale, od, os_):
         w.symm_free(t)
+
+
+def test_one_rank_communicator_copies_at_any_alignment():
+    """A communicator of one rank: every collective is a local copy (its own kernel when source and destination
+    share the offset inside a 16-byte line, else the ring kernel); in place nothing runs."""
+    import mintccl_b200
+    from mintccl_b200 import Config
+    comm = mintccl_b200.Communicator(config=Config.from_env(heap_bytes=256 << 20, max_channels=4))
+    assert comm.world_size == 1
+    base_in = torch.arange(0, 3_000_064, device="cuda", dtype=torch.int32).view(torch.uint8)
+    base_out = torch.zeros(base_in.numel() + 64, device="cuda", dtype=torch.uint8)
+    for nbytes, oi, oo in [(16, 0, 0), (1, 3, 3), (15, 1, 1), (4096 * 8 + 5, 7, 7), (1_000_003, 0, 0), (2_500_000, 13, 13),
+                           (33, 5, 9), (100_001, 2, 0), (8 << 20, 0, 16)]:
+        src = base_in[oi:oi + nbytes]
+        dst = base_out[oo:oo + nbytes]
+        base_out.zero_()
+        comm.allgather(dst.view(1, -1), src)
+        comm.check()
+        assert torch.equal(dst, src), (nbytes, oi, oo)
+        assert int(base_out[oo + nbytes:oo + nbytes + 32].sum()) == 0 and int(base_out[:oo].sum()) == 0, "wrote outside"
+    x = torch.randn(1, 100_000, device="cuda", dtype=torch.float16)
+    y = x.clone()
+    comm.allgather(x)          # in place: nothing to do
+    comm.reducescatter(x)
+    comm.broadcast(x, 0)
+    comm.reduce(x, 0)
+    comm.check()
+    assert torch.equal(x, y)
+    out = torch.zeros(100_000, device="cuda", dtype=torch.float16)
+    comm.reducescatter(x, out)
+    comm.check()
+    assert torch.equal(out, x[0])
