@@ -417,8 +417,23 @@ class Communicator:
         self._run(self.lib.mt_direct, (dtype, dop, inp, outp, in_off or 0, out_off or 0, nbytes, root, variant,
                                        1 if nvls else 0, nctas))
 
-    def _algo(self, algo: Optional[str]) -> str:
-        return algo or self.cfg.algo
+    _ALGOS = {
+        "allreduce": ("auto", "ring", "direct", "nvls", "ll", "oneshot"),
+        "allgather": ("auto", "ring", "direct", "nvls", "pull"),
+        "reducescatter": ("auto", "ring", "direct", "nvls"),
+        "broadcast": ("auto", "ring", "direct", "nvls", "pull", "push", "nvls1"),
+        "reduce": ("auto", "ring", "direct", "nvls", "direct1", "nvls1"),
+    }
+
+    def _algo(self, algo: Optional[str], collective: str) -> str:
+        """The algorithm of one call: ``algo=`` must be one this collective has; the process-wide default
+        (``MINTCCL_ALGO``) applies where the collective has it and means ``auto`` elsewhere."""
+        known = self._ALGOS[collective]
+        if algo is not None:
+            if algo not in known:
+                raise ValueError(f"{collective}: unknown algo {algo!r} (one of {', '.join(known)})")
+            return algo
+        return self.cfg.algo if self.cfg.algo in known else "auto"
 
     def _want_nvls(self, nbytes: int, tensors) -> bool:
         """In-switch reduction / replication pays off from four ranks on (with two ranks the switch only
@@ -468,7 +483,7 @@ class Communicator:
         outs = self._lists(out) or ins
         nbytes = ins[0].numel() * ins[0].element_size()
         dt = _dtype_code(ins[0], True)
-        algo = self._algo(algo)
+        algo = self._algo(algo, "allreduce")
         in_off, out_off = self._symm_off_all(ins), self._symm_off_all(outs)
         if self.world_size == 1:
             algo = "ring"  # a single rank: the ring kernel degenerates to a local copy
@@ -522,7 +537,7 @@ class Communicator:
         if B * n != outs[0].numel() * outs[0].element_size():
             raise ValueError("contribution and buffer sizes do not match")
         dt = _dtype_code(outs[0], False)
-        algo = self._algo(algo)
+        algo = self._algo(algo, "allgather")
         out_off = self._symm_off_all(outs)
         if n == 1:
             algo = "ring"
@@ -566,7 +581,7 @@ class Communicator:
         outs = self._lists(out) or [i[r] for i, r in zip(ins, ranks)]
         B = outs[0].numel() * outs[0].element_size()
         dt = _dtype_code(ins[0], True)
-        algo = self._algo(algo)
+        algo = self._algo(algo, "reducescatter")
         in_off = self._symm_off_all(ins)
         if n == 1:
             algo = "ring"
@@ -599,7 +614,7 @@ class Communicator:
         dt = _dtype_code(ts[0], False)
         if self.world_size == 1:
             return
-        algo = self._algo(algo)
+        algo = self._algo(algo, "broadcast")
         off = self._symm_off_all(ts)
         if algo == "auto":
             # A wide pipelined ring (algo="ring", 48+ channels) moves more bytes per second when broadcasts
@@ -615,9 +630,10 @@ class Communicator:
         if algo in ("direct", "nvls", "pull", "push", "nvls1"):
             if off is None:
                 raise ValueError(f"algo={algo} needs a symmetric buffer")
-            # "direct"/"nvls": scatter + all-gather (every rank replicates one sub-slice); "push": the root
-            # writes everything to everybody; "pull": everybody reads the root; "nvls1": only the root issues
-            # multicast stores.  With two ranks scatter + all-gather is the plain push.
+            # "direct"/"nvls": pull + replicate (every rank reads one sub-slice from the root and stores it to
+            # all ranks, through the switch's multicast with "nvls"); "push": the root writes everything to
+            # everybody; "pull": everybody reads the root; "nvls1": only the root issues multicast stores.
+            # With two ranks pull + replicate is the plain push.
             variant = {"pull": 1, "push": 0, "nvls1": 0}.get(algo, 2 if (self.world_size > 2 and nbytes % 16 == 0) else 0)
             self._launch_direct(N.DOP_BROADCAST, ts, ts, off, off, nbytes, dt, root=root, variant=variant,
                                 nvls=algo in ("nvls", "nvls1"), nctas=nch)
@@ -640,7 +656,7 @@ class Communicator:
         outs = self._lists(out) or ins
         nbytes = ins[0].numel() * ins[0].element_size()
         dt = _dtype_code(ins[0], True)
-        algo = self._algo(algo)
+        algo = self._algo(algo, "reduce")
         if self.world_size == 1:
             algo = "ring"
         off = self._symm_off_all(ins)

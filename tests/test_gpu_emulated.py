@@ -359,3 +359,28 @@ def test_one_rank_communicator_copies_at_any_alignment():
     comm.reducescatter(x, out)
     comm.check()
     assert torch.equal(out, x[0])
+
+
+def test_algorithm_names_are_checked_per_collective():
+    w = world(2)
+    bufs = [torch.zeros(2, 64, device="cuda", dtype=torch.float16) for _ in range(2)]
+    with pytest.raises(ValueError, match="unknown algo"):
+        w.reducescatter(bufs, algo="pull")          # an all-gather / broadcast variant only
+    with pytest.raises(ValueError, match="unknown algo"):
+        w.allgather(bufs, algo="oneshot")
+    with pytest.raises(ValueError, match="unknown algo"):
+        w.allreduce([b[0] for b in bufs], algo="nonsense")
+    # a process-wide default that a collective does not have means "automatic" there
+    old = w.cfg.algo
+    try:
+        w.cfg.algo = "ll"   # MINTCCL_ALGO=ll: the one-shot all-reduce; reduce-scatter has no such variant
+        srcs = rand(2, 2 * 64, torch.float16)
+        for b, s_ in zip(bufs, srcs):
+            b.copy_(s_.view(2, 64))
+        w.reducescatter(bufs)
+        w.check()
+        ref = oracle_sum(srcs).view(2, 64)
+        for r in range(2):
+            assert_sum_close(bufs[r][r], ref[r], torch.float16, 2)
+    finally:
+        w.cfg.algo = old
