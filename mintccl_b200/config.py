@@ -3,7 +3,7 @@
 Keeps every knob of the reference (common.py:76-118: ``MINTCCL_NUM_BLOCKS``, ``MINTCCL_NUM_WARPS``,
 ``MINTCCL_BUFFSIZE``, ``MINTCCL_TEST_MODE``, ``MINTCCL_TEST_COUNT``, ``MINTCCL_TEST_VERBOSE``) under the
 same names and adds the ones its roadmap asks for (README.md:57 "fine-grained control of SM layout"):
-algorithm, protocol, channel count, FIFO depth, wait budget, heap size.  Booleans are parsed properly:
+algorithm, protocol, channel count, FIFO depth, wait time limit, heap size.  Booleans are parsed properly:
 the reference's ``bool(os.getenv(...))`` (common.py:113,118) is true for the string ``"0"``.
 """
 from __future__ import annotations

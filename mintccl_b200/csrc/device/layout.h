@@ -100,7 +100,7 @@ struct MtDevComm {
   int32_t ring_pos;                    // my position in ring[]
   int32_t ring[MT_MAX_RANKS];          // ring order: ring[i+1] is the successor of ring[i]
   int32_t has_mc;                      // multicast (NVLS) mapping available
-  uint64_t timeout_ns;                 // budget of every device-side wait
+  uint64_t timeout_ns;                 // time limit of every device-side wait
   uint8_t* heap[MT_MAX_RANKS];         // heap base of every rank in MY address space
   uint8_t* mc;                         // multicast alias of the heap (all ranks at once) or nullptr
   MtHeapLayout L;

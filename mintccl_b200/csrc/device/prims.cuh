@@ -162,7 +162,7 @@ __device__ __forceinline__ MtStatus* status_of(const MtDevComm& c, int rank) {
 }
 
 // Record the first error of this rank and raise the abort flag here and on every peer so that all
-// other waits give up quickly instead of each running out its own budget.
+// other waits give up quickly instead of each running out its own time limit.
 static __device__ __noinline__ void report_error(const MtDevComm& c, uint32_t code, uint32_t channel, uint32_t where,
                                           uint64_t expected, uint64_t seen, uint64_t step) {
   MtStatus* st = status_of(c, c.rank);
@@ -182,7 +182,7 @@ __device__ __forceinline__ bool abort_raised(const MtDevComm& c) {
   return load32_volatile(&status_of(c, c.rank)->abort) != 0u;
 }
 
-// Spin until pred() holds.  Every 256 polls the abort flag and the wall-clock budget are checked; the
+// Spin until pred() holds.  Every 256 polls the abort flag and the wall-clock limit are checked; the
 // wait backs off with nanosleep once it has clearly not been satisfied at once.  Returns false when it
 // gave up (after recording the error); the caller must then unwind without touching peer memory again.
 template <class Pred>

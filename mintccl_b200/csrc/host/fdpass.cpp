@@ -67,7 +67,7 @@ extern "C" int mt_fd_send(const char* name, int tag, int fd, int timeout_ms) {
   timespec t0;
   clock_gettime(CLOCK_MONOTONIC, &t0);
   int s = -1;
-  while (true) {  // the listener may not be up yet: retry until the budget runs out
+  while (true) {  // the listener may not be up yet: retry until the time limit runs out
     s = socket(AF_UNIX, SOCK_STREAM, 0);
     if (s < 0) return -1;
     if (connect(s, (sockaddr*)&a, len) == 0) break;

@@ -40,7 +40,7 @@ cudaError_t launch_ll_allreduce(int dtype, const MtDevComm* comms, const LLArgs&
   }
 }
 
-// A wait on a word that nothing ever writes: must give up after the communicator's budget, record
+// A wait on a word that nothing ever writes: must give up after the communicator's time limit, record
 // MT_ERR_TIMEOUT_SIGNAL and return, leaving the context usable.
 __global__ void wait_timeout_test_kernel(const MtDevComm* comms) {
   const MtDevComm& c = comms[blockIdx.y];

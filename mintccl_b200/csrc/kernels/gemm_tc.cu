@@ -57,7 +57,7 @@ struct SharedCtl {
   int abort;
 };
 
-// Bounded mbarrier wait.  Returns false after the budget or when the CTA-wide abort flag is up.
+// Bounded mbarrier wait.  Returns false after the time limit or when the CTA-wide abort flag is up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, uint64_t timeout_ns) {
   uint32_t spins = 0;
   uint64_t t0 = 0;

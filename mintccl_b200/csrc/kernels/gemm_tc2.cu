@@ -316,7 +316,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
   tc_fence_before();
   __syncthreads();
   if (threadIdx.x == 0 && *abort_flag) {
-    // tell the peer (it would notice by itself after its own budget) and the host
+    // tell the peer (it would notice by itself after its own time limit) and the host
     st_cluster_u32(map_to_cta(smem_u32(&ctl->abort), cr ^ 1), 1u);
     atomicExch(&g_pair_error, 1);
   }

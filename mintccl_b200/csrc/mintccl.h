@@ -24,7 +24,7 @@ typedef struct {
   uint64_t ll_bytes;           // one-shot area: wire bytes per (parity, sender)
   uint64_t scratch_bytes;
   uint64_t heap_bytes;         // whole heap (control + user part)
-  uint64_t timeout_ms;         // budget of device-side waits
+  uint64_t timeout_ms;         // time limit of device-side waits
   int32_t heap_kind;           // 0 = cuMem VMM (fd export, NVLS capable), 1 = cudaMalloc + cudaIpc
 } MtConfig;
 

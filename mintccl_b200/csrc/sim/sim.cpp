@@ -4,7 +4,7 @@
 // ld/st.acquire/release.  It proves properties that must not be probed on a shared GPU:
 //   * no deadlock at 2/4/8 ranks over many back-to-back operations with random scheduling jitter;
 //   * flags and counters that grow across operations never match stale data;
-//   * a rank that never shows up makes every waiting rank give up after its budget with an error
+//   * a rank that never shows up makes every waiting rank give up after its time limit with an error
 //     record (fault injection on the host), instead of spinning forever as the reference's waits do
 //     (protocol.py:115,127,177).
 #include <string.h>

@@ -850,7 +850,7 @@ class Communicator:
 
     # ------------------------------------------------------------------------------ self tests
     def test_wait_timeout(self) -> N.MtStatus:
-        """Launch a wait that nothing satisfies; it must give up after the communicator's budget and
+        """Launch a wait that nothing satisfies; it must give up after the communicator's time limit and
         leave an error record instead of hanging.  Returns the status of local rank 0."""
         N.check(self.lib.mt_test_wait_timeout(self._handle, self._stream()), "test_wait_timeout")
         return self.status(0)

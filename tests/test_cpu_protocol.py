@@ -118,7 +118,7 @@ def test_simulated_allreduce_eight_ranks_many_iterations_with_jitter():
 
 @pytest.mark.parametrize("proto", [0, 1])
 def test_injected_dead_rank_is_reported_not_hung(proto):
-    """A rank that never joins: every rank that depends on it gives up after its budget, records who was
+    """A rank that never joins: every rank that depends on it gives up after its time limit, records who was
     waiting for what, and raises the abort flag on its peers.  Nothing spins forever."""
     rc, st = sim(4, 2, proto, OPS["allreduce"], 4000, dead=2, timeout_ms=300)
     assert rc == 2

@@ -274,7 +274,7 @@ def test_direct_sendrecv_symmetric():
 
 
 def test_bounded_wait_reports_instead_of_hanging():
-    """A wait that nothing satisfies returns after the budget with an error record; the context stays
+    """A wait that nothing satisfies returns after the time limit with an error record; the context stays
     usable and the communicator reports the failure on the host."""
     from mintccl_b200 import Config, emulated
     from mintccl_b200.parallel.comm import CollectiveError
@@ -283,7 +283,7 @@ def test_bounded_wait_reports_instead_of_hanging():
     w = emulated(2, 0, cfg)
     w.test_wait_timeout()
     sts = [w.status(r) for r in range(2)]
-    # the rank whose budget ran out first reports the timeout (5) and raises the abort flag everywhere;
+    # the rank whose time limit ran out first reports the timeout (5) and raises the abort flag everywhere;
     # the other one may notice that flag first and report "aborted by a peer" (6)
     assert all(st.code in (5, 6) and st.where == 10 and st.abort == 1 for st in sts)
     assert any(st.code == 5 for st in sts)
