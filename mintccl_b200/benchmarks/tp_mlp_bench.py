@@ -30,6 +30,8 @@ def main() -> None:
     ap.add_argument("--ncomm", default="0", help="comma list of comm-CTA counts to try for the all-gather fusion")
     ap.add_argument("--split", default="1", help="comma list: comm CTAs that share one 128-row chunk")
     ap.add_argument("--modes", default="push", help="comma list of all-gather transports: push, pull, push_st")
+    ap.add_argument("--mxfp8", action="store_true",
+                    help="also time both fused kernels on MXFP8 operands (quantised once, outside the timed loop)")
     a = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -115,6 +117,29 @@ def main() -> None:
     out["max_abs_err_up"], out["max_abs_err_down"] = round(err_up, 4), round(err_down, 4)
     out["up_speedup"] = round(out["up_unfused_us"] / out["up_fused_us"], 3)
     out["down_speedup"] = round(out["down_unfused_us"] / out["down_fused_us"], 3)
+    if a.mxfp8 and H % 128 == 0 and F % 128 == 0:
+        # The same two projections on block-scaled fp8 operands.  Activations and weights are quantised before the
+        # timed loop (a model would quantise in the epilogue of the producing kernel); the tiling of the activation
+        # scales and their small all-gather are inside it.  Checked against the dequantised fp32 product.
+        from mintccl_b200.ops import mxfp8 as mx
+        qx = mx.quantize_rows_mxfp8(x_shard.float())
+        qwu = mx.quantize_rows_mxfp8(w_up.float())
+        qwd = mx.quantize_rows_mxfp8(w_down.float())
+        qact = mx.quantize_rows_mxfp8(act.float())
+        twu, twd = mx.tile_scales(qwu[1]), mx.tile_scales(qwd[1])
+        ag8 = AllGatherGemm(comm, T, F, H, fp8=True)
+        h8 = torch.empty(T, F, device="cuda", dtype=torch.bfloat16)
+        out["up_fused_mxfp8_us"] = round(timed(lambda: ag8.call_mxfp8(qx[0], qx[1], qwu[0], twu, out=h8, w_scale_tiled=True)), 1)
+        comm.check()
+        y8 = torch.empty(T // n, H, device="cuda", dtype=torch.bfloat16)
+        out["down_fused_mxfp8_us"] = round(timed(lambda: rs.call_mxfp8(qact[0], qact[1], qwd[0], twd, out=y8, w_scale_tiled=True)), 1)
+        comm.check()
+        # against the bf16 results: both carry the fp8 quantisation error of operands of unit scale (~2^-4 relative
+        # per element, averaged down over K)
+        out["mxfp8_rel_err_up"] = round(((h8.float() - h_ref.float()).norm() / h_ref.float().norm()).item(), 4)
+        out["mxfp8_rel_err_down"] = round(((y8.float() - y_ref.float()).norm() / y_ref.float().norm()).item(), 4)
+        out["up_mxfp8_speedup_vs_unfused_bf16"] = round(out["up_unfused_us"] / out["up_fused_mxfp8_us"], 3)
+        out["down_mxfp8_speedup_vs_unfused_bf16"] = round(out["down_unfused_us"] / out["down_fused_mxfp8_us"], 3)
     # roofline: the slower of the GEMM at the measured cuBLAS peak and the bytes over NVLink at 770 GB/s
     link_bytes = (n - 1) / n * T * H * 2
     peak = 1369.5e12

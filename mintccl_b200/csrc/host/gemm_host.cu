@@ -97,28 +97,32 @@ static int gemm_pair(void* stream, const void* A, const void* sfa, const void* B
                      int K, int ldc, int nctas, bool fp8) {
   int dev = 0;
   cudaGetDevice(&dev);
-  mt::Gemm2Maps maps;
+  mt::GemmMaps maps;
+  mt::PairSfMaps sf;
   memset(&maps, 0, sizeof(maps));
-  if (make_map(&maps.a, A, M, K, 128, fp8) || make_map(&maps.b, B, N, K, 128, fp8)) return -1;
+  memset(&sf, 0, sizeof(sf));
+  if (make_map(&maps.a[0], A, M, K, 128, fp8) || make_map(&maps.b[0], B, N, K, 128, fp8)) return -1;
+  maps.a2[0] = maps.a[0];
   if (fp8) {
-    if (make_sf_map(&maps.sfa, sfa, (uint64_t)(M / 128) * (K / 128)) ||
-        make_sf_map(&maps.sfb, sfb, (uint64_t)(N / 128) * (K / 128)))
+    if (make_sf_map(&sf.sfa[0], sfa, (uint64_t)(M / 128) * (K / 128)) ||
+        make_sf_map(&sf.sfb[0], sfb, (uint64_t)(N / 128) * (K / 128)))
       return -1;
   }
-  mt::Gemm2Args a;
+  mt::GemmArgs a;
   memset(&a, 0, sizeof(a));
-  a.c = C;
+  a.c[0] = C;
   a.M = M;
   a.N = N;
   a.K = K;
   a.ldc = ldc;
+  a.nranks = 1;
   a.raster = raster_for(M, N, K, fp8 ? 1 : 2) / 2;
   a.timeout_ns = 4000000000ull;
   const int tiles = (M / 256) * (N / kBN);
   int nclusters = (nctas > 0 ? nctas : sm_count(dev)) / 2;
   if (nclusters > tiles) nclusters = tiles;
   if (nclusters < 1) nclusters = 1;
-  cudaError_t e = mt::launch_gemm_pair(maps, a, nclusters, (cudaStream_t)stream, fp8);
+  cudaError_t e = mt::launch_gemm_pair(mt::MODE_PLAIN, maps, sf, a, nclusters, 1, (cudaStream_t)stream, fp8);
   if (e != cudaSuccess) return fail(std::string("pair gemm launch: ") + cudaGetErrorString(e));
   return 0;
 }
@@ -257,6 +261,24 @@ static int ag_gemm_impl(MtComm* c, void* stream, const void* const* a_shard, con
       a.sfb[lr] = sfb[lr];
     }
   }
+  if (use_pair(M / n) && comm_mode != 2) {
+    // CTA pairs: 256-row tiles inside one owner's rows, B split between the two CTAs, comm CTAs in whole clusters
+    mt::PairSfMaps sf;
+    memset(&sf, 0, sizeof(sf));
+    for (int lr = 0; lr < c->nlocal; ++lr) {
+      if (make_map(&maps.b[lr], B[lr], N, K, 128, fp8)) return -1;
+      if (fp8 && (make_sf_map(&sf.sfa[lr], sfa[lr], (uint64_t)(M / 128) * (K / 128)) ||
+                  make_sf_map(&sf.sfb[lr], sfb[lr], (uint64_t)(N / 128) * (K / 128))))
+        return -1;
+    }
+    a.ncomm = (ncomm + 1) & ~1;
+    if (a.comm_split > 1 && a.ncomm % a.comm_split) return fail("comm_split must divide the (even) number of comm CTAs");
+    const int nclusters = (grid - a.ncomm) / 2;
+    if (nclusters < 1) return fail("not enough CTAs for the requested comm CTAs");
+    cudaError_t e2 = mt::launch_gemm_pair(mt::MODE_AG_GEMM, maps, sf, a, nclusters, c->nlocal, (cudaStream_t)stream, fp8);
+    if (e2 != cudaSuccess) return fail(std::string("pair ag_gemm launch: ") + cudaGetErrorString(e2));
+    return 0;
+  }
   cudaError_t e = mt::launch_gemm_tc(mt::MODE_AG_GEMM, maps, a, grid, c->nlocal, (cudaStream_t)stream, fp8);
   if (e != cudaSuccess) return fail(std::string("ag_gemm launch: ") + cudaGetErrorString(e));
   return 0;
@@ -304,6 +326,22 @@ static int gemm_rs_impl(MtComm* c, void* stream, const void* const* A, const voi
       a.sfa[lr] = sfa[lr];
       a.sfb[lr] = sfb[lr];
     }
+  }
+  if (use_pair(M / c->nranks)) {
+    mt::PairSfMaps sf;
+    memset(&sf, 0, sizeof(sf));
+    for (int lr = 0; lr < c->nlocal; ++lr) {
+      if (make_map(&maps.b[lr], B[lr], N, K, 128, fp8)) return -1;
+      if (fp8 && (make_sf_map(&sf.sfa[lr], sfa[lr], (uint64_t)(M / 128) * (K / 128)) ||
+                  make_sf_map(&sf.sfb[lr], sfb[lr], (uint64_t)(N / 128) * (K / 128))))
+        return -1;
+    }
+    a.ncomm = (nred + 1) & ~1;
+    const int nclusters = (grid - a.ncomm) / 2;
+    if (nclusters < 1) return fail("nred out of range");
+    cudaError_t e2 = mt::launch_gemm_pair(mt::MODE_GEMM_RS, maps, sf, a, nclusters, c->nlocal, (cudaStream_t)stream, fp8);
+    if (e2 != cudaSuccess) return fail(std::string("pair gemm_rs launch: ") + cudaGetErrorString(e2));
+    return 0;
   }
   cudaError_t e = mt::launch_gemm_tc(mt::MODE_GEMM_RS, maps, a, grid, c->nlocal, (cudaStream_t)stream, fp8);
   if (e != cudaSuccess) return fail(std::string("gemm_rs launch: ") + cudaGetErrorString(e));

@@ -42,18 +42,15 @@ struct GemmArgs {
 cudaError_t launch_gemm_tc(int mode, const GemmMaps& maps, const GemmArgs& a, int nctas, int nlocal, cudaStream_t s,
                            bool fp8 = false);
 
-// ---- GEMM on CTA pairs (gemm_tc2.cu): one 256 x 256 tile per cluster of two CTAs, plain GEMM only ----------
-struct Gemm2Maps {
-  CUtensorMap a, b;      // [M, K] and [N, K], boxes of 128 rows x 128 bytes, 128-byte swizzle
-  CUtensorMap sfa, sfb;  // MXFP8: tiled scales as [atoms, 128] u32, box = one 512-byte atom
+// ---- GEMM on CTA pairs (gemm_tc2.cu): one 256 x 256 tile per cluster of two CTAs, same modes and arguments ----
+// GemmMaps for this kernel: boxes of 128 rows x 128 bytes for A and for B (each CTA of a pair loads half of B).
+struct PairSfMaps {
+  CUtensorMap sfa[MT_MAX_RANKS];  // MXFP8: tiled scales of (the gathered) A as [atoms, 128] u32, box = one 512-byte atom
+  CUtensorMap sfb[MT_MAX_RANKS];  // same for B
 };
-struct Gemm2Args {
-  void* c;               // [M, ldc] bf16
-  int32_t M, N, K, ldc;
-  int32_t raster;        // 256-row blocks per group of the tile order (<= 1: row-major)
-  uint64_t timeout_ns;
-};
-cudaError_t launch_gemm_pair(const Gemm2Maps& maps, const Gemm2Args& a, int nclusters, cudaStream_t s, bool fp8);
+cudaError_t launch_gemm_pair(int mode, const GemmMaps& maps, const PairSfMaps& sf, const GemmArgs& a, int nclusters,
+                             int nlocal, cudaStream_t s, bool fp8);
+int gemm_pair_max_clusters(int mode, bool fp8);
 int gemm_pair_error();   // 1 after a wait of the pair kernel expired (synchronises), -1 on a CUDA error
 
 }  // namespace mt

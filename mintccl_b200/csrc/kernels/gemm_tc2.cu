@@ -19,8 +19,13 @@
 // at the closing cluster barrier (so neither exits while the other may still signal into it), TMEM is
 // released and a device-side error word is set for the host.  No load is replicated across the cluster.
 //
-// The reference has no compute kernels (README.md:5 only asks that collectives fuse with others); this is the
-// stand-alone GEMM beside the fused kernels of gemm_tc.cu.
+// Modes (as in gemm_tc.cu): the plain GEMM; all-gather -> GEMM, where extra CTAs of the grid move the peers' rows
+// into local memory and each producer waits for the arrival counter of its own 128 rows; GEMM -> reduce-scatter,
+// where the epilogue stores partial tiles into the row owner's staging area over NVLink and extra CTAs (then
+// all CTAs) reduce this rank's rows.  The comm and reducer CTAs are the ones of gemm_tc.cu
+// (gemm_fused_parts.cuh); they come in whole clusters and never take part in a cluster barrier.
+//
+// The reference has no compute kernels (README.md:5 only asks that collectives fuse with others).
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -30,6 +35,7 @@
 
 #include "../device/prims.cuh"
 #include "../device/tc_prims.cuh"
+#include "gemm_fused_parts.cuh"
 #include "gemm_tc.h"
 #include "launch.h"
 
@@ -58,7 +64,9 @@ struct Ctl {
   uint32_t tmem_base;
   int abort;
 };
-static_assert(sizeof(Ctl) <= CTL_BYTES, "control block");
+static_assert(sizeof(Ctl) <= CTL_BYTES && sizeof(fused::CommCtl) <= CTL_BYTES, "control block");
+static_assert(STAGES * STAGE_BYTES >= fused::COMM_SLOTS * fused::COMM_PIECE, "the comm ring reuses the operand stages");
+static_assert(kThreads == fused::kGemmThreads, "comm and reducer code assumes this block size");
 
 __device__ int g_pair_error;  // set when a wait of this kernel expired (read by mt_gemm_pair_error)
 
@@ -80,26 +88,51 @@ __device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, volatil
 }
 
 struct Tile {
-  int mb, nb;  // 256-row block, 256-column block
+  int mb, nb;     // 256-row block, 256-column block
+  int owner, jb;  // fused modes: rank that owns the rows, 256-row block inside that rank's rows
 };
-// Groups of `raster` row blocks, row block fastest inside a group (keeps a wave's operands in the L2).
-__device__ __forceinline__ Tile tile_of(const Gemm2Args& a, int t) {
+// PLAIN: groups of `raster` row blocks, row block fastest inside a group (keeps a wave's operands in the L2).
+// AG_GEMM: column blocks fastest; row blocks of rank r, r - 1, ... (the order in which the pushes arrive).
+// GEMM_RS: block j of every owner in turn, each rank starting at a different owner (links stay balanced and
+// block j of every owner is complete everywhere after (j + 1) / per of the run, so reducers work alongside).
+template <int MODE>
+__device__ __forceinline__ Tile tile_of(const GemmArgs& a, int lr, int t) {
   const int mbs = a.M / BM2, nbs = a.N / BN;
-  const int G = a.raster > 1 ? a.raster : 1;
-  const int per_group = G * nbs;
-  const int g0 = (t / per_group) * G;
-  const int gsz = (mbs - g0) < G ? (mbs - g0) : G;
-  const int r = t % per_group;
   Tile c;
-  c.mb = g0 + r % gsz;
-  c.nb = r / gsz;
+  if (MODE == MODE_PLAIN) {
+    const int G = a.raster > 1 ? a.raster : 1;
+    const int per_group = G * nbs;
+    const int g0 = (t / per_group) * G;
+    const int gsz = (mbs - g0) < G ? (mbs - g0) : G;
+    const int r = t % per_group;
+    c.mb = g0 + r % gsz;
+    c.nb = r / gsz;
+    c.owner = 0;
+    c.jb = c.mb;
+    return c;
+  }
+  c.nb = t % nbs;
+  const int mi = t / nbs;
+  const int per2 = (a.M / a.nranks) / BM2;
+  int d;
+  if (MODE == MODE_AG_GEMM) {
+    d = mi / per2;
+    c.jb = mi % per2;
+    c.owner = mt_mod(a.rank[lr] - d, a.nranks);
+  } else {
+    c.jb = mi / a.nranks;
+    d = mi % a.nranks;
+    c.owner = mt_mod(a.rank[lr] + 1 + d, a.nranks);
+  }
+  c.mb = c.owner * per2 + c.jb;
   return c;
 }
 
-template <bool FP8>
+template <int MODE, bool FP8>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
-    gemm_pair_kernel(const __grid_constant__ Gemm2Maps maps, Gemm2Args a) {
+    gemm_pair_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ PairSfMaps sfmaps, GemmArgs a) {
   extern __shared__ uint8_t smem_raw[];
+  const int lr = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // the same offsets in both CTAs: the MMA descriptors name shared memory of the pair by offset
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -112,8 +145,19 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
   constexpr uint32_t ACC = FP8 ? 1 : 2;  // accumulator buffers (MXFP8 keeps TMEM columns for the scales)
   const uint32_t cr = cluster_ctarank();
   const bool leader = cr == 0;
-  const int cluster_id = blockIdx.x >> 1, nclusters = gridDim.x >> 1;
+  const int nextra = MODE == MODE_PLAIN ? 0 : a.ncomm;  // AG: data movers, RS: dedicated reducers (whole clusters)
+  const int ngemm = (int)gridDim.x - nextra;
+  const int cluster_id = blockIdx.x >> 1, nclusters = ngemm >> 1;
   const uint64_t timeout_ns = a.timeout_ns;
+
+  if (MODE == MODE_AG_GEMM && (int)blockIdx.x >= ngemm) {
+    fused::ag_comm_cta<FP8>(a, lr, (int)blockIdx.x - ngemm, nextra, smem, (fused::CommCtl*)(sEpi + EPI_BYTES));
+    return;
+  }
+  if (MODE == MODE_GEMM_RS && (int)blockIdx.x >= ngemm) {
+    fused::rs_reduce_loop(a, lr);
+    return;
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -127,8 +171,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     mbar_init(&ctl->drain, 1);
     ctl->abort = 0;
     fence_barrier_init();
-    tma_prefetch_desc(&maps.a);
-    tma_prefetch_desc(&maps.b);
+    tma_prefetch_desc(&maps.a[lr]);
+    tma_prefetch_desc(&maps.b[lr]);
   }
   if (warp == 1) {
     tmem_alloc_pair(&ctl->tmem_base, TMEM_COLS);
@@ -149,9 +193,37 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     if (lane == 0) {
       uint32_t it = 0;
       for (int t = cluster_id; t < tiles && !*abort_flag; t += nclusters) {
-        const Tile tc_ = tile_of(a, t);
-        const int arow = tc_.mb * BM2 + (int)cr * BMC;
+        const Tile tc_ = tile_of<MODE>(a, lr, t);
+        int arow = tc_.mb * BM2 + (int)cr * BMC;
         const int brow = tc_.nb * BN + (int)cr * BNC;
+        const int sfa_row = tc_.mb * 2 + (int)cr;  // 128-row block of A in the (gathered) scale tensor
+        const CUtensorMap* amap = &maps.a[lr];
+        if (MODE == MODE_AG_GEMM) {
+          if (tc_.owner == a.rank[lr]) {
+            amap = &maps.a2[lr];  // own rows come straight from the local shard
+            arow -= tc_.owner * (a.M / a.nranks);
+          } else {
+            // this CTA's 128 rows were pushed by `owner`: wait until its comm CTAs have counted the block in
+            const int per = (a.M / a.nranks) / BMC;
+            const uint64_t* cnt = (const uint64_t*)a.flags_local[lr] + (uint64_t)tc_.owner * per + (tc_.jb * 2 + (int)cr);
+            const uint64_t want = a.epoch * (uint64_t)a.comm_split;
+            uint32_t spins = 0;
+            uint64_t t0 = 0;
+            while (load64_acquire_sys(cnt) < want) {
+              if ((++spins & 0xffu) == 0) {
+                const uint64_t now = globaltimer();
+                if (t0 == 0) t0 = now;
+                else if (now - t0 > timeout_ns || *abort_flag) {
+                  *abort_flag = 1;
+                  fused::gemm_report(a, lr, MT_WHERE_GEMM_FLAG);
+                  break;
+                }
+              }
+            }
+            if (*abort_flag) break;
+            fence_proxy_async_global();  // peer stores (generic proxy) before our TMA reads (async proxy)
+          }
+        }
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
           if (!wait_bar(&ctl->empty[s], ph ^ 1, abort_flag, timeout_ns)) break;
@@ -159,14 +231,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
           if (leader && it >= (uint32_t)STAGES) mbar_arrive_cluster(map_to_cta(smem_u32(&ctl->empty[s]), 1));
           const uint32_t full0 = map_to_cta(smem_u32(&ctl->full[s]), 0);
           if (leader) mbar_expect_tx(&ctl->full[s], 2 * (STAGE_BYTES + (FP8 ? SF_STAGE_BYTES : 0)));
-          tma_load_2d_pair(sA + s * A_BYTES, &maps.a, kb * BKE, arow, full0);
-          tma_load_2d_pair(sB + s * B_BYTES, &maps.b, kb * BKE, brow, full0);
+          tma_load_2d_pair(sA + s * A_BYTES, amap, kb * BKE, arow, full0);
+          tma_load_2d_pair(sB + s * B_BYTES, &maps.b[lr], kb * BKE, brow, full0);
           if (FP8) {
             // scale atoms are rows of a [atoms, 128 x u32] tensor: atom (row block of 128, K block of 128)
             uint8_t* sf = sSF + s * SF_STAGE_BYTES;
-            tma_load_2d_pair(sf, &maps.sfa, 0, (tc_.mb * 2 + (int)cr) * kblocks + kb, full0);
-            tma_load_2d_pair(sf + 512, &maps.sfb, 0, (tc_.nb * 2) * kblocks + kb, full0);
-            tma_load_2d_pair(sf + 1024, &maps.sfb, 0, (tc_.nb * 2 + 1) * kblocks + kb, full0);
+            tma_load_2d_pair(sf, &sfmaps.sfa[lr], 0, sfa_row * kblocks + kb, full0);
+            tma_load_2d_pair(sf + 512, &sfmaps.sfb[lr], 0, (tc_.nb * 2) * kblocks + kb, full0);
+            tma_load_2d_pair(sf + 1024, &sfmaps.sfb[lr], 0, (tc_.nb * 2 + 1) * kblocks + kb, full0);
           }
         }
       }
@@ -225,7 +297,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     // ------------------------------------------------------------ epilogue warps (2..5, both CTAs)
     const int q = warp & 3;  // TMEM lane quarter this warp may access
     uint8_t* stg = sEpi + (warp - 2) * 32 * EPI_PITCH;
-    const uint64_t ld_bytes = (uint64_t)a.ldc * 2;
     uint32_t tile_i = 0;
     for (int t = cluster_id; t < tiles; t += nclusters, ++tile_i) {
       const uint32_t as = tile_i % ACC, aph = (tile_i / ACC) & 1;
@@ -233,8 +304,25 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
       // the commit lands on the leader's barrier only: its first epilogue warp passes it on to the peer
       if (leader && warp == 2 && lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&ctl->acc_full[as]), 1));
       tc_fence_after();
-      const Tile tc_ = tile_of(a, t);
-      uint8_t* dst = (uint8_t*)a.c + (uint64_t)(tc_.mb * BM2 + (int)cr * BMC + q * 32) * ld_bytes + (uint64_t)tc_.nb * BN * 2;
+      const Tile tc_ = tile_of<MODE>(a, lr, t);
+      // destination of this CTA's 128 rows of the tile
+      uint8_t* dst;
+      uint64_t ld_bytes;
+      uint64_t* rs_cnt = nullptr;
+      if (MODE == MODE_GEMM_RS) {
+        // partial tile -> staging[my rank] of the owner (peer memory unless the owner is this rank), tile-major:
+        // [source rank][128-row block][column block][128 x 256], one contiguous 64 KiB region per CTA and tile
+        const MtDevComm& c = a.comms[lr];
+        const int per = (a.M / a.nranks) / BMC;
+        const uint64_t slot = ((uint64_t)a.rank[lr] * per + (tc_.jb * 2 + (int)cr)) * (a.N / BN) + tc_.nb;
+        ld_bytes = (uint64_t)BN * 2;
+        dst = c.heap[tc_.owner] + a.stage_off + slot * (uint64_t)(BMC * BN * 2);
+        rs_cnt = (uint64_t*)(c.heap[tc_.owner] + a.flags_off) + slot;
+      } else {
+        ld_bytes = (uint64_t)a.ldc * 2;
+        dst = (uint8_t*)a.c[lr] + (uint64_t)(tc_.mb * BM2 + (int)cr * BMC) * ld_bytes + (uint64_t)tc_.nb * BN * 2;
+      }
+      dst += (uint64_t)(q * 32) * ld_bytes;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + as * BN;
       const uint32_t acc_empty0 = map_to_cta(smem_u32(&ctl->acc_empty[as]), 0);
       // 4 rows per pass of 8 lanes x 16 bytes: full 128-byte lines
@@ -243,7 +331,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         for (int p = 0; p < 8; ++p) {
           const int rr = p * 4 + (lane >> 3), c16 = lane & 7;
           const uint4 v = *(const uint4*)(stg + rr * EPI_PITCH + c16 * 16);
-          *(uint4*)(dst + (uint64_t)rr * ld_bytes + cb * 128 + c16 * 16) = v;
+          uint8_t* g = dst + (uint64_t)rr * ld_bytes + cb * 128 + c16 * 16;
+          if (MODE == MODE_GEMM_RS) {
+            u128 w;
+            w.x = (uint64_t)v.x | ((uint64_t)v.y << 32);
+            w.y = (uint64_t)v.z | ((uint64_t)v.w << 32);
+            store128_relaxed_sys(g, w);
+          } else {
+            *(uint4*)g = v;
+          }
         }
       };
       if constexpr (FP8) {
@@ -309,6 +405,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(acc_empty0);
       }
+      if (MODE == MODE_GEMM_RS) {
+        // count this warp's quarter of the partial tile on the owner (release: the stores above come first)
+        __syncwarp();
+        if (lane == 0) asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(rs_cnt), "l"(1ull) : "memory");
+      }
     }
   }
 
@@ -319,22 +420,42 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     // tell the peer (it would notice by itself after its own time limit) and the host
     st_cluster_u32(map_to_cta(smem_u32(&ctl->abort), cr ^ 1), 1u);
     atomicExch(&g_pair_error, 1);
+    if (MODE != MODE_PLAIN) fused::gemm_report(a, lr, MT_WHERE_GEMM_FLAG);
   }
   cluster_sync_all();  // neither CTA leaves, or frees TMEM, while the other may still signal into it
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc_pair(tmem_base, TMEM_COLS);
   }
+  // ---------------------------------------------------------------- reducer phase of GEMM -> reduce-scatter
+  if (MODE == MODE_GEMM_RS) {
+    if (*abort_flag) return;
+    fused::rs_reduce_loop(a, lr);
+  }
 }
 
 }  // namespace pair
 
+static const void* pair_fn(int mode, bool fp8) {
+  switch (mode * 2 + (fp8 ? 1 : 0)) {
+    case MODE_PLAIN * 2: return (const void*)pair::gemm_pair_kernel<MODE_PLAIN, false>;
+    case MODE_PLAIN * 2 + 1: return (const void*)pair::gemm_pair_kernel<MODE_PLAIN, true>;
+    case MODE_AG_GEMM * 2: return (const void*)pair::gemm_pair_kernel<MODE_AG_GEMM, false>;
+    case MODE_AG_GEMM * 2 + 1: return (const void*)pair::gemm_pair_kernel<MODE_AG_GEMM, true>;
+    case MODE_GEMM_RS * 2: return (const void*)pair::gemm_pair_kernel<MODE_GEMM_RS, false>;
+    case MODE_GEMM_RS * 2 + 1: return (const void*)pair::gemm_pair_kernel<MODE_GEMM_RS, true>;
+    default: return nullptr;
+  }
+}
+
 // Clusters of this kernel that the device can hold at once.  The kernel is persistent (cluster i takes tiles
 // i, i + n, ...), so a grid with more clusters than fit would run its tail after the rest has finished.
-int gemm_pair_max_clusters(bool fp8) {
-  static int cached[2] = {0, 0};
-  if (cached[fp8] > 0) return cached[fp8];
-  const void* fn = fp8 ? (const void*)pair::gemm_pair_kernel<true> : (const void*)pair::gemm_pair_kernel<false>;
+int gemm_pair_max_clusters(int mode, bool fp8) {
+  static int cached[6] = {0, 0, 0, 0, 0, 0};
+  const void* fn = pair_fn(mode, fp8);
+  if (!fn) return 0;
+  int& slot = cached[mode * 2 + (fp8 ? 1 : 0)];
+  if (slot > 0) return slot;
   if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, pair::SMEM_BYTES) != cudaSuccess) return 0;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
@@ -357,22 +478,44 @@ int gemm_pair_max_clusters(bool fp8) {
     n = sms / 2;
   }
   if (const char* e = getenv("MINTCCL_DEBUG")) {
-    if (atoi(e) > 0) fprintf(stderr, "[mintccl] pair GEMM (%s): %d clusters of 2 CTAs fit on %d SMs\n", fp8 ? "mxfp8" : "bf16", n, sms);
+    if (atoi(e) > 0)
+      fprintf(stderr, "[mintccl] pair GEMM (mode %d, %s): %d clusters of 2 CTAs fit on %d SMs\n", mode, fp8 ? "mxfp8" : "bf16", n, sms);
   }
-  cached[fp8] = n;
+  slot = n;
   return n;
 }
 
-cudaError_t launch_gemm_pair(const Gemm2Maps& maps, const Gemm2Args& a, int nclusters, cudaStream_t s, bool fp8) {
-  const void* fn = fp8 ? (const void*)pair::gemm_pair_kernel<true> : (const void*)pair::gemm_pair_kernel<false>;
-  const int fit = gemm_pair_max_clusters(fp8);  // also sets the shared-memory attribute once
+// Grid: 2 * nclusters GEMM CTAs followed by a.ncomm comm / reducer CTAs (even), times nlocal emulated ranks.
+cudaError_t launch_gemm_pair(int mode, const GemmMaps& maps, const PairSfMaps& sf, const GemmArgs& a, int nclusters,
+                             int nlocal, cudaStream_t s, bool fp8) {
+  const void* fn = pair_fn(mode, fp8);
+  if (!fn) return cudaErrorInvalidValue;
+  const int fit = gemm_pair_max_clusters(mode, fp8);  // also sets the shared-memory attribute once
   if (fit <= 0) return cudaErrorInvalidValue;
-  if (nclusters > fit) nclusters = fit;
-  Gemm2Maps m = maps;
-  Gemm2Args args = a;
-  void* p[] = {(void*)&m, (void*)&args};
+  const int extra = mode == MODE_PLAIN ? 0 : a.ncomm;
+  if (extra & 1) return cudaErrorInvalidValue;
+  if ((nclusters + extra / 2) * nlocal > fit) nclusters = fit / nlocal - extra / 2;
+  if (nclusters < 1) return cudaErrorInvalidValue;
+  GemmMaps m = maps;
+  PairSfMaps sm = sf;
+  GemmArgs args = a;
+  void* p[] = {(void*)&m, (void*)&sm, (void*)&args};
   count_launch();
-  return cudaLaunchKernel(fn, dim3(2 * nclusters), dim3(pair::kThreads), p, pair::SMEM_BYTES, s);
+  const dim3 grid(2 * nclusters + extra, nlocal);
+  if (nlocal == 1) return cudaLaunchKernel(fn, grid, dim3(pair::kThreads), p, pair::SMEM_BYTES, s);
+  // emulated ranks wait on each other inside one grid: every CTA has to be resident
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(pair::kThreads);
+  cfg.dynamicSmemBytes = pair::SMEM_BYTES;
+  cfg.stream = s;
+  cudaLaunchAttribute at;
+  at.id = cudaLaunchAttributeCooperative;
+  at.val.cooperative = 1;
+  cfg.attrs = &at;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelExC(&cfg, fn, p);
 }
 
 int gemm_pair_error() {

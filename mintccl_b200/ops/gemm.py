@@ -74,7 +74,9 @@ class AllGatherGemm(_Fused):
         self.mode = self.MODES[mode]
         self.fp8 = fp8
         if ncomm is None:
-            ncomm = self.pick_ncomm((M // BM) * (N_ // BN))
+            nw = comm.world_size
+            ncomm = self.pick_ncomm((M // BM) * (N_ // BN), flops=2.0 * M * N_ * K,
+                                    bytes_in=(nw - 1) / max(nw, 1) * M * K * (1 if fp8 else 2), fp8=fp8)
         self.split = max(1, min(split, ncomm))
         n = comm.world_size
         if M % (BM * n) or N_ % BN or K % BK:
@@ -90,10 +92,11 @@ class AllGatherGemm(_Fused):
         comm.control.barrier()
 
     def call_mxfp8(self, a_data: TensorOrList, a_scale: TensorOrList, w_data: TensorOrList, w_scale: TensorOrList,
-                   out: Optional[TensorOrList] = None, nctas: int = 0):
+                   out: Optional[TensorOrList] = None, nctas: int = 0, w_scale_tiled: bool = False):
         """MXFP8 operands: ``a_data`` uint8 ``[M / n, K]`` (e4m3) with row-major scales ``[M / n, K / 32]``, ``w_data``
-        ``[N, K]`` with scales ``[N, K / 32]``; bf16 result.  The payload rows are gathered inside the fused kernel,
-        the (32 x smaller) scales by an all-gather of this library just before it."""
+        ``[N, K]`` with scales ``[N, K / 32]`` (or already in the layout of ``ops.mxfp8.tile_scales`` with
+        ``w_scale_tiled``: weights are tiled once); bf16 result.  The payload rows are gathered inside the fused
+        kernel, the (32 x smaller) scales by an all-gather of this library just before it."""
         from . import mxfp8 as mx
         if not self.fp8:
             raise ValueError("create the plan with fp8=True")
@@ -106,7 +109,7 @@ class AllGatherGemm(_Fused):
         for lr, r in enumerate(ranks):
             sfa_all[lr][r].copy_(mx.tile_scales(a_sc[lr]))
         c.allgather(self.sfa_all)
-        sfb = [mx.tile_scales(t) for t in w_sc]
+        sfb = list(w_sc) if w_scale_tiled else [mx.tile_scales(t) for t in w_sc]
         self.epoch += 1
         rc = c.lib.mt_ag_gemm_mxfp8(c._handle, c._stream(), N.ptr_array([t.data_ptr() for t in a_s]),
                                     N.ptr_array([t.data_ptr() for t in sfa_all]), N.ptr_array([t.data_ptr() for t in ws]),
@@ -119,9 +122,19 @@ class AllGatherGemm(_Fused):
         return outs if c.emulated else outs[0]
 
     @staticmethod
-    def pick_ncomm(tiles: int, sms: int = 148, lo: int = 16, hi: int = 24) -> int:
-        """Comm CTAs for a problem of ``tiles`` output tiles: the GEMM takes ceil(tiles / (sms - ncomm)) waves,
-        so take the most comm CTAs (faster transfer) that do not add a wave over the fewest allowed."""
+    def pick_ncomm(tiles: int, sms: int = 148, lo: int = 16, hi: int = 24, flops: Optional[float] = None,
+                   bytes_in: Optional[float] = None, fp8: bool = False) -> int:
+        """Comm CTAs for a problem of ``tiles`` output tiles.  The transfer has to keep pace with the GEMM and no
+        more: one comm CTA moves about 28 GB/s (24 of them 680 GB/s on 8 GPUs), the GEMM CTAs sustain about
+        1.3 PFLOP/s in bf16 and 2.2 in MXFP8, so ``bytes_in / (flops / rate) / 28e9`` CTAs (plus a quarter) are
+        wanted, at most ``hi``; a GEMM-bound problem (few ranks, wide N) gets few and keeps its SMs.  Among the
+        allowed counts the GEMM takes ceil(tiles / (sms - ncomm)) waves: take the most comm CTAs that do not add
+        a wave over the fewest allowed."""
+        if flops and bytes_in is not None:
+            t = flops / (2.2e15 if fp8 else 1.3e15)
+            want = int(bytes_in / t / 28e9 * 1.25) + 1
+            hi = max(2, min(hi, want))
+            lo = max(2, min(lo, hi - 2))
         waves = lambda nc: -(-tiles // (sms - nc))  # noqa: E731
         best = min(waves(nc) for nc in range(lo, hi + 1))
         return max(nc for nc in range(lo, hi + 1) if waves(nc) == best)
@@ -157,17 +170,28 @@ class GemmReduceScatter(_Fused):
     """Plan for ``reduce_scatter(a[M, K_local] @ w[N, K_local].T)`` over token rows: owns the staging area
     for partial tiles and their arrival counters in the symmetric heap."""
 
-    def __init__(self, comm, M: int, N_: int, K: int, nred: int = 12):
+    def __init__(self, comm, M: int, N_: int, K: int, nred: Optional[int] = None):
         super().__init__(comm)
         n = comm.world_size
         if M % (BM * n) or N_ % BN or K % BK:
             raise ValueError("M must be a multiple of 128 x world, N of 256, K of 64")
         self.M, self.N, self.K = M, N_, K
+        if nred is None:
+            nred = self.pick_nred(M, N_, K, n)
         self.nred = nred if n > 1 else 0
         self.stage = comm.symm_empty((n, M // n, N_), torch.bfloat16)
         self.flags = comm.symm_zeros((n * (M // n // BM) * (N_ // BN) + 2,), torch.int64)
         torch.cuda.synchronize()
         comm.control.barrier()
+
+    @staticmethod
+    def pick_nred(M: int, N_: int, K: int, n: int) -> int:
+        """Dedicated reducer CTAs: they read n partial tiles and write one for every output tile of this rank while
+        the GEMM runs, about 70 GB/s per CTA (12 CTAs keep up with the 8-rank Llama-3-8B down projection:
+        75 MB in 92 us).  A longer GEMM over the same bytes needs fewer, which leaves the SMs to the GEMM."""
+        t = 2.0 * M * N_ * K / 1.3e15
+        bytes_red = (M // n) * N_ * 2.0 * (n + 1)
+        return max(2, min(16, int(bytes_red / t / 70e9 + 0.999)))
 
     def __call__(self, a: TensorOrList, w: TensorOrList, out: Optional[TensorOrList] = None, nctas: int = 0):
         c = self.comm
@@ -191,16 +215,17 @@ class GemmReduceScatter(_Fused):
         return outs if c.emulated else outs[0]
 
     def call_mxfp8(self, a_data: TensorOrList, a_scale: TensorOrList, w_data: TensorOrList, w_scale: TensorOrList,
-                   out: Optional[TensorOrList] = None, nctas: int = 0):
-        """MXFP8 operands (e4m3 payloads, row-major ue8m0 scales per 32 elements along K); bf16 partial tiles and
-        result, fp32 accumulation in the tensor core and in the cross-rank sum."""
+                   out: Optional[TensorOrList] = None, nctas: int = 0, w_scale_tiled: bool = False):
+        """MXFP8 operands (e4m3 payloads, row-major ue8m0 scales per 32 elements along K; ``w_scale_tiled``: the
+        weight scales are already in the layout of ``ops.mxfp8.tile_scales``); bf16 partial tiles and result,
+        fp32 accumulation in the tensor core and in the cross-rank sum."""
         from . import mxfp8 as mx
         c = self.comm
         a_s, ws = self._lists(a_data), self._lists(w_data)
         rows = self.M // c.world_size
         outs = self._lists(out) if out is not None else [torch.empty(rows, self.N, device=a_s[0].device, dtype=torch.bfloat16) for _ in a_s]
         sfa = [mx.tile_scales(t) for t in self._lists(a_scale)]
-        sfb = [mx.tile_scales(t) for t in self._lists(w_scale)]
+        sfb = list(self._lists(w_scale)) if w_scale_tiled else [mx.tile_scales(t) for t in self._lists(w_scale)]
         self.epoch += 1
         rc = c.lib.mt_gemm_rs_mxfp8(c._handle, c._stream(), N.ptr_array([t.data_ptr() for t in a_s]),
                                     N.ptr_array([t.data_ptr() for t in sfa]), N.ptr_array([t.data_ptr() for t in ws]),
