@@ -140,3 +140,22 @@ def test_timer_host(capsys):
     with m.Timer(quiet=True):
         pass
     assert capsys.readouterr().out == ""
+
+
+def test_fused_plan_cta_counts_follow_the_gemm_to_transfer_ratio():
+    """Comm CTAs of all-gather -> GEMM and reducer CTAs of GEMM -> reduce-scatter: as many as keep pace with the
+    GEMM, the rest computes (Llama-3-8B MLP, tokens 8192, hidden 4096, ffn 14336 split over the ranks)."""
+    from mintccl_b200.ops.gemm import AllGatherGemm, GemmReduceScatter
+    T, H = 8192, 4096
+    picks = {}
+    for n, F in ((8, 1792), (4, 3584), (2, 7168)):
+        tiles = (T // 128) * (F // 256)
+        picks[n] = (AllGatherGemm.pick_ncomm(tiles, flops=2.0 * T * F * H, bytes_in=(n - 1) / n * T * H * 2),
+                    GemmReduceScatter.pick_nred(T, H, F, n))
+    assert picks[8] == (24, 12)           # the counts tuned on 8 GPUs
+    assert picks[2][0] <= 6 and picks[2][1] <= 4   # GEMM-bound: nearly all SMs compute
+    assert picks[8][0] >= picks[4][0] >= picks[2][0] and picks[8][1] >= picks[4][1] >= picks[2][1]
+    # without the sizes: the widest transfer that does not add a GEMM wave
+    assert AllGatherGemm.pick_ncomm(448) == 24
+    # MXFP8 halves the bytes and nearly doubles the GEMM rate: never more comm CTAs than bf16
+    assert AllGatherGemm.pick_ncomm(448, flops=2.0 * T * 1792 * H, bytes_in=7 / 8 * T * H, fp8=True) <= 24
