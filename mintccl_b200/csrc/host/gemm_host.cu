@@ -300,7 +300,10 @@ int mt_ag_gemm_mxfp8(MtComm* c, void* stream, const void* const* a_shard, const 
 }
 
 // out[M / ranks, N] = reduce_scatter over rows of (A[M, K] * B[N, K]^T), K being this rank's slice of the
-// contraction.  `stage_off`: symmetric buffer of ranks * (M / ranks) * N bf16 partial tiles;
+// contraction.  `stage_off`: symmetric buffer of 2 * ranks * (M / ranks) * N bf16 partial tiles.  Calls alternate
+// between its halves (by the parity of `epoch`): a rank that has finished call e may already write partial tiles
+// of call e + 1 into a peer whose reducers still read those of call e; it cannot reach call e + 2 before that
+// peer has finished call e, because call e + 1 needs the peer's partial tiles of call e + 1.
 // `flags_off`: symmetric u64 counters [ranks][M / ranks / 128][N / 256] followed by two ticket words, all zero
 // before the first call.  `nred`: CTAs that only reduce (the others join them when their tiles are done).
 static int gemm_rs_impl(MtComm* c, void* stream, const void* const* A, const void* const* B, void* const* out,
@@ -314,7 +317,7 @@ static int gemm_rs_impl(MtComm* c, void* stream, const void* const* A, const voi
   if (nred < 0 || nred >= grid) return fail("nred out of range");
   a.ncomm = nred;
   a.ldc = N;
-  a.stage_off = stage_off;
+  a.stage_off = stage_off + (epoch & 1) * (uint64_t)M * N * 2;
   mt::GemmMaps maps;
   memset(&maps, 0, sizeof(maps));
   for (int lr = 0; lr < c->nlocal; ++lr) {

@@ -115,6 +115,12 @@ int mt_mxfp8_reduce(MtComm* c, void* stream, int op, uint64_t data_in_off, uint6
 // ---- device-wait self test: a wait nothing satisfies must time out and report, not hang -----------
 int mt_test_wait_timeout(MtComm* c, void* stream);
 
+// ---- host model of the fused GEMM + collective protocols (threads and atomics, no GPU; sim/sim_fused.cpp) ----
+// op: 0 all-gather -> GEMM, 1 GEMM -> reduce-scatter.  Returns 0 ok, 1 data of another call was read, 2 a wait gave
+// up, -1 bad argument.
+int mt_sim_fused(int op, int nranks, int per, int nbs, int ngemm, int nextra, int pair, int iters, uint32_t seed,
+                 int dead_rank, int slow_rank, int double_buffer, uint64_t timeout_ms);
+
 // ---- topology ---------------------------------------------------------------------------------------
 // bw: n*n row-major matrix of link bandwidth (0 = no link).  Results are written to `out`.
 int mt_find_ring(const double* bw, int n, int* out);                          // returns length (n+1) or 0

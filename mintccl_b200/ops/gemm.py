@@ -168,7 +168,7 @@ class AllGatherGemm(_Fused):
 
 class GemmReduceScatter(_Fused):
     """Plan for ``reduce_scatter(a[M, K_local] @ w[N, K_local].T)`` over token rows: owns the staging area
-    for partial tiles and their arrival counters in the symmetric heap."""
+    for partial tiles (double-buffered across calls) and their arrival counters in the symmetric heap."""
 
     def __init__(self, comm, M: int, N_: int, K: int, nred: Optional[int] = None):
         super().__init__(comm)
@@ -179,7 +179,9 @@ class GemmReduceScatter(_Fused):
         if nred is None:
             nred = self.pick_nred(M, N_, K, n)
         self.nred = nred if n > 1 else 0
-        self.stage = comm.symm_empty((n, M // n, N_), torch.bfloat16)
+        # two halves used alternately: a fast peer may already write the next call's partial tiles while this
+        # rank still reduces the current ones
+        self.stage = comm.symm_empty((2, n, M // n, N_), torch.bfloat16)
         self.flags = comm.symm_zeros((n * (M // n // BM) * (N_ // BN) + 2,), torch.int64)
         torch.cuda.synchronize()
         comm.control.barrier()

@@ -154,3 +154,40 @@ def test_fd_passing_between_processes():
     p.join(20)
     lib.mt_fd_close(sock)
     assert lib.mt_fd_accept(sock, C.byref(tag), 10) < 0  # closed socket: clean failure, no hang
+
+
+# ---- fused GEMM + collective protocols (host model: threads for CTAs, stamps for data) ----------------------
+def _fused(op, n, per, nbs, ngemm, nextra, pair, iters, seed=1, dead=-1, slow=-1, double_buffer=1, timeout_ms=4000):
+    from mintccl_b200 import _native as N
+    return N.lib().mt_sim_fused(op, n, per, nbs, ngemm, nextra, pair, iters, seed, dead, slow, double_buffer, timeout_ms)
+
+
+@pytest.mark.parametrize("n", [2, 4, 8])
+@pytest.mark.parametrize("pair", [0, 1])
+def test_fused_allgather_gemm_protocol_many_calls(n, pair):
+    """Arrival counters that only grow, the comm CTAs' entry barrier and both tile sizes: 150 back-to-back calls,
+    every block read by a GEMM CTA must carry the stamp of the current call."""
+    assert _fused(0, n, 4, 2, 3, 2, pair, 150, seed=n) == 0
+    assert _fused(0, n, 4, 2, 3, 2, pair, 20, seed=n, slow=0) == 0   # one rank's GEMM far behind the others
+
+
+@pytest.mark.parametrize("n", [2, 4, 8])
+@pytest.mark.parametrize("pair", [0, 1])
+def test_fused_gemm_reducescatter_protocol_many_calls(n, pair):
+    """Partial-tile counters, ticketed reducers with two alternating ticket words, two alternating staging halves:
+    every tile of every call reduced exactly once from partial tiles of that call."""
+    assert _fused(1, n, 4, 3, 3, 2, pair, 150, seed=n) == 0
+    assert _fused(1, n, 4, 3, 3, 0, pair, 50, seed=n) == 0           # no dedicated reducers: GEMM CTAs reduce at the end
+    assert _fused(1, n, 4, 3, 3, 2, pair, 20, seed=n, slow=0) == 0   # one rank's reducers far behind
+
+
+def test_fused_gemm_reducescatter_single_staging_buffer_is_a_race():
+    """Why the staging area has two halves: with one, a rank that has finished call e overwrites, in call e + 1,
+    partial tiles that a slower peer has not reduced yet.  The model reports the foreign stamp."""
+    assert _fused(1, 4, 4, 3, 3, 2, 0, 20, seed=3, slow=0, double_buffer=0) == 1
+
+
+def test_fused_protocols_dead_rank_times_out():
+    """A rank that never starts: the others give up after their time limit instead of spinning forever."""
+    assert _fused(0, 4, 4, 2, 3, 2, 0, 3, dead=2, timeout_ms=300) == 2
+    assert _fused(1, 4, 4, 3, 3, 2, 1, 3, dead=1, timeout_ms=300) == 2
