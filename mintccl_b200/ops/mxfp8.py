@@ -58,10 +58,29 @@ def _off(comm, ts, what):
     return offs[0]
 
 
+def _cpu_reduce(comm, data: torch.Tensor, scale: torch.Tensor, out_data: torch.Tensor, out_scale: torch.Tensor,
+                scatter: bool) -> None:
+    """The same sum on the CPU reference backend (gloo): dequantise, add in fp32 across the ranks, quantise once."""
+    if scale.numel() * BLOCK != data.numel():
+        raise ValueError("one scale byte per 32 payload bytes")
+    total = comm._sum_fp32(dequantize_mxfp8(data.reshape(-1), scale.reshape(-1)))
+    if scatter:
+        per = total.numel() // comm.world_size
+        if per % BLOCK or per * comm.world_size != total.numel():
+            raise ValueError("the blocks must divide evenly over the ranks")
+        total = total[comm.rank * per:(comm.rank + 1) * per]
+    q, sc = quantize_mxfp8(total)
+    out_data.reshape(-1).copy_(q)
+    out_scale.reshape(-1).copy_(sc)
+
+
 def allreduce_mxfp8(comm, data: TensorOrList, scale: TensorOrList, out_data: Optional[TensorOrList] = None,
                     out_scale: Optional[TensorOrList] = None, nctas: int = 64) -> None:
     """Sum the MXFP8 tensors of all ranks; the result (requantised once) replaces ``data`` / ``scale`` on every
     rank, or goes to ``out_data`` / ``out_scale``.  All tensors must be symmetric uint8 tensors."""
+    if not hasattr(comm, "lib"):
+        return _cpu_reduce(comm, data, scale, out_data if out_data is not None else data,
+                           out_scale if out_scale is not None else scale, scatter=False)
     d, s = _lists(comm, data), _lists(comm, scale)
     od = _lists(comm, out_data) if out_data is not None else d
     os_ = _lists(comm, out_scale) if out_scale is not None else s
@@ -77,6 +96,8 @@ def allreduce_mxfp8(comm, data: TensorOrList, scale: TensorOrList, out_data: Opt
 def reducescatter_mxfp8(comm, data: TensorOrList, scale: TensorOrList, out_data: TensorOrList, out_scale: TensorOrList,
                         nctas: int = 64) -> None:
     """Shard ``rank`` (a contiguous 1/world of the blocks) of the sum lands in the local ``out_data`` / ``out_scale``."""
+    if not hasattr(comm, "lib"):
+        return _cpu_reduce(comm, data, scale, out_data, out_scale, scatter=True)
     d, s = _lists(comm, data), _lists(comm, scale)
     od, os_ = _lists(comm, out_data), _lists(comm, out_scale)
     n_el = d[0].numel()

@@ -59,6 +59,19 @@ def _worker(rank, world, init_file, result_q):
         # a mismatched send/recv pair is rejected on the host before anything is launched
         comm = m.get_comm(buf)
         assert comm.world_size == world and comm.rank == rank
+        # block-scaled fp8 sums: fp32 accumulation over the dequantised inputs, one requantisation
+        from mintccl_b200.ops import mxfp8 as mx
+        xs = [torch.randn(n * 256, generator=torch.Generator().manual_seed(40 + r)) * (r + 1) for r in range(n)]
+        qs = [mx.quantize_mxfp8(t) for t in xs]
+        total = sum(mx.dequantize_mxfp8(d_, s_) for d_, s_ in qs)
+        want_d, want_s = mx.quantize_mxfp8(total)
+        d_, s_ = qs[rank][0].clone(), qs[rank][1].clone()
+        mx.allreduce_mxfp8(comm, d_, s_)
+        assert torch.equal(d_, want_d) and torch.equal(s_, want_s)
+        od, os_ = torch.empty(256, dtype=torch.uint8), torch.empty(8, dtype=torch.uint8)
+        mx.reducescatter_mxfp8(comm, qs[rank][0], qs[rank][1], od, os_)
+        wd, ws = mx.quantize_mxfp8(total[rank * 256:(rank + 1) * 256])
+        assert torch.equal(od, wd) and torch.equal(os_, ws)
         result_q.put((rank, "ok"))
     except Exception as e:  # noqa: BLE001
         result_q.put((rank, f"{type(e).__name__}: {e}"))
