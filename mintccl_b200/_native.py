@@ -112,6 +112,7 @@ def lib():
     sig("mt_gemm", i32, vp, vp, vp, vp, i32, i32, i32, i32, i32)
     sig("mt_gemm_mxfp8", i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32)
     sig("mt_sim_fused", i32, i32, i32, i32, i32, i32, i32, i32, i32, C.c_uint32, i32, i32, i32, u64)
+    sig("mt_sched_fused_tile", None, i32, i32, i32, i32, i32, i32, i32, i32, i32, ip)
     sig("mt_gemm_pair_error", i32)
     sig("mt_gemm_set_pair", None, i32)
     sig("mt_ag_gemm", i32, vp, vp, pp, pp, pp, u64, u64, u64, i32, i32, i32, i32, i32, i32, i32, u64, i32)

@@ -27,6 +27,7 @@
 #include "../device/prims.cuh"
 #include "../device/sched.h"
 #include "../device/tc_prims.cuh"
+#include "fused_schedule.h"
 #include "gemm_fused_parts.cuh"
 #include "gemm_tc.h"
 #include "launch.h"
@@ -52,49 +53,18 @@ struct SharedCtl {
   int abort;
 };
 
-// Tile order.  PLAIN: row-major over (m block, n block).  AG_GEMM: row blocks of rank r, r-1, r-2, ...
-// (arrival order of the pushes).  GEMM_RS: see below.
+// Tile order: fused_schedule.h (shared with the CTA-pair kernel and the host model).
 struct TileCoord {
   int mb, nb, owner;
 };
 template <int MODE>
 __device__ __forceinline__ TileCoord tile_coord(const GemmArgs& a, int lr, int t) {
-  const int nbs = a.N / BN;
+  static_assert(MODE_PLAIN == MT_TILE_PLAIN && MODE_AG_GEMM == MT_TILE_AG_GEMM && MODE_GEMM_RS == MT_TILE_GEMM_RS, "mode codes");
+  const MtTile m = mt_fused_tile(MODE, t, a.M, a.N, a.nranks, a.rank[lr], a.raster, BM, BN);
   TileCoord c;
-  if (MODE == MODE_PLAIN) {
-    // Groups of a.raster row blocks, row block fastest inside a group: the tiles in flight at any time
-    // (one per CTA, consecutive t) then span about as many rows of A as of B, which keeps the operands of
-    // a wave, and of the next wave, inside the L2 for large problems.
-    const int mbs = a.M / BM;
-    const int G = a.raster > 1 ? a.raster : 1;
-    const int per_group = G * nbs;
-    const int g0 = (t / per_group) * G;
-    const int gsz = (mbs - g0) < G ? (mbs - g0) : G;
-    const int r = t % per_group;
-    c.mb = g0 + r % gsz;
-    c.nb = r / gsz;
-    c.owner = 0;
-    return c;
-  }
-  c.nb = t % nbs;
-  int mi = t / nbs;
-  {
-    const int per = (a.M / a.nranks) / BM;  // row blocks per rank
-    int d, j;
-    if (MODE == MODE_AG_GEMM) {
-      d = mi / per;
-      j = mi % per;
-      c.owner = mt_mod(a.rank[lr] - d, a.nranks);
-    } else {
-      // every rank walks the row blocks j = 0, 1, ... of all owners in step, each starting at a
-      // different owner: the links stay balanced and block j of every owner is complete everywhere
-      // after (j + 1) / per of the run, so the reducers work alongside the GEMM instead of after it
-      j = mi / a.nranks;
-      d = mi % a.nranks;
-      c.owner = mt_mod(a.rank[lr] + 1 + d, a.nranks);
-    }
-    c.mb = c.owner * per + j;
-  }
+  c.mb = m.mb;
+  c.nb = m.nb;
+  c.owner = m.owner;
   return c;
 }
 

@@ -35,6 +35,7 @@
 
 #include "../device/prims.cuh"
 #include "../device/tc_prims.cuh"
+#include "fused_schedule.h"
 #include "gemm_fused_parts.cuh"
 #include "gemm_tc.h"
 #include "launch.h"
@@ -87,45 +88,12 @@ __device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, volatil
   return true;
 }
 
-struct Tile {
-  int mb, nb;     // 256-row block, 256-column block
-  int owner, jb;  // fused modes: rank that owns the rows, 256-row block inside that rank's rows
-};
-// PLAIN: groups of `raster` row blocks, row block fastest inside a group (keeps a wave's operands in the L2).
-// AG_GEMM: column blocks fastest; row blocks of rank r, r - 1, ... (the order in which the pushes arrive).
-// GEMM_RS: block j of every owner in turn, each rank starting at a different owner (links stay balanced and
-// block j of every owner is complete everywhere after (j + 1) / per of the run, so reducers work alongside).
+// Tile order: fused_schedule.h with 256-row tiles (mb, jb count 256-row blocks).
+using Tile = MtTile;
 template <int MODE>
 __device__ __forceinline__ Tile tile_of(const GemmArgs& a, int lr, int t) {
-  const int mbs = a.M / BM2, nbs = a.N / BN;
-  Tile c;
-  if (MODE == MODE_PLAIN) {
-    const int G = a.raster > 1 ? a.raster : 1;
-    const int per_group = G * nbs;
-    const int g0 = (t / per_group) * G;
-    const int gsz = (mbs - g0) < G ? (mbs - g0) : G;
-    const int r = t % per_group;
-    c.mb = g0 + r % gsz;
-    c.nb = r / gsz;
-    c.owner = 0;
-    c.jb = c.mb;
-    return c;
-  }
-  c.nb = t % nbs;
-  const int mi = t / nbs;
-  const int per2 = (a.M / a.nranks) / BM2;
-  int d;
-  if (MODE == MODE_AG_GEMM) {
-    d = mi / per2;
-    c.jb = mi % per2;
-    c.owner = mt_mod(a.rank[lr] - d, a.nranks);
-  } else {
-    c.jb = mi / a.nranks;
-    d = mi % a.nranks;
-    c.owner = mt_mod(a.rank[lr] + 1 + d, a.nranks);
-  }
-  c.mb = c.owner * per2 + c.jb;
-  return c;
+  static_assert(MODE_PLAIN == MT_TILE_PLAIN && MODE_AG_GEMM == MT_TILE_AG_GEMM && MODE_GEMM_RS == MT_TILE_GEMM_RS, "mode codes");
+  return mt_fused_tile(MODE, t, a.M, a.N, a.nranks, a.rank[lr], a.raster, BM2, BN);
 }
 
 template <int MODE, bool FP8>

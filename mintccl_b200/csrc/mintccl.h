@@ -118,6 +118,8 @@ int mt_test_wait_timeout(MtComm* c, void* stream);
 // ---- host model of the fused GEMM + collective protocols (threads and atomics, no GPU; sim/sim_fused.cpp) ----
 // op: 0 all-gather -> GEMM, 1 GEMM -> reduce-scatter.  Returns 0 ok, 1 data of another call was read, 2 a wait gave
 // up, -1 bad argument.
+void mt_sched_fused_tile(int mode, int t, int M, int N, int nranks, int rank, int raster, int tile_rows, int tile_cols,
+                         int* out);   // tile order of the GEMM kernels: {row block, column block, owner, block in owner}
 int mt_sim_fused(int op, int nranks, int per, int nbs, int ngemm, int nextra, int pair, int iters, uint32_t seed,
                  int dead_rank, int slow_rank, int double_buffer, uint64_t timeout_ms);
 

@@ -3,8 +3,9 @@
 // system-scope loads, stores and reductions, stamps for the data.  The tile orders, the arrival counters
 // (which only ever grow: call e waits for e x arrivals), the entry barrier of the comm CTAs, the ticketed
 // reducers with their two alternating ticket words and the two alternating halves of the staging area are
-// the ones of the kernels.  Every datum carries the number of the call that produced it, so a read that sees
-// another call's data (a buffer reused too early) is reported, not just a deadlock.
+// the ones of the kernels (the tile order is the kernels' own code, kernels/fused_schedule.h).  Every datum
+// carries the number of the call that produced it, so a read that sees another call's data (a buffer reused
+// too early) is reported, not just a deadlock.
 //
 // What it is for: schedules that cannot be forced on a GPU (one rank far ahead of another, reducers that
 // stall) and failures that must not be provoked there (a rank that never starts).  The reference has no such
@@ -17,6 +18,8 @@
 #include <random>
 #include <thread>
 #include <vector>
+
+#include "../kernels/fused_schedule.h"
 
 namespace {
 
@@ -98,8 +101,6 @@ struct Ctx {
   }
 };
 
-inline int mod(int a, int n) { return ((a % n) + n) % n; }
-
 // ---- all-gather -> GEMM -----------------------------------------------------------------------------------
 void ag_comm_cta(Ctx& c, int me, int cc, uint64_t e) {
   const Params& p = c.w->p;
@@ -121,9 +122,9 @@ void ag_gemm_cta(Ctx& c, int me, int g, uint64_t e) {
   const int bpt = p.pair ? 2 : 1, per_t = p.per / bpt;
   const int tiles = p.n * per_t * p.nbs;
   for (int t = g; t < tiles; t += p.ngemm) {
-    const int mi = t / p.nbs;
-    const int d = mi / per_t, j = mi % per_t;
-    const int owner = mod(me - d, p.n);
+    // the kernels' own tile order (128-row tiles, or 256-row tiles of a CTA pair)
+    const MtTile tl = mt_fused_tile(MT_TILE_AG_GEMM, t, p.n * p.per * 128, p.nbs * 256, p.n, me, 0, 128 * bpt, 256);
+    const int owner = tl.owner, j = tl.jb;
     if (owner != me) {
       for (int h = 0; h < bpt; ++h) {  // with pairs, each CTA of the pair waits for its own block
         const int blk = j * bpt + h;
@@ -165,9 +166,8 @@ void rs_gemm_cta(Ctx& c, int me, int g, uint64_t e) {
   const int tiles = p.n * per_t * p.nbs;
   const int buf = p.double_buffer ? (int)(e & 1) : 0;
   for (int t = g; t < tiles; t += p.ngemm) {
-    const int nb = t % p.nbs, mi = t / p.nbs;
-    const int j = mi / p.n, d = mi % p.n;
-    const int owner = mod(me + 1 + d, p.n);
+    const MtTile tl = mt_fused_tile(MT_TILE_GEMM_RS, t, p.n * p.per * 128, p.nbs * 256, p.n, me, 0, 128 * bpt, 256);
+    const int nb = tl.nb, j = tl.jb, owner = tl.owner;
     c.jitter();
     Rank& r = c.w->ranks[owner];
     for (int h = 0; h < bpt; ++h) {
@@ -207,6 +207,16 @@ void cta_thread(World* w, int me, int idx, uint32_t seed) {
 }  // namespace
 
 extern "C" {
+
+// The kernels' tile order, for tests of its coverage: out = {row block, column block, owner, row block in owner}.
+void mt_sched_fused_tile(int mode, int t, int M, int N, int nranks, int rank, int raster, int tile_rows, int tile_cols,
+                         int* out) {
+  const MtTile c = mt_fused_tile(mode, t, M, N, nranks, rank, raster, tile_rows, tile_cols);
+  out[0] = c.mb;
+  out[1] = c.nb;
+  out[2] = c.owner;
+  out[3] = c.jb;
+}
 
 // Runs `iters` back-to-back calls of one fused op on a simulated world.  op: 0 all-gather -> GEMM, 1 GEMM ->
 // reduce-scatter.  Returns 0 ok, 1 a CTA read data of another call (or a tile was reduced twice / not at all),

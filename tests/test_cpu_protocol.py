@@ -191,3 +191,38 @@ def test_fused_protocols_dead_rank_times_out():
     """A rank that never starts: the others give up after their time limit instead of spinning forever."""
     assert _fused(0, 4, 4, 2, 3, 2, 0, 3, dead=2, timeout_ms=300) == 2
     assert _fused(1, 4, 4, 3, 3, 2, 1, 3, dead=1, timeout_ms=300) == 2
+
+
+def _tile(mode, t, M, N, n, rank, raster, rows, cols=256):
+    import ctypes
+    from mintccl_b200 import _native as N_
+    out = (ctypes.c_int * 4)()
+    N_.lib().mt_sched_fused_tile(mode, t, M, N, n, rank, raster, rows, cols, out)
+    return tuple(out)
+
+
+@pytest.mark.parametrize("rows", [128, 256])
+def test_gemm_tile_orders_cover_every_tile_once(rows):
+    """The tile order the GEMM kernels walk (single-CTA 128-row tiles, 256-row tiles of a CTA pair), every mode:
+    a permutation of all tiles on every rank; owners and blocks consistent; the documented visiting order."""
+    M, N = 2048 * 2, 1024
+    mbs, nbs = M // rows, N // 256
+    for raster in (0, 1, 3, 4, 16):                                   # plain: grouped raster, ragged last group
+        seen = {_tile(0, t, M, N, 1, 0, raster, rows)[:2] for t in range(mbs * nbs)}
+        assert seen == {(mb, nb) for mb in range(mbs) for nb in range(nbs)}
+    for n in (1, 2, 4, 8):
+        per = M // n // rows
+        for mode in (1, 2):
+            for rank in range(n):
+                tiles = [_tile(mode, t, M, N, n, rank, 0, rows) for t in range(mbs * nbs)]
+                assert {(mb, nb) for mb, nb, _, _ in tiles} == {(mb, nb) for mb in range(mbs) for nb in range(nbs)}
+                assert all(mb == owner * per + jb and 0 <= jb < per for mb, _, owner, jb in tiles)
+                owners = [owner for _, _, owner, _ in tiles]
+                if mode == 1:
+                    # all-gather -> GEMM: own rows first, then rank - 1, rank - 2, ... (arrival order of the pushes)
+                    firsts = [owners.index(o) for o in [(rank - d) % n for d in range(n)]]
+                    assert owners[0] == rank and firsts == sorted(firsts)
+                else:
+                    # GEMM -> reduce-scatter: the first n * nbs tiles are block 0 of every owner, starting at rank + 1
+                    assert owners[0] == (rank + 1) % n
+                    assert {(o, jb) for _, _, o, jb in tiles[:n * nbs]} == {(o, 0) for o in range(n)}
