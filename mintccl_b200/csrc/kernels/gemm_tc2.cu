@@ -446,7 +446,7 @@ int gemm_pair_max_clusters(int mode, bool fp8) {
     n = sms / 2;
   }
   if (const char* e = getenv("MINTCCL_DEBUG")) {
-    if (atoi(e) > 0)
+    if (strcmp(e, "info") == 0 || strcmp(e, "trace") == 0 || atoi(e) > 0)  // same levels as the Python side
       fprintf(stderr, "[mintccl] pair GEMM (mode %d, %s): %d clusters of 2 CTAs fit on %d SMs\n", mode, fp8 ? "mxfp8" : "bf16", n, sms);
   }
   slot = n;
