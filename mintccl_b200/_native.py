@@ -75,6 +75,10 @@ def lib():
     sig("mt_version", i32)
     sig("mt_launch_count", u64)
     sig("mt_reset_launch_count", None)
+    sig("mt_stats_count", i32)
+    sig("mt_stats_name", cp, i32)
+    sig("mt_stats_get", i32, i32, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64))
+    sig("mt_stats_reset", None)
     sig("mt_comm_create", vp, i32, i32, i32, C.POINTER(MtConfig))
     sig("mt_comm_create_emulated", vp, i32, i32, C.POINTER(MtConfig))
     sig("mt_comm_destroy", None, vp)

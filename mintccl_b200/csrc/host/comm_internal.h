@@ -39,6 +39,13 @@ struct MtComm {
 };
 
 namespace mthost {
+// Per-family counters of successful launches through the C interface (calls and work: bytes of the message for
+// collectives and copies, floating-point operations for GEMMs); read with mt_stats_get.
+enum StatKind {
+  ST_RING_SIMPLE = 0, ST_RING_LL128, ST_DIRECT, ST_NVLS, ST_LL_ONESHOT, ST_P2P, ST_LOCAL_COPY, ST_GEMM, ST_GEMM_MXFP8,
+  ST_AG_GEMM, ST_GEMM_RS, ST_MXFP8_REDUCE, ST_COUNT
+};
+void stat_add(int kind, uint64_t work);
 // Records an error message for mt_last_error() and returns -1.
 int fail(const std::string& m);
 // Looks a driver entry point up through the runtime (no link-time dependency on the driver library).

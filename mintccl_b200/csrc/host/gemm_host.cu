@@ -124,6 +124,7 @@ static int gemm_pair(void* stream, const void* A, const void* sfa, const void* B
   if (nclusters < 1) nclusters = 1;
   cudaError_t e = mt::launch_gemm_pair(mt::MODE_PLAIN, maps, sf, a, nclusters, 1, (cudaStream_t)stream, fp8);
   if (e != cudaSuccess) return fail(std::string("pair gemm launch: ") + cudaGetErrorString(e));
+  mthost::stat_add(fp8 ? mthost::ST_GEMM_MXFP8 : mthost::ST_GEMM, (uint64_t)(2.0 * M * N * K));
   return 0;
 }
 
@@ -160,6 +161,7 @@ int mt_gemm(void* stream, const void* A, const void* B, void* C, int M, int N, i
   if (grid > tiles) grid = tiles;
   cudaError_t e = mt::launch_gemm_tc(mt::MODE_PLAIN, maps, a, grid, 1, (cudaStream_t)stream);
   if (e != cudaSuccess) return fail(std::string("gemm launch: ") + cudaGetErrorString(e));
+  mthost::stat_add(mthost::ST_GEMM, (uint64_t)(2.0 * M * N * K));
   return 0;
 }
 
@@ -196,6 +198,7 @@ int mt_gemm_mxfp8(void* stream, const void* A, const void* sfa, const void* B, c
   if (grid > tiles) grid = tiles;
   cudaError_t e = mt::launch_gemm_tc(mt::MODE_PLAIN, maps, a, grid, 1, (cudaStream_t)stream, true);
   if (e != cudaSuccess) return fail(std::string("mxfp8 gemm launch: ") + cudaGetErrorString(e));
+  mthost::stat_add(mthost::ST_GEMM_MXFP8, (uint64_t)(2.0 * M * N * K));
   return 0;
 }
 
@@ -277,10 +280,12 @@ static int ag_gemm_impl(MtComm* c, void* stream, const void* const* a_shard, con
     if (nclusters < 1) return fail("not enough CTAs for the requested comm CTAs");
     cudaError_t e2 = mt::launch_gemm_pair(mt::MODE_AG_GEMM, maps, sf, a, nclusters, c->nlocal, (cudaStream_t)stream, fp8);
     if (e2 != cudaSuccess) return fail(std::string("pair ag_gemm launch: ") + cudaGetErrorString(e2));
+    mthost::stat_add(mthost::ST_AG_GEMM, (uint64_t)(2.0 * M * N * K));
     return 0;
   }
   cudaError_t e = mt::launch_gemm_tc(mt::MODE_AG_GEMM, maps, a, grid, c->nlocal, (cudaStream_t)stream, fp8);
   if (e != cudaSuccess) return fail(std::string("ag_gemm launch: ") + cudaGetErrorString(e));
+  mthost::stat_add(mthost::ST_AG_GEMM, (uint64_t)(2.0 * M * N * K));
   return 0;
 }
 
@@ -344,10 +349,12 @@ static int gemm_rs_impl(MtComm* c, void* stream, const void* const* A, const voi
     if (nclusters < 1) return fail("nred out of range");
     cudaError_t e2 = mt::launch_gemm_pair(mt::MODE_GEMM_RS, maps, sf, a, nclusters, c->nlocal, (cudaStream_t)stream, fp8);
     if (e2 != cudaSuccess) return fail(std::string("pair gemm_rs launch: ") + cudaGetErrorString(e2));
+    mthost::stat_add(mthost::ST_GEMM_RS, (uint64_t)(2.0 * M * N * K));
     return 0;
   }
   cudaError_t e = mt::launch_gemm_tc(mt::MODE_GEMM_RS, maps, a, grid, c->nlocal, (cudaStream_t)stream, fp8);
   if (e != cudaSuccess) return fail(std::string("gemm_rs launch: ") + cudaGetErrorString(e));
+  mthost::stat_add(mthost::ST_GEMM_RS, (uint64_t)(2.0 * M * N * K));
   return 0;
 }
 
@@ -387,6 +394,7 @@ int mt_mxfp8_reduce(MtComm* c, void* stream, int op, uint64_t data_in_off, uint6
   }
   cudaError_t e = mt::launch_mxfp8(c->d_comms, a, nctas, c->nlocal, (cudaStream_t)stream);
   if (e != cudaSuccess) return fail(std::string("mxfp8 launch: ") + cudaGetErrorString(e));
+  mthost::stat_add(mthost::ST_MXFP8_REDUCE, nelems);
   return 0;
 }
 

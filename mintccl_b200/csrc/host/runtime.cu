@@ -22,11 +22,15 @@
 #include "../kernels/p2p_engine.cuh"
 #include "../kernels/ring_engine.cuh"
 #include "../mintccl.h"
+#include "comm_internal.h"
 
 namespace {
 
 thread_local std::string g_err;
 std::atomic<uint64_t> g_launches{0};
+std::atomic<uint64_t> g_stat_calls[mthost::ST_COUNT], g_stat_work[mthost::ST_COUNT];
+const char* const g_stat_names[mthost::ST_COUNT] = {"ring_simple", "ring_ll128", "direct", "nvls", "ll_oneshot", "p2p",
+                                                     "local_copy", "gemm", "gemm_mxfp8", "ag_gemm", "gemm_rs", "mxfp8_reduce"};
 
 int fail(const std::string& m) {
   g_err = m;
@@ -57,9 +61,13 @@ F drv(const char* name) {
 
 }  // namespace
 
-#include "comm_internal.h"
 namespace mthost {
 int fail(const std::string& m) { return ::fail(m); }
+void stat_add(int kind, uint64_t work) {
+  if (kind < 0 || kind >= ST_COUNT) return;
+  g_stat_calls[kind].fetch_add(1, std::memory_order_relaxed);
+  g_stat_work[kind].fetch_add(work, std::memory_order_relaxed);
+}
 void* driver_entry(const char* name) { return (void*)drv<void*>(name); }
 }  // namespace mthost
 
@@ -127,6 +135,21 @@ const char* mt_last_error(void) { return g_err.c_str(); }
 int mt_version(void) { return 100; }
 uint64_t mt_launch_count(void) { return g_launches.load(); }
 void mt_reset_launch_count(void) { g_launches.store(0); }
+
+int mt_stats_count(void) { return mthost::ST_COUNT; }
+const char* mt_stats_name(int kind) { return kind >= 0 && kind < mthost::ST_COUNT ? g_stat_names[kind] : ""; }
+int mt_stats_get(int kind, uint64_t* calls, uint64_t* work) {
+  if (kind < 0 || kind >= mthost::ST_COUNT) return -1;
+  if (calls) *calls = g_stat_calls[kind].load();
+  if (work) *work = g_stat_work[kind].load();
+  return 0;
+}
+void mt_stats_reset(void) {
+  for (int i = 0; i < mthost::ST_COUNT; ++i) {
+    g_stat_calls[i].store(0);
+    g_stat_work[i].store(0);
+  }
+}
 
 static int check_cfg(const MtConfig* cfg, int nranks) {
   if (nranks < 1 || nranks > MT_MAX_RANKS) return fail("nranks must be in [1, 8]");
@@ -491,7 +514,10 @@ int mt_ring(MtComm* c, void* stream, int proto, int dtype, int op, const void* c
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, c->device);
     cudaError_t e = mt::launch_local_copy(out[0], in[0], nbytes, sms, (cudaStream_t)stream);
-    if (e == cudaSuccess) return 0;
+    if (e == cudaSuccess) {
+      mthost::stat_add(mthost::ST_LOCAL_COPY, nbytes);
+      return 0;
+    }
     if (e != cudaErrorInvalidValue) return fail(std::string("local copy launch: ") + cudaGetErrorString(e));
     cudaGetLastError();  // pointers not co-aligned: the ring kernel copies any alignment
   }
@@ -513,6 +539,7 @@ int mt_ring(MtComm* c, void* stream, int proto, int dtype, int op, const void* c
                       ? mt::launch_ring_ll128(dtype, c->d_comms, a, nchannels, c->nlocal, (cudaStream_t)stream)
                       : mt::launch_ring_simple(dtype, c->d_comms, a, nchannels, c->nlocal, (cudaStream_t)stream);
   if (e != cudaSuccess) return fail(std::string("ring launch: ") + cudaGetErrorString(e));
+  mthost::stat_add(proto == MT_PROTO_LL128 ? mthost::ST_RING_LL128 : mthost::ST_RING_SIMPLE, nbytes);
   return 0;
 }
 
@@ -538,6 +565,7 @@ int mt_direct(MtComm* c, void* stream, int dtype, int op, const void* const* in,
   a.nvls = nvls;
   cudaError_t e = mt::launch_direct(dtype, c->d_comms, a, nctas, c->nlocal, (cudaStream_t)stream);
   if (e != cudaSuccess) return fail(std::string("direct launch: ") + cudaGetErrorString(e));
+  mthost::stat_add(nvls ? mthost::ST_NVLS : mthost::ST_DIRECT, nbytes);
   return 0;
 }
 
@@ -558,6 +586,7 @@ int mt_ll_allreduce(MtComm* c, void* stream, int dtype, const void* const* in, v
   // whose private epoch is the flag value
   cudaError_t e = mt::launch_ll_allreduce(dtype, c->d_comms, a, c->ll_grid, c->nlocal, (cudaStream_t)stream);
   if (e != cudaSuccess) return fail(std::string("ll launch: ") + cudaGetErrorString(e));
+  mthost::stat_add(mthost::ST_LL_ONESHOT, nbytes);
   return 0;
 }
 
@@ -594,6 +623,7 @@ int mt_p2p(MtComm* c, void* stream, int src_rank, int dst_rank, const void* src_
   if (!any) return 0;
   cudaError_t e = mt::launch_p2p(c->d_comms, a, nctas, c->nlocal, (cudaStream_t)stream);
   if (e != cudaSuccess) return fail(std::string("p2p launch: ") + cudaGetErrorString(e));
+  mthost::stat_add(mthost::ST_P2P, nbytes);
   return 0;
 }
 

@@ -32,6 +32,12 @@ const char* mt_last_error(void);
 int mt_version(void);
 uint64_t mt_launch_count(void);          // kernels launched by this library in this process
 void mt_reset_launch_count(void);
+// Per-family counters of successful launches: calls, and work (message bytes for collectives and copies,
+// floating-point operations for GEMMs).  Families: mt_stats_name(0 .. mt_stats_count() - 1).
+int mt_stats_count(void);
+const char* mt_stats_name(int kind);
+int mt_stats_get(int kind, uint64_t* calls, uint64_t* work);
+void mt_stats_reset(void);
 
 // ---- communicator life cycle ------------------------------------------------------------------------
 // Real communicator: one rank per process.  Steps: create -> export -> (exchange) -> import peers ->

@@ -159,3 +159,14 @@ def test_fused_plan_cta_counts_follow_the_gemm_to_transfer_ratio():
     assert AllGatherGemm.pick_ncomm(448) == 24
     # MXFP8 halves the bytes and nearly doubles the GEMM rate: never more comm CTAs than bf16
     assert AllGatherGemm.pick_ncomm(448, flops=2.0 * T * 1792 * H, bytes_in=7 / 8 * T * H, fp8=True) <= 24
+
+
+def test_launch_statistics_interface():
+    """Per-family counters of the native library: names, zero without launches, reset."""
+    from mintccl_b200.utils import stats
+    stats.reset()
+    allf = stats.snapshot(skip_idle=False)
+    assert {"ring_simple", "ring_ll128", "direct", "nvls", "ll_oneshot", "p2p", "local_copy", "gemm", "gemm_mxfp8",
+            "ag_gemm", "gemm_rs", "mxfp8_reduce"} == set(allf)
+    assert all(v == {"calls": 0, "work": 0} for v in allf.values())
+    assert stats.snapshot() == {} and stats.report() == "(nothing launched)"

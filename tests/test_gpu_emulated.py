@@ -336,6 +336,8 @@ def test_one_rank_communicator_copies_at_any_alignment():
     from mintccl_b200 import Config
     comm = mintccl_b200.Communicator(config=Config.from_env(heap_bytes=256 << 20, max_channels=4))
     assert comm.world_size == 1
+    from mintccl_b200.utils import stats
+    stats.reset()
     base_in = torch.arange(0, 3_000_064, device="cuda", dtype=torch.int32).view(torch.uint8)
     base_out = torch.zeros(base_in.numel() + 64, device="cuda", dtype=torch.uint8)
     for nbytes, oi, oo in [(16, 0, 0), (1, 3, 3), (15, 1, 1), (4096 * 8 + 5, 7, 7), (1_000_003, 0, 0), (2_500_000, 13, 13),
@@ -347,6 +349,8 @@ def test_one_rank_communicator_copies_at_any_alignment():
         comm.check()
         assert torch.equal(dst, src), (nbytes, oi, oo)
         assert int(base_out[oo + nbytes:oo + nbytes + 32].sum()) == 0 and int(base_out[:oo].sum()) == 0, "wrote outside"
+    seen = stats.snapshot()   # co-aligned pairs went to the copy kernel, the two others to the ring kernel
+    assert seen["local_copy"]["calls"] >= 1 and seen["ring_simple"]["calls"] >= 1 and seen["local_copy"]["work"] >= 8 << 20
     x = torch.randn(1, 100_000, device="cuda", dtype=torch.float16)
     y = x.clone()
     comm.allgather(x)          # in place: nothing to do
