@@ -82,8 +82,9 @@ static int raster_for(int M, int N, int K, int elem_bytes) {
   return b_bytes > 48e6 ? 16 : 1;
 }
 
-// The plain GEMM runs on CTA pairs (one 256 x 256 tile per cluster of two CTAs, gemm_tc2.cu) when M allows
-// it; MINTCCL_GEMM_PAIR=0 selects the single-CTA kernel.
+// GEMMs run on CTA pairs (one 256 x 256 tile per cluster of two CTAs, gemm_tc2.cu) when the rows (of the
+// problem for the plain GEMM, of one rank for the fused kernels) are a multiple of 256; otherwise, and with
+// MINTCCL_GEMM_PAIR=0, on the single-CTA kernels of gemm_tc.cu.
 static int g_pair_mode = -1;
 static bool use_pair(int M) {
   if (g_pair_mode < 0) {
