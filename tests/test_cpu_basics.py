@@ -170,3 +170,13 @@ def test_launch_statistics_interface():
             "ag_gemm", "gemm_rs", "mxfp8_reduce"} == set(allf)
     assert all(v == {"calls": 0, "work": 0} for v in allf.values())
     assert stats.snapshot() == {} and stats.report() == "(nothing launched)"
+
+
+def test_profile_range_is_a_noop_without_cuda():
+    from mintccl_b200.utils.profiler import profile_range
+    ran = []
+    with profile_range("x"):
+        ran.append(1)
+    with profile_range("y", enabled=False):
+        ran.append(2)
+    assert ran == [1, 2]
