@@ -5,6 +5,11 @@ Keeps every knob of the reference (common.py:76-118: ``MINTCCL_NUM_BLOCKS``, ``M
 same names and adds the ones its roadmap asks for (README.md:57 "fine-grained control of SM layout"):
 algorithm, protocol, channel count, FIFO depth, wait time limit, heap size.  Booleans are parsed properly:
 the reference's ``bool(os.getenv(...))`` (common.py:113,118) is true for the string ``"0"``.
+
+Read by the native library itself, at every call (tuning switches, not part of :class:`Config`):
+``MINTCCL_GEMM_PAIR`` (0: single-CTA GEMM kernels instead of CTA pairs), ``MINTCCL_GEMM_RASTER`` (row blocks per
+group of the plain GEMM's tile order), ``MINTCCL_CHAIN_STEP_BYTES`` (bytes per FIFO step of chain operations over
+the Simple protocol, default one slot), ``MINTCCL_NO_LOCAL_COPY`` (one-rank communicators use the ring kernel).
 """
 from __future__ import annotations
 

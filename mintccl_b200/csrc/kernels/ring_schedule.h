@@ -16,6 +16,7 @@
 //   OP_REDUCESCATTER 7_reducescatter.py:13-79
 //   OP_ALLREDUCE     on the reference's roadmap only (README.md:23)
 #pragma once
+#include <stdlib.h>
 #include "../device/sched.h"
 
 #if defined(__CUDACC__)
@@ -45,7 +46,23 @@ struct RingArgs {
   int32_t chain_len;              // OP_SENDRECV: number of ranks on the route
   int32_t chain[MT_MAX_RANKS + 1];
   int32_t elem_size;
+  uint32_t step_bytes;            // chain ops over the Simple protocol: bytes per FIFO step when smaller than a slot
+                                  // (0: whole slots); a multiple of 128
 };
+
+// Step size of chain operations (send/recv over a route, broadcast, reduce).  The last of L ranks sees its first
+// byte after L - 2 extra steps, so a message of few slot-sized steps per channel spends most of its time filling
+// the chain; smaller steps shorten the fill at the price of more flag traffic per byte.  MINTCCL_CHAIN_STEP_BYTES
+// sets it (rounded down to a multiple of 128, at least 4 KiB); unset or 0 keeps whole slots.
+static inline uint32_t mt_chain_step_from_env() {
+  const char* e = getenv("MINTCCL_CHAIN_STEP_BYTES");
+  if (!e) return 0;
+  long long v = atoll(e);
+  if (v <= 0) return 0;
+  if (v < 4096) v = 4096;
+  if (v > (1ll << 30)) v = 1ll << 30;
+  return (uint32_t)(v & ~127ll);
+}
 
 enum Role : int {
   R_NONE = 0,
@@ -119,7 +136,8 @@ MT_SCHED_FN void ring_body(const MtDevComm& c, const RingArgs& a, int lr, int ch
     if (role == R_NONE) return;
     Proto<T, NTHREADS> p(c, ch, up, down, s_fail);
     const MtRange r = mt_split(a.nbytes, nch, ch, kSplitAlign);
-    const uint64_t P = p.step_payload();
+    uint64_t P = p.step_payload();
+    if (a.step_bytes && a.step_bytes < P) P = a.step_bytes;  // sub-slot steps: a shorter fill of the chain
     bool ok = true;
     for (uint64_t off = r.lo; ok && off < r.hi; off += P) {
       const uint64_t nb = mt_min64(P, r.hi - off);

@@ -226,3 +226,18 @@ def test_gemm_tile_orders_cover_every_tile_once(rows):
                     # GEMM -> reduce-scatter: the first n * nbs tiles are block 0 of every owner, starting at rank + 1
                     assert owners[0] == (rank + 1) % n
                     assert {(o, jb) for _, _, o, jb in tiles[:n * nbs]} == {(o, 0) for o in range(n)}
+
+
+def test_chain_operations_with_sub_slot_steps(monkeypatch):
+    """MINTCCL_CHAIN_STEP_BYTES: chain operations over the Simple protocol step through the FIFOs in pieces smaller
+    than a slot (a shorter fill of the chain).  Same results, many operations back to back, with and without it;
+    the LL128 protocol and the closed-ring collectives ignore the knob."""
+    for step in ("4096", "8192", "1000000", "0"):
+        monkeypatch.setenv("MINTCCL_CHAIN_STEP_BYTES", step)
+        for op, kw in (("broadcast", dict(root=3)), ("reduce", dict(root=5)), ("sendrecv", dict(chain=[0, 1, 2, 3, 4]))):
+            rc, st = sim(8, 2, 0, OPS[op], 50_003, iters=40, jitter=5, slot_bytes=32768, slots=2, **kw)
+            assert rc == 0, (step, op, [(s.code, s.where, s.step) for s in st[:8]])
+        rc, _ = sim(8, 2, 1, OPS["broadcast"], 20_001, root=1, iters=10, slot_bytes=32768)
+        assert rc == 0
+        rc, _ = sim(4, 2, 0, OPS["allreduce"], 20_001, iters=10, slot_bytes=32768)
+        assert rc == 0
