@@ -40,17 +40,31 @@ struct Params {
   uint64_t timeout_ms;
 };
 
+// The payload (gathered rows, partial tiles).  Normally atomics, so that the model itself has no undefined
+// behaviour even when it demonstrates a protocol that reuses a buffer too early.  With MT_SIM_PLAIN_DATA the
+// payload is plain memory: built with -fsanitize=thread, ThreadSanitizer then checks that the counters and
+// barriers (the only atomics left) order every payload write before the reads that depend on it.
+#ifdef MT_SIM_PLAIN_DATA
+struct Datum {
+  uint64_t v = 0;
+  void store(uint64_t x, std::memory_order = std::memory_order_relaxed) { v = x; }
+  uint64_t load(std::memory_order = std::memory_order_relaxed) const { return v; }
+};
+#else
+using Datum = std::atomic<uint64_t>;
+#endif
+
 inline uint64_t stamp(uint64_t call, int rank, int block, int nb) {
   return (call << 32) | ((uint64_t)rank << 24) | ((uint64_t)block << 12) | (uint64_t)nb;
 }
 
 struct Rank {
   // all-gather -> GEMM
-  std::vector<std::atomic<uint64_t>> gathered;  // [n][per]: rows of every source rank
+  std::vector<Datum> gathered;                  // [n][per]: rows of every source rank
   std::vector<std::atomic<uint64_t>> ag_cnt;    // [n][per]
   std::vector<std::atomic<uint64_t>> bar;       // [nextra][n]: entry barrier of comm CTA cc, slot of rank p
   // GEMM -> reduce-scatter
-  std::vector<std::atomic<uint64_t>> stage;     // [2][n][per][nbs]
+  std::vector<Datum> stage;                     // [2][n][per][nbs]
   std::vector<std::atomic<uint64_t>> rs_cnt;    // [n][per][nbs]
   std::atomic<uint64_t> tickets[2];
   std::vector<std::atomic<uint64_t>> out;       // [per][nbs]: call number of the last reduction
@@ -229,13 +243,15 @@ int mt_sim_fused(int op, int nranks, int per, int nbs, int ngemm, int nextra, in
   Params p{op, nranks, per, nbs, ngemm, nextra, pair, iters, dead_rank, slow_rank, double_buffer, timeout_ms ? timeout_ms : 2000};
   World w(p);
   for (auto& r : w.ranks) {
-    r.gathered = std::vector<std::atomic<uint64_t>>((size_t)nranks * per);
+    r.gathered = std::vector<Datum>((size_t)nranks * per);
     r.ag_cnt = std::vector<std::atomic<uint64_t>>((size_t)nranks * per);
     r.bar = std::vector<std::atomic<uint64_t>>((size_t)(nextra > 0 ? nextra : 1) * nranks);
-    r.stage = std::vector<std::atomic<uint64_t>>((size_t)2 * nranks * per * nbs);
+    r.stage = std::vector<Datum>((size_t)2 * nranks * per * nbs);
     r.rs_cnt = std::vector<std::atomic<uint64_t>>((size_t)nranks * per * nbs);
     r.out = std::vector<std::atomic<uint64_t>>((size_t)per * nbs);
-    for (auto* v : {&r.gathered, &r.ag_cnt, &r.bar, &r.stage, &r.rs_cnt, &r.out})
+    for (auto* v : {&r.ag_cnt, &r.bar, &r.rs_cnt, &r.out})
+      for (auto& x : *v) x.store(0);
+    for (auto* v : {&r.gathered, &r.stage})
       for (auto& x : *v) x.store(0);
     r.tickets[0].store(0);
     r.tickets[1].store(0);
@@ -251,3 +267,15 @@ int mt_sim_fused(int op, int nranks, int per, int nbs, int ngemm, int nextra, in
 }
 
 }  // extern "C"
+
+#ifdef MT_SIM_MAIN
+// Stand-alone driver (used for the ThreadSanitizer build): the arguments of mt_sim_fused in order.
+#include <stdlib.h>
+int main(int argc, char** argv) {
+  if (argc != 14) return 64;
+  long v[13];
+  for (int i = 0; i < 13; ++i) v[i] = atol(argv[i + 1]);
+  return mt_sim_fused((int)v[0], (int)v[1], (int)v[2], (int)v[3], (int)v[4], (int)v[5], (int)v[6], (int)v[7], (uint32_t)v[8],
+                      (int)v[9], (int)v[10], (int)v[11], (uint64_t)v[12]);
+}
+#endif

@@ -241,3 +241,37 @@ def test_chain_operations_with_sub_slot_steps(monkeypatch):
         assert rc == 0
         rc, _ = sim(4, 2, 0, OPS["allreduce"], 20_001, iters=10, slot_bytes=32768)
         assert rc == 0
+
+
+def test_fused_protocols_under_thread_sanitizer(tmp_path):
+    """The host model of the fused kernels with its payload as PLAIN memory, built with -fsanitize=thread: the
+    arrival counters, the entry barrier and the tickets must order every payload write before the reads that
+    depend on it (no report), and ThreadSanitizer must see the race of a single staging buffer."""
+    import shutil
+    import subprocess
+    gxx = shutil.which("g++")
+    if gxx is None:
+        pytest.skip("no g++")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    src = os.path.join(root, "mintccl_b200", "csrc", "sim", "sim_fused.cpp")
+    exe = str(tmp_path / "sim_fused_tsan")
+    r = subprocess.run([gxx, "-O1", "-g", "-std=c++17", "-fsanitize=thread", "-DMT_SIM_PLAIN_DATA", "-DMT_SIM_MAIN",
+                        "-I", os.path.join(root, "mintccl_b200", "csrc"), src, "-o", exe, "-pthread"],
+                       capture_output=True, text=True)
+    if r.returncode != 0:
+        pytest.skip("ThreadSanitizer is not available: " + r.stderr[-300:])
+    env = dict(os.environ, TSAN_OPTIONS="exitcode=66 halt_on_error=1")
+
+    def run(*a):
+        p = subprocess.run([exe] + [str(x) for x in a], env=env, capture_output=True, text=True, timeout=300)
+        return p.returncode, p.stderr
+
+    # op, ranks, row blocks, column blocks, GEMM CTAs, comm / reducer CTAs, pair, calls, seed, dead, slow, halves, ms
+    clean = [(0, 4, 4, 2, 3, 2, 0, 20, 1, -1, -1, 1, 4000), (0, 4, 4, 2, 3, 2, 1, 20, 2, -1, 0, 1, 4000),
+             (1, 4, 4, 3, 3, 2, 0, 20, 3, -1, -1, 1, 4000), (1, 4, 4, 3, 3, 2, 1, 20, 4, -1, 0, 1, 4000),
+             (1, 8, 2, 2, 2, 0, 0, 10, 5, -1, -1, 1, 4000)]
+    for a in clean:
+        rc, err = run(*a)
+        assert rc == 0, (a, err[-1500:])
+    rc, err = run(1, 4, 4, 3, 3, 2, 0, 20, 3, -1, 0, 0, 4000)      # one staging buffer, one slow rank
+    assert rc == 66 and "data race" in err
