@@ -369,3 +369,19 @@ int mt_sim_run(int nranks, int nchannels, int proto, int op, uint64_t count, int
 }
 
 }  // extern "C"
+
+#ifdef MT_SIM_MAIN
+// Stand-alone driver (used for the ThreadSanitizer build):
+//   sim ranks channels proto op count root spatial iters jitter_us slot_bytes slots [chain ranks ...]
+#include <stdlib.h>
+int main(int argc, char** argv) {
+  if (argc < 12) return 64;
+  long v[11];
+  for (int i = 0; i < 11; ++i) v[i] = atol(argv[i + 1]);
+  int chain[MT_MAX_RANKS + 1];
+  int chain_len = 0;
+  for (int i = 12; i < argc && chain_len <= MT_MAX_RANKS; ++i) chain[chain_len++] = atoi(argv[i]);
+  return mt_sim_run((int)v[0], (int)v[1], (int)v[2], (int)v[3], (uint64_t)v[4], (int)v[5], (int)v[6], chain_len ? chain : nullptr,
+                    chain_len, nullptr, (int)v[7], (int)v[8], -1, 8000, 1u, (uint64_t)v[9], (uint32_t)v[10], nullptr);
+}
+#endif

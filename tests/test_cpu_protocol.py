@@ -275,3 +275,42 @@ def test_fused_protocols_under_thread_sanitizer(tmp_path):
         assert rc == 0, (a, err[-1500:])
     rc, err = run(1, 4, 4, 3, 3, 2, 0, 20, 3, -1, 0, 0, 4000)      # one staging buffer, one slow rank
     assert rc == 66 and "data race" in err
+
+
+def test_ring_protocols_under_thread_sanitizer(tmp_path):
+    """The ring / chain simulator (the GPU kernels' own schedule code over host FIFOs) built with
+    -fsanitize=thread: payload bytes are plain memory, so ThreadSanitizer checks that the step counters and
+    credits (release / acquire) order every slot write before its read and every slot reuse after its drain."""
+    import shutil
+    import subprocess
+    gxx = shutil.which("g++")
+    if gxx is None:
+        pytest.skip("no g++")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    src = os.path.join(root, "mintccl_b200", "csrc", "sim", "sim.cpp")
+    exe = str(tmp_path / "sim_tsan")
+    inc = ["-I", os.path.join(root, "mintccl_b200", "csrc")]
+    if os.path.isdir("/usr/local/cuda/include"):
+        inc += ["-I", "/usr/local/cuda/include"]
+    r = subprocess.run([gxx, "-O1", "-g", "-std=c++17", "-fsanitize=thread", "-DMT_SIM_MAIN", *inc, src, "-o", exe, "-pthread"],
+                       capture_output=True, text=True)
+    if r.returncode != 0:
+        pytest.skip("ThreadSanitizer build not available: " + r.stderr[-300:])
+    env = dict(os.environ, TSAN_OPTIONS="exitcode=66 halt_on_error=1")
+    # ranks channels proto op count root spatial iters jitter_us slot_bytes slots [chain ...]
+    cases = {
+        "allreduce simple": "8 2 0 5 7001 0 0 10 5 2048 2",
+        "broadcast simple": "8 2 0 1 20001 3 0 10 5 2048 2",
+        "reduce simple": "8 2 0 2 20001 5 0 10 5 2048 2",
+        "multi-hop send/recv": "8 2 0 0 600 0 0 50 0 2048 2 0 1 2 3 4",
+        "allgather spatial": "4 4 0 3 5000 0 1 10 5 2048 2",
+        "reducescatter": "4 2 0 4 5000 0 0 10 5 2048 2",
+        "allreduce ll128": "8 2 1 5 7001 0 0 5 5 2048 2",
+    }
+    for name, args in cases.items():
+        p = subprocess.run([exe] + args.split(), env=env, capture_output=True, text=True, timeout=300)
+        assert p.returncode == 0, (name, p.stderr[-1500:])
+    # chain with sub-slot steps
+    p = subprocess.run([exe] + "8 2 0 1 50003 2 0 10 5 32768 2".split(), env=dict(env, MINTCCL_CHAIN_STEP_BYTES="4096"),
+                       capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0, p.stderr[-1500:]
