@@ -180,3 +180,42 @@ def test_profile_range_is_a_noop_without_cuda():
     with profile_range("y", enabled=False):
         ran.append(2)
     assert ran == [1, 2]
+
+
+def test_clock_sampler_against_a_fake_nvidia_smi(tmp_path, monkeypatch):
+    """The sampler only READS clocks (through ``nvidia-smi --query-gpu``).  A stand-in ``nvidia-smi`` on PATH prints
+    the CSV it would print under load with a power cap; the summary must report the median clock of the timed
+    region, the largest maximum clock and the active reasons."""
+    import os
+    import stat
+    import time
+    from mintccl_b200.utils.clocks import ClockSampler
+    fake = tmp_path / "nvidia-smi"
+    fake.write_text("""#!/usr/bin/env python3
+import datetime, sys, time
+assert any(a.startswith("--query-gpu=") for a in sys.argv) and "-lms" in sys.argv, sys.argv
+clocks = [1965, 1500, 1320, 1335, 1327, 1965]
+for i in range(400):
+    now = datetime.datetime.now().strftime("%Y/%m/%d %H:%M:%S.%f")[:-3]
+    cap = "Active" if 1 <= i % 6 <= 4 else "Not Active"
+    print(f"{now}, {clocks[i % 6]}, 1965, 950.5, Not Active, Not Active, Not Active, {cap}", flush=True)
+    time.sleep(0.01)
+""")
+    fake.chmod(fake.stat().st_mode | stat.S_IEXEC)
+    monkeypatch.setenv("PATH", str(tmp_path) + os.pathsep + os.environ["PATH"])
+    s = ClockSampler(0, period_ms=10).start()
+    time.sleep(0.15)
+    s.mark_begin()
+    time.sleep(0.4)
+    s.mark_end()
+    out = s.stop()
+    assert out["samples"] >= 10 and out["note"] == "samples inside the timed region"
+    assert out["sm_max_mhz"] == 1965.0 and 1320.0 <= out["sm_mhz"] <= 1965.0
+    assert out["reasons"] == ["sw_power_cap"]
+    # a region shorter than the sampling period falls back to the nearest samples
+    s2 = ClockSampler(0, period_ms=10).start()
+    time.sleep(0.2)
+    s2.mark_begin()
+    s2.mark_end()
+    out2 = s2.stop()
+    assert out2["samples"] >= 1 and "nearest" in out2["note"]
