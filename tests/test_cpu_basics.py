@@ -219,3 +219,24 @@ for i in range(400):
     s2.mark_end()
     out2 = s2.stop()
     assert out2["samples"] >= 1 and "nearest" in out2["note"]
+
+
+def test_bench_reference_arm_reports_unavailable():
+    """``bench.py --impl reference`` never runs the reference's GPU code (it faulted on its first call on this
+    hardware): rank 0 prints one JSON line with the reason, every rank exits 0."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for rank in (0, 1):
+        env = dict(os.environ, RANK=str(rank), WORLD_SIZE="2", LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT="29987")
+        r = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--gpus", "2", "--steps", "2",
+                            "--warmup", "1"], env=env, capture_output=True, text=True, timeout=120)
+        assert r.returncode == 0, r.stderr[-500:]
+        lines = [l for l in r.stdout.splitlines() if l.startswith("{")]
+        if rank == 0:
+            d = json.loads(lines[-1])
+            assert d["impl"] == "reference" and "illegal memory access" in d["unavailable"]
+        else:
+            assert not lines
