@@ -33,7 +33,7 @@ struct DirectArgs {
   int32_t op;
   int32_t root;
   int32_t variant;               // all-reduce: 0 two-shot, 1 one-shot; all-gather/all-to-all: 0 push, 1 pull;
-                                 // broadcast: 0 root pushes, 1 peers pull, 2 scatter + all-gather;
+                                 // broadcast: 0 root pushes, 1 peers pull, 2 pull + replicate (every rank reads 1/n from the root and stores it to all);
                                  // reduce: 0 root sums, 2 reduce-scatter + gather into the root
   int32_t nvls;                  // use multimem instructions
 };
