@@ -115,6 +115,7 @@ def lib():
     sig("mt_p2p", i32, vp, vp, i32, i32, vp, vp, u64, i32, i32)
     sig("mt_gemm", i32, vp, vp, vp, vp, i32, i32, i32, i32, i32)
     sig("mt_gemm_mxfp8", i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32)
+    sig("mt_sim_direct", i32, i32, i32, i32, C.c_uint32, i32, i32, i32, i32, u64)
     sig("mt_sim_fused", i32, i32, i32, i32, i32, i32, i32, i32, i32, C.c_uint32, i32, i32, i32, u64)
     sig("mt_sched_fused_tile", None, i32, i32, i32, i32, i32, i32, i32, i32, i32, ip)
     sig("mt_gemm_pair_error", i32)

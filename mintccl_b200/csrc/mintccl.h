@@ -129,6 +129,12 @@ void mt_sched_fused_tile(int mode, int t, int M, int N, int nranks, int rank, in
 int mt_sim_fused(int op, int nranks, int per, int nbs, int ngemm, int nextra, int pair, int iters, uint32_t seed,
                  int dead_rank, int slow_rank, int double_buffer, uint64_t timeout_ms);
 
+// Host model of the one-hop collectives (entry / exit barrier per CTA index, in-place buffers rewritten between
+// calls) and of the one-shot all-reduce (sim/sim_direct.cpp).  only_op: -1 random mix, 0 two-shot all-reduce,
+// 1 all-gather, 2 reduce-scatter, 3 all-to-all, 4 one-shot all-reduce.  Returns 0 ok, 1 wrong data, 2 a wait gave up.
+int mt_sim_direct(int nranks, int nctas, int iters, uint32_t seed, int only_op, int slow_rank, int dead_rank,
+                  int exit_barrier, uint64_t timeout_ms);
+
 // ---- topology ---------------------------------------------------------------------------------------
 // bw: n*n row-major matrix of link bandwidth (0 = no link).  Results are written to `out`.
 int mt_find_ring(const double* bw, int n, int* out);                          // returns length (n+1) or 0

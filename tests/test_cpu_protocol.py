@@ -314,3 +314,56 @@ def test_ring_protocols_under_thread_sanitizer(tmp_path):
     p = subprocess.run([exe] + "8 2 0 1 50003 2 0 10 5 32768 2".split(), env=dict(env, MINTCCL_CHAIN_STEP_BYTES="4096"),
                        capture_output=True, text=True, timeout=300)
     assert p.returncode == 0, p.stderr[-1500:]
+
+
+# ---- one-hop ("direct") collectives and the one-shot all-reduce (host model) -------------------------------
+def _direct(n, nctas, iters, seed=1, only_op=-1, slow=-1, dead=-1, exit_barrier=1, timeout_ms=4000):
+    from mintccl_b200 import _native as N
+    return N.lib().mt_sim_direct(n, nctas, iters, seed, only_op, slow, dead, exit_barrier, timeout_ms)
+
+
+@pytest.mark.parametrize("n", [2, 4, 8])
+def test_direct_protocols_random_mix_back_to_back(n):
+    """Two-shot all-reduce (in place), all-gather, reduce-scatter, all-to-all and the one-shot all-reduce in a
+    random order on the same buffers, which the 'user' rewrites between calls: every value read carries the
+    stamp of the expected call and rank; also with one rank far behind."""
+    assert _direct(n, 3, 300, seed=n) == 0
+    assert _direct(n, 2, 60, seed=10 + n, slow=0) == 0
+    for op in range(5):
+        assert _direct(n, 2, 40, seed=20 + op, only_op=op) == 0
+
+
+def test_direct_protocols_need_the_exit_barrier_and_report_dead_ranks():
+    # without the second barrier a rank returns while a slower peer still reads its buffer
+    assert _direct(4, 2, 30, seed=5, slow=0, exit_barrier=0) == 1
+    assert _direct(4, 2, 3, seed=6, dead=2, timeout_ms=300) == 2
+
+
+def test_direct_protocols_under_thread_sanitizer(tmp_path):
+    """The same model with a plain-memory payload under -fsanitize=thread: the per-CTA barriers must order the
+    users' rewrites, the pulls and the pushes of consecutive calls; without the exit barrier a race is reported."""
+    import shutil
+    import subprocess
+    gxx = shutil.which("g++")
+    if gxx is None:
+        pytest.skip("no g++")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    src = os.path.join(root, "mintccl_b200", "csrc", "sim", "sim_direct.cpp")
+    exe = str(tmp_path / "sim_direct_tsan")
+    r = subprocess.run([gxx, "-O1", "-g", "-std=c++17", "-fsanitize=thread", "-DMT_SIM_PLAIN_DATA", "-DMT_SIM_MAIN", src, "-o", exe,
+                        "-pthread"], capture_output=True, text=True)
+    if r.returncode != 0:
+        pytest.skip("ThreadSanitizer is not available: " + r.stderr[-300:])
+    env = dict(os.environ, TSAN_OPTIONS="exitcode=66 halt_on_error=1")
+
+    def run(*a):
+        p = subprocess.run([exe] + [str(x) for x in a], env=env, capture_output=True, text=True, timeout=300)
+        return p.returncode, p.stderr
+
+    # ranks, CTAs, calls, seed, operation (-1 mix), slow rank, dead rank, exit barrier, ms
+    for a in [(8, 3, 60, 1, -1, -1, -1, 1, 8000), (4, 2, 60, 2, -1, 0, -1, 1, 8000), (4, 2, 60, 3, 0, 1, -1, 1, 8000),
+              (4, 4, 100, 4, 4, 2, -1, 1, 8000)]:
+        rc, err = run(*a)
+        assert rc == 0, (a, err[-1500:])
+    rc, err = run(4, 2, 30, 5, 0, 0, -1, 0, 8000)
+    assert rc == 66 and "data race" in err
