@@ -45,6 +45,9 @@ def main() -> None:
     ap.add_argument("--sync", action="store_true",
                     help="follow every call with an 8-byte all-reduce of this library (a cross-rank fence), so that "
                          "pipelined algorithms cannot overlap consecutive calls; the fence's own time is subtracted")
+    ap.add_argument("--chain-steps", default="",
+                    help="comma list of MINTCCL_CHAIN_STEP_BYTES values (0 = whole slots) to try for this library's "
+                         "broadcast and reduce (they only matter for algo=ring over the Simple protocol)")
     ap.add_argument("--out", default="")
     a = ap.parse_args()
 
@@ -123,7 +126,14 @@ def main() -> None:
                 algos = a.algos.split(",") if impl == "mintccl" else ["nccl"]
                 ctas_list = [int(x) for x in a.ctas.split(",")] if (a.ctas and impl == "mintccl") else [0]
                 vlist = make_views(nbytes)
-                for algo, ctas in [(x, y) for x in algos for y in ctas_list]:
+                if a.chain_steps:
+                    os.environ.pop("MINTCCL_CHAIN_STEP_BYTES", None)  # no value left over from the previous combination
+                steps_list = ([int(x) for x in a.chain_steps.split(",")]
+                              if (a.chain_steps and impl == "mintccl" and coll in ("broadcast", "reduce")) else [None])
+                for algo, ctas, chain_step in [(x, y, z) for x in algos for y in ctas_list for z in steps_list]:
+                    if chain_step is not None:  # read by the native library at every call
+                        os.environ["MINTCCL_CHAIN_STEP_BYTES"] = str(chain_step)
+
                     def call():
                         i, o = vlist[state["k"] % len(vlist)]
                         state["k"] += 1
@@ -174,6 +184,8 @@ def main() -> None:
                     row = {"collective": coll, "bytes": nbytes, "impl": impl, "algo": algo, "ctas": ctas, "us": round(ms * 1e3, 2),
                            "algbw_GBps": round(nbytes / (ms * 1e-3) / 1e9, 3), "busbw_GBps": round(bus, 3), "n": n,
                            "dtype": a.dtype, "sync": bool(fence)}
+                    if chain_step is not None:
+                        row["chain_step"] = chain_step
                     results.append(row)
                     if rank == 0:
                         print(json.dumps(row), flush=True)
