@@ -76,7 +76,7 @@ int make_bf16_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K,
 // Row blocks per group of the plain GEMM's tile order.  Row-major order streams the whole of B through the
 // L2 once per wave of CTAs; when B does not fit beside A's rows (large N x K) a grouped order keeps a wave's
 // operands resident.  MINTCCL_GEMM_RASTER overrides (for tuning).
-static int raster_for(int M, int N, int K, int elem_bytes) {
+static int raster_for(int /*M*/, int N, int K, int elem_bytes) {
   if (const char* e = getenv("MINTCCL_GEMM_RASTER")) return atoi(e);
   const double b_bytes = (double)N * K * elem_bytes;
   return b_bytes > 48e6 ? 16 : 1;

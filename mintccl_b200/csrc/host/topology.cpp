@@ -12,8 +12,8 @@
 
 namespace {
 struct RingSearch {
-  const double* bw;
-  int n;
+  const double* bw = nullptr;
+  int n = 0;
   std::vector<int> path, best;
   std::vector<char> used;
   double best_bw = 0;
@@ -50,7 +50,9 @@ extern "C" int mt_find_ring(const double* bw, int n, int* out) {
     out[1] = 0;
     return 2;
   }
-  RingSearch s{bw, n};
+  RingSearch s;
+  s.bw = bw;
+  s.n = n;
   s.used.assign(n, 0);
   s.used[0] = 1;
   s.path.push_back(0);

@@ -333,6 +333,8 @@ int mt_sim_run(int nranks, int nchannels, int proto, int op, uint64_t count, int
           int s_fail = 0;
           if (proto == MT_PROTO_LL128) ring_body<HostLL128, SimF32, 1>(comms[r], mine, 0, ch, nchannels, &s_fail);
           else ring_body<HostSimple, SimF32, 1>(comms[r], mine, 0, ch, nchannels, &s_fail);
+          t_rng = nullptr;  // they point into this frame
+          t_env = nullptr;
         });
       }
     }
