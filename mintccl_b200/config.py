@@ -14,7 +14,7 @@ the Simple protocol, default one slot), ``MINTCCL_NO_LOCAL_COPY`` (one-rank comm
 from __future__ import annotations
 
 import os
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 
 WARP_SIZE = 32            # common.py:104
 VECTORIZED_BYTES = 16     # common.py:105

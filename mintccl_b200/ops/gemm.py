@@ -13,7 +13,6 @@ ops; its README (README.md:5) names fusion with other kernels as the purpose of 
 """
 from __future__ import annotations
 
-import ctypes as C
 from typing import List, Optional, Sequence, Union
 
 import torch

@@ -6,7 +6,7 @@ checks itself against NCCL on a GPU box only (e.g. 6_allgather.py:170-179).
 """
 from __future__ import annotations
 
-from typing import List, Optional, Sequence
+from typing import Optional, Sequence
 
 import torch
 import torch.distributed as dist

@@ -16,7 +16,7 @@ from __future__ import annotations
 import datetime
 import os
 import pickle
-from typing import Any, List, Optional
+from typing import Any, List
 
 
 class ControlPlane:
