@@ -1,0 +1,130 @@
+"""Which native entry point, algorithm variant and CTA count every collective resolves to, checked without a GPU:
+the communicator's own (slow-path) code runs on CPU tensors, with the native launch recorded instead of made and
+a slab of host memory standing in for the symmetric heap."""
+import pytest
+import torch
+
+from mintccl_b200 import Config
+from mintccl_b200 import _native as N
+from mintccl_b200.parallel.comm import Communicator
+
+
+class Recorder(Communicator):
+    def __init__(self, world=8, nvls=True, rank=0, **cfg):   # no device, no native communicator
+        self.cfg = Config.from_env(**cfg)
+        self.lib = N.lib()
+        self.world_size, self.rank, self.nlocal, self.emulated, self.nvls = world, rank, 1, False, nvls
+        self.device = 0
+        self._plans, self._rec_key, self._pending = {}, None, []
+        self.heap = torch.zeros(64 << 20, dtype=torch.uint8)
+        self.heap_base, self.user_off, self.heap_bytes = [self.heap.data_ptr()], 0, self.heap.numel()
+        self.ll_capacity = 200 << 10
+        self.ring = list(range(world))
+        self.calls = []
+        self._next = 0
+
+    def sym(self, numel, dtype=torch.float16):
+        nbytes = numel * torch.empty((), dtype=dtype).element_size()
+        off = (self._next + 255) // 256 * 256
+        self._next = off + nbytes
+        return self.heap[off:off + nbytes].view(dtype)
+
+    def _lists(self, t):
+        if t is None:
+            return None
+        return [t] if isinstance(t, torch.Tensor) else list(t)
+
+    def _run(self, fn, args):
+        self.calls.append((fn.__name__, args))
+        self._rec_key = None
+
+    def last(self):
+        name, a = self.calls[-1]
+        if name == "mt_direct":
+            return dict(fn=name, dtype=a[0], op=a[1], nbytes=a[6], root=a[7], variant=a[8], nvls=a[9], nctas=a[10])
+        if name == "mt_ring":
+            return dict(fn=name, proto=a[0], dtype=a[1], op=a[2], nbytes=a[5], root=a[6], spatial=a[7], nch=a[10])
+        return dict(fn=name, args=a)
+
+
+def test_allreduce_dispatch_by_size_and_memory():
+    c = Recorder(world=8)
+    small = torch.zeros(1000, dtype=torch.float16)
+    c.allreduce(small)
+    assert c.last()["fn"] == "mt_ll_allreduce"                      # <= MINTCCL_LL_MAX_BYTES: one-shot, any memory
+    big_plain = torch.zeros(1 << 20, dtype=torch.float16)
+    c.allreduce(big_plain)
+    l = c.last()
+    assert l["fn"] == "mt_ring" and l["op"] == N.OP_ALLREDUCE and l["proto"] == N.PROTO_SIMPLE   # ordinary tensor: ring
+    x = c.sym(1 << 20)
+    c.allreduce(x)
+    l = c.last()
+    assert l["fn"] == "mt_direct" and l["op"] == N.DOP_ALLREDUCE and l["nvls"] == 1 and l["nctas"] <= c.cfg.nvls_ctas
+    c2 = Recorder(world=2)
+    y = c2.sym(1 << 20)
+    c2.allreduce(y)
+    assert c2.last()["fn"] == "mt_direct" and c2.last()["nvls"] == 0            # two ranks: plain peer loads
+    c2.allreduce(y, algo="ring", proto="ll128")
+    assert c2.last()["fn"] == "mt_ring" and c2.last()["proto"] == N.PROTO_LL128
+    with pytest.raises(ValueError):
+        c2.allreduce(torch.zeros(1 << 20, dtype=torch.float16), algo="direct")  # needs symmetric memory
+    with pytest.raises(ValueError):
+        c2.allreduce(y, algo="oneshot")                                          # one-shot cannot run in place
+    with pytest.raises(TypeError):
+        c2.allreduce(torch.zeros(64, dtype=torch.int32))                         # reductions: float types only
+
+
+def test_allgather_reducescatter_dispatch():
+    c = Recorder(world=4)
+    buf = c.sym(4 * 65536).view(4, 65536)
+    c.allgather(buf)
+    l = c.last()
+    assert l["fn"] == "mt_direct" and l["op"] == N.DOP_ALLGATHER and l["nvls"] == 1 and l["nbytes"] == 65536 * 2
+    c.allgather(buf, algo="pull")
+    assert c.last()["variant"] == 1 and c.last()["nvls"] == 0
+    plain = torch.zeros(4, 1000, dtype=torch.float32)
+    c.allgather(plain, mode="spatial")
+    l = c.last()
+    assert l["fn"] == "mt_ring" and l["op"] == N.OP_ALLGATHER and l["spatial"] == 1 and l["nch"] % 4 == 0
+    c.reducescatter(buf)
+    l = c.last()
+    assert l["fn"] == "mt_direct" and l["op"] == N.DOP_REDUCESCATTER and l["nvls"] == 1
+    c.reducescatter(plain)
+    assert c.last()["fn"] == "mt_ring" and c.last()["op"] == N.OP_REDUCESCATTER
+    with pytest.raises(ValueError):
+        c.allgather(torch.zeros(3, 10))                                          # first dimension = world size
+    c.alltoall(buf, c.sym(4 * 65536).view(4, 65536))
+    assert c.last()["fn"] == "mt_direct" and c.last()["op"] == N.DOP_ALLTOALL
+
+
+def test_broadcast_and_reduce_dispatch():
+    c = Recorder(world=8)
+    x, out = c.sym(1 << 20), c.sym(1 << 20)
+    c.broadcast(x, root=3)
+    l = c.last()
+    assert l["fn"] == "mt_direct" and l["op"] == N.DOP_BROADCAST and l["nvls"] == 1 and l["variant"] == 2 and l["root"] == 3
+    c.broadcast(torch.zeros(100, dtype=torch.float16), root=1)
+    assert c.last()["fn"] == "mt_ring" and c.last()["proto"] == N.PROTO_LL128    # small, ordinary memory: LL128 chain
+    c.reduce(x, root=2, out=out)
+    l = c.last()
+    assert l["fn"] == "mt_direct" and l["op"] == N.DOP_REDUCE and l["nvls"] == 1 and l["variant"] == 2
+    c.reduce(x, root=2)                                                          # in place: the ring reduces in place
+    assert c.last()["fn"] == "mt_ring" and c.last()["op"] == N.OP_REDUCE
+    with pytest.raises(ValueError):
+        c.reduce(x, root=2, algo="direct")                                       # direct reduce needs a separate output
+    c2 = Recorder(world=2)
+    y, o2 = c2.sym(1 << 20), c2.sym(1 << 20)
+    c2.broadcast(y)
+    assert c2.last()["fn"] == "mt_direct" and c2.last()["nvls"] == 0 and c2.last()["variant"] == 0   # root pushes once
+    c2.reduce(y, out=o2)
+    assert c2.last()["fn"] == "mt_direct" and c2.last()["variant"] == 0
+
+
+def test_one_rank_world_always_takes_the_copy_path():
+    c = Recorder(world=1)
+    x, out = c.sym(4096), c.sym(4096)
+    c.allreduce(x, out=out)
+    assert c.last()["fn"] == "mt_ring" and c.last()["proto"] == N.PROTO_SIMPLE   # the native side turns it into a copy
+    n0 = len(c.calls)
+    c.broadcast(x)
+    assert len(c.calls) == n0                                                    # nothing to do
