@@ -6,6 +6,9 @@ same names and adds the ones its roadmap asks for (README.md:57 "fine-grained co
 algorithm, protocol, channel count, FIFO depth, wait time limit, heap size.  Booleans are parsed properly:
 the reference's ``bool(os.getenv(...))`` (common.py:113,118) is true for the string ``"0"``.
 
+``MINTCCL_TUNING_FILE`` names a table of measured choices that overrides the size thresholds of the built-in policy
+(:mod:`mintccl_b200.tuning`).
+
 Read by the native library itself, at every call (tuning switches, not part of :class:`Config`):
 ``MINTCCL_GEMM_PAIR`` (0: single-CTA GEMM kernels instead of CTA pairs), ``MINTCCL_GEMM_RASTER`` (row blocks per
 group of the plain GEMM's tile order), ``MINTCCL_CHAIN_STEP_BYTES`` (bytes per FIFO step of chain operations over

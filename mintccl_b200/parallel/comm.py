@@ -26,6 +26,7 @@ import torch
 from .. import _native as N
 from ..config import Config
 from ..topology import find_ring, find_route, uniform_topology
+from ..tuning import TuningTable
 from .rendezvous import ControlPlane, SingleControl, connect, local_rank_default
 
 TensorOrList = Union[torch.Tensor, Sequence[torch.Tensor]]
@@ -74,6 +75,7 @@ class Communicator:
         self._registered: dict = {}
         self._plans: dict = {}
         self._rec_key = None
+        self._tuning = TuningTable.from_env()   # MINTCCL_TUNING_FILE: measured choices, or None
         self.emulated = _emulate > 0
         if self.emulated:
             self.control = SingleControl()
@@ -435,6 +437,23 @@ class Communicator:
             return algo
         return self.cfg.algo if self.cfg.algo in known else "auto"
 
+    def _tuned(self, collective: str, nbytes: int, algo: Optional[str], nch: Optional[int], symmetric: bool,
+               tensors=(), unit: Optional[int] = None):
+        """Where the caller left ``algo`` and ``nch`` open and a tuning table (``MINTCCL_TUNING_FILE``) has a row for
+        this collective, rank count, size and kind of memory, that row decides; otherwise nothing changes.  A row
+        that asks for NVLS is skipped for buffers NVLS cannot take (``unit``, the bytes one multimem stream moves,
+        and every pointer must be multiples of 16)."""
+        table = getattr(self, "_tuning", None)
+        if table is None or algo is not None or nch is not None:
+            return algo, nch
+        hit = table.lookup(collective, self.world_size, nbytes, symmetric)
+        if hit is None:
+            return algo, nch
+        if hit[0].startswith("nvls") and (not self.nvls or (unit if unit is not None else nbytes) % 16
+                                          or any(t.data_ptr() % 16 for t in tensors)):
+            return algo, nch
+        return hit
+
     def _want_nvls(self, nbytes: int, tensors) -> bool:
         """In-switch reduction / replication pays off from four ranks on (with two ranks the switch only
         adds a hop: measured 394 against 606 GB/s for a 256 MiB all-reduce) and needs 16-byte alignment."""
@@ -483,8 +502,9 @@ class Communicator:
         outs = self._lists(out) or ins
         nbytes = ins[0].numel() * ins[0].element_size()
         dt = _dtype_code(ins[0], True)
-        algo = self._algo(algo, "allreduce")
         in_off, out_off = self._symm_off_all(ins), self._symm_off_all(outs)
+        algo, nch = self._tuned("allreduce", nbytes, algo, nch, in_off is not None and out_off is not None, ins + outs)
+        algo = self._algo(algo, "allreduce")
         if self.world_size == 1:
             algo = "ring"  # a single rank: the ring kernel degenerates to a local copy
         if algo == "auto":
@@ -537,8 +557,9 @@ class Communicator:
         if B * n != outs[0].numel() * outs[0].element_size():
             raise ValueError("contribution and buffer sizes do not match")
         dt = _dtype_code(outs[0], False)
-        algo = self._algo(algo, "allgather")
         out_off = self._symm_off_all(outs)
+        algo, nch = self._tuned("allgather", B * n, algo, nch, out_off is not None, ins + outs, B)
+        algo = self._algo(algo, "allgather")
         if n == 1:
             algo = "ring"
         if algo == "auto":
@@ -581,8 +602,9 @@ class Communicator:
         outs = self._lists(out) or [i[r] for i, r in zip(ins, ranks)]
         B = outs[0].numel() * outs[0].element_size()
         dt = _dtype_code(ins[0], True)
-        algo = self._algo(algo, "reducescatter")
         in_off = self._symm_off_all(ins)
+        algo, nch = self._tuned("reducescatter", B * n, algo, nch, in_off is not None, ins + outs, B)
+        algo = self._algo(algo, "reducescatter")
         if n == 1:
             algo = "ring"
         if algo == "auto":
@@ -614,8 +636,9 @@ class Communicator:
         dt = _dtype_code(ts[0], False)
         if self.world_size == 1:
             return
-        algo = self._algo(algo, "broadcast")
         off = self._symm_off_all(ts)
+        algo, nch = self._tuned("broadcast", nbytes, algo, nch, off is not None, ts)
+        algo = self._algo(algo, "broadcast")
         if algo == "auto":
             # A wide pipelined ring (algo="ring", 48+ channels) moves more bytes per second when broadcasts
             # follow each other back to back (631 against 528 GB/s at 1 GiB on 4 GPUs), but a single broadcast
@@ -656,10 +679,12 @@ class Communicator:
         outs = self._lists(out) or ins
         nbytes = ins[0].numel() * ins[0].element_size()
         dt = _dtype_code(ins[0], True)
+        off = self._symm_off_all(ins)
+        separate = all(o.data_ptr() != i.data_ptr() for i, o in zip(ins, outs))
+        algo, nch = self._tuned("reduce", nbytes, algo, nch, off is not None and separate, ins + outs)
         algo = self._algo(algo, "reduce")
         if self.world_size == 1:
             algo = "ring"
-        off = self._symm_off_all(ins)
         if algo == "auto":
             separate = all(o.data_ptr() != i.data_ptr() for i, o in zip(ins, outs))
             if off is not None and separate and self._want_nvls(nbytes, ins + outs):

@@ -128,3 +128,67 @@ def test_one_rank_world_always_takes_the_copy_path():
     n0 = len(c.calls)
     c.broadcast(x)
     assert len(c.calls) == n0                                                    # nothing to do
+
+
+def test_tuning_table_overrides_the_policy_only_where_it_applies(tmp_path, monkeypatch):
+    from mintccl_b200.tuning import TuningTable
+    table = TuningTable([
+        {"collective": "allreduce", "nranks": 8, "max_bytes": 1 << 20, "algo": "direct", "nch": 48},
+        {"collective": "allreduce", "nranks": 8, "max_bytes": 1 << 26, "algo": "nvls", "nch": 16},
+        {"collective": "broadcast", "nranks": 8, "max_bytes": 1 << 30, "algo": "ring", "nch": 64},
+        {"collective": "allgather", "nranks": 8, "max_bytes": 1 << 30, "symmetric": False, "algo": "ring", "nch": 24},
+    ])
+    c = Recorder(world=8)
+    c._tuning = table
+    x = c.sym(1 << 18)                                   # 512 KiB, symmetric
+    c.allreduce(x)
+    assert (c.last()["fn"], c.last()["nvls"], c.last()["nctas"]) == ("mt_direct", 0, 48)
+    y = c.sym(1 << 21)                                   # 4 MiB
+    c.allreduce(y)
+    assert (c.last()["nvls"], c.last()["nctas"]) == (1, 16)
+    c.allreduce(y, nch=8)                                # the caller's own choice stands
+    assert c.last()["nctas"] == 8
+    c.allreduce(y, algo="ring")
+    assert c.last()["fn"] == "mt_ring"
+    c.allreduce(torch.zeros(1 << 20, dtype=torch.float16))   # ordinary memory: the symmetric rows do not apply
+    assert c.last()["fn"] == "mt_ring"
+    odd = c.sym((1 << 21) + 4)[: (1 << 21) + 4]          # byte count not a multiple of 16: the NVLS row is skipped
+    c.allreduce(odd)
+    assert c.last()["fn"] == "mt_direct" and c.last()["nvls"] == 0
+    c.broadcast(y, root=1)
+    assert c.last()["fn"] == "mt_ring" and c.last()["nch"] == 64
+    plain = torch.zeros(8, 4096, dtype=torch.float32)
+    c.allgather(plain)
+    assert c.last()["fn"] == "mt_ring" and c.last()["nch"] == 24
+    c4 = Recorder(world=4)
+    c4._tuning = table                                    # no rows for 4 ranks: built-in policy
+    z = c4.sym(1 << 18)
+    c4.allreduce(z)
+    assert c4.last()["nvls"] == 1
+    # file round trip and the environment variable
+    path = str(tmp_path / "tuning.json")
+    table.dump(path)
+    monkeypatch.setenv("MINTCCL_TUNING_FILE", path)
+    again = TuningTable.from_env()
+    assert again.lookup("allreduce", 8, 1 << 19) == ("direct", 48) and again.lookup("allreduce", 8, 1 << 27) is None
+    monkeypatch.delenv("MINTCCL_TUNING_FILE")
+    assert TuningTable.from_env() is None
+
+
+def test_tuning_table_from_sweep_rows():
+    from mintccl_b200.tuning import TuningTable
+    rows = []
+    for nbytes, best in ((1 << 10, ("ll", 0)), (1 << 14, ("ll", 0)), (1 << 20, ("direct", 64)), (1 << 24, ("nvls", 32)), (1 << 28, ("nvls", 32))):
+        for algo, ctas in (("ll", 0), ("direct", 64), ("nvls", 32), ("ring", 64)):
+            rows.append({"collective": "allreduce", "bytes": nbytes, "impl": "mintccl", "algo": algo, "ctas": ctas,
+                         "us": 10.0 if (algo, ctas) == best else 20.0, "n": 8})
+        rows.append({"collective": "allreduce", "bytes": nbytes, "impl": "nccl", "algo": "nccl", "ctas": 0, "us": 1.0, "n": 8})
+    t = TuningTable.from_sweep(rows)
+    got = t.rows[("allreduce", 8, True)]
+    assert [(r["algo"], r["nch"]) for r in got] == [("ll", None), ("direct", 64), ("nvls", 32)]     # neighbours merged, NCCL ignored
+    assert t.lookup("allreduce", 8, 1 << 12) == ("ll", None)
+    assert t.lookup("allreduce", 8, 1 << 20) == ("direct", 64)
+    assert t.lookup("allreduce", 8, 1 << 26) == ("nvls", 32)
+    assert t.lookup("allreduce", 8, 1 << 29) is None and t.lookup("allreduce", 4, 1 << 20) is None
+    # boundaries sit between the measured sizes (geometric mean)
+    assert got[0]["max_bytes"] == int((float(1 << 14) * (1 << 20)) ** 0.5)
