@@ -24,3 +24,12 @@ def pytest_collection_modifyitems(config, items):
             item.add_marker(skip_gpu)
         if "multigpu" in item.keywords and ngpu < 2:
             item.add_marker(skip_multi)
+
+
+def pytest_sessionstart(session):
+    """A fresh checkout has no built library (it is not kept in the history): build it once, for sm_100a, before the
+    first test needs it.  nvcc cross-compiles, so this works without a GPU; an existing build is left alone."""
+    from mintccl_b200 import _native
+    if not _native._LIB_PATH.exists():
+        from mintccl_b200 import build
+        build.build()
