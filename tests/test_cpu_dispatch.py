@@ -192,3 +192,24 @@ def test_tuning_table_from_sweep_rows():
     assert t.lookup("allreduce", 8, 1 << 29) is None and t.lookup("allreduce", 4, 1 << 20) is None
     # boundaries sit between the measured sizes (geometric mean)
     assert got[0]["max_bytes"] == int((float(1 << 14) * (1 << 20)) ** 0.5)
+
+
+def test_emulated_world_takes_one_tensor_per_rank():
+    """The single-GPU emulation passes lists (one tensor per emulated rank) through the same selection code."""
+    n = 4
+    c = Recorder(world=n)
+    c.emulated, c.nlocal = True, n
+    c.heap_base = [c.heap.data_ptr()] * n           # every emulated rank's heap: same offsets
+    xs = [c.sym(1 << 16) for _ in range(n)]
+    # the ranks' tensors sit at different offsets of one slab here, so they do not count as symmetric: ring
+    c.allreduce(xs)
+    assert c.last()["fn"] == "mt_ring" and c.last()["nch"] <= 148 // n
+    bufs = [torch.zeros(n, 1024, dtype=torch.float16) for _ in range(n)]
+    c.allgather(bufs)
+    assert c.last()["fn"] == "mt_ring" and c.last()["op"] == N.OP_ALLGATHER
+    c.reducescatter(bufs, out=[torch.zeros(1024, dtype=torch.float16) for _ in range(n)])
+    assert c.last()["op"] == N.OP_REDUCESCATTER
+    c.broadcast([torch.zeros(100) for _ in range(n)], root=2)
+    assert c.last()["op"] == N.OP_BROADCAST and c.last()["root"] == 2
+    c.reduce([torch.zeros(100) for _ in range(n)], root=1, out=[torch.zeros(100) for _ in range(n)])
+    assert c.last()["op"] == N.OP_REDUCE
