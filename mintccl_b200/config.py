@@ -9,6 +9,10 @@ the reference's ``bool(os.getenv(...))`` (common.py:113,118) is true for the str
 ``MINTCCL_TUNING_FILE`` names a table of measured choices that overrides the size thresholds of the built-in policy
 (:mod:`mintccl_b200.tuning`).
 
+``MINTCCL_TOPO_FILE`` / ``MINTCCL_TOPO_DISCOVER`` / ``MINTCCL_TOPO_MEASURE`` choose the link map behind the ring and
+the routes (default: uniform, which is exact on an NVSwitch node); ``MINTCCL_RING``, ``MINTCCL_RING_SEED`` and
+``MINTCCL_ROUTE=ring`` override the result.
+
 Read by the native library itself, at every call (tuning switches, not part of :class:`Config`):
 ``MINTCCL_GEMM_PAIR`` (0: single-CTA GEMM kernels instead of CTA pairs), ``MINTCCL_GEMM_RASTER`` (row blocks per
 group of the plain GEMM's tile order), ``MINTCCL_CHAIN_STEP_BYTES`` (bytes per FIFO step of chain operations over

@@ -24,8 +24,8 @@ from typing import List, Optional, Sequence, Union
 import torch
 
 from .. import _native as N
-from ..config import Config
-from ..topology import find_ring, find_route, uniform_topology
+from ..config import Config, env_bool
+from ..topology import find_ring, find_route, get_topology, uniform_topology
 from ..tuning import TuningTable
 from .rendezvous import ControlPlane, SingleControl, connect, local_rank_default
 
@@ -225,6 +225,26 @@ class Communicator:
             raise RuntimeError(f"multicast bind failed on some rank ({N.last_error()}); cannot continue safely")
         self.nvls = True
 
+    def _topology(self):
+        """Link map behind the ring and the routes.  An NVSwitch node (every HGX B200 board) is uniform: every
+        pair at full bandwidth; that is the default and needs no probing.  ``MINTCCL_TOPO_FILE`` names a cached
+        topology (the ``topo.json`` of :func:`mintccl_b200.topology.get_topology`, as in the reference,
+        topology.py:128-149), discovered and written by rank 0 if the file does not exist yet;
+        ``MINTCCL_TOPO_DISCOVER=1`` discovers without a file (peer-access matrix from the driver, bandwidths
+        measured with ``MINTCCL_TOPO_MEASURE=1``).  Rank 0 decides and shares the result, so every rank derives
+        the same ring and routes."""
+        topo = getattr(self, "_topo", None)
+        if topo is not None:
+            return topo
+        path = os.environ.get("MINTCCL_TOPO_FILE", "")
+        if path or env_bool("MINTCCL_TOPO_DISCOVER", False):
+            topo = get_topology(path, ndev=self.world_size) if self.rank == 0 else None
+            topo = self.control.bcast(topo, root=0)
+        else:
+            topo = uniform_topology(self.world_size)
+        self._topo = topo
+        return topo
+
     def _choose_ring(self) -> List[int]:
         n = self.world_size
         env = os.environ.get("MINTCCL_RING")
@@ -237,7 +257,7 @@ class Communicator:
         if seed is not None:
             g = torch.Generator().manual_seed(int(seed))
             return torch.randperm(n, generator=g).tolist()
-        ring = find_ring(uniform_topology(n))
+        ring = find_ring(self._topology())
         return ring[:n] if ring else list(range(n))
 
     def set_ring(self, ring: Sequence[int]) -> None:
@@ -836,7 +856,7 @@ class Communicator:
                 pos = (pos + 1) % self.world_size
                 out.append(self.ring[pos])
             return out
-        r = find_route(src, dst, uniform_topology(self.world_size))
+        r = find_route(src, dst, self._topology())
         return r or [src, dst]
 
     def sync(self, proto: Optional[str] = None) -> None:

@@ -213,3 +213,45 @@ def test_emulated_world_takes_one_tensor_per_rank():
     assert c.last()["op"] == N.OP_BROADCAST and c.last()["root"] == 2
     c.reduce([torch.zeros(100) for _ in range(n)], root=1, out=[torch.zeros(100) for _ in range(n)])
     assert c.last()["op"] == N.OP_REDUCE
+
+
+def test_ring_and_routes_follow_the_topology(tmp_path, monkeypatch):
+    """Default: the uniform NVSwitch topology (direct routes).  MINTCCL_TOPO_FILE: a cached link map, here the
+    hybrid cube mesh of an 8-GPU board without a switch, gives a ring over existing links only and multi-hop
+    routes between GPUs that share no link; MINTCCL_RING / MINTCCL_RING_SEED / MINTCCL_ROUTE still override."""
+    import json
+    from mintccl_b200.parallel.rendezvous import SingleControl
+    for k in ("MINTCCL_TOPO_FILE", "MINTCCL_TOPO_DISCOVER", "MINTCCL_RING", "MINTCCL_RING_SEED", "MINTCCL_ROUTE"):
+        monkeypatch.delenv(k, raising=False)
+    c = Recorder(world=8)
+    c.control = SingleControl()
+    assert sorted(c._choose_ring()) == list(range(8)) and c.route(0, 5) == [0, 5]
+    # DGX-1 style hybrid cube mesh: two fully connected quads {0..3}, {4..7} plus the links i <-> i + 4
+    links = {i: [] for i in range(8)}
+    for q in (0, 4):
+        for a in range(q, q + 4):
+            for b in range(q, q + 4):
+                if a != b:
+                    links[a].append((b, 50.0))
+    for i in range(4):
+        links[i].append((i + 4, 25.0))
+        links[i + 4].append((i, 25.0))
+    path = tmp_path / "topo.json"
+    path.write_text(json.dumps({str(k): v for k, v in links.items()}))
+    monkeypatch.setenv("MINTCCL_TOPO_FILE", str(path))
+    m = Recorder(world=8)
+    m.control = SingleControl()
+    ring = m._choose_ring()
+    assert sorted(ring) == list(range(8))
+    has = lambda a, b: any(d == b for d, _ in links[a])  # noqa: E731
+    assert all(has(ring[i], ring[(i + 1) % 8]) for i in range(8)), ring       # every hop of the ring is a real link
+    r = m.route(0, 5)
+    assert r[0] == 0 and r[-1] == 5 and len(r) == 3 and all(has(a, b) for a, b in zip(r, r[1:]))   # via 1 or 4
+    monkeypatch.setenv("MINTCCL_RING", "7,6,5,4,3,2,1,0")
+    assert m._choose_ring() == [7, 6, 5, 4, 3, 2, 1, 0]
+    monkeypatch.delenv("MINTCCL_RING")
+    monkeypatch.setenv("MINTCCL_RING_SEED", "3")
+    assert sorted(m._choose_ring()) == list(range(8))
+    m.ring = [0, 1, 2, 3, 7, 6, 5, 4]
+    monkeypatch.setenv("MINTCCL_ROUTE", "ring")
+    assert m.route(2, 6) == [2, 3, 7, 6]
