@@ -240,3 +240,30 @@ def test_bench_reference_arm_reports_unavailable():
             assert d["impl"] == "reference" and "illegal memory access" in d["unavailable"]
         else:
             assert not lines
+
+
+def test_ctypes_signatures_match_the_c_header():
+    """Every function of csrc/mintccl.h (and of the no-alloc entry point's header) has a ctypes signature with the
+    same number of parameters: a mismatch would otherwise only show as garbage arguments on a GPU."""
+    import os
+    import re
+    from mintccl_b200 import _native as N
+    lib = N.lib()
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "mintccl_b200", "csrc")
+    text = open(os.path.join(root, "mintccl.h")).read()
+    text = re.sub(r"//[^\n]*", "", text)
+    decls = re.findall(r"\b(mt_\w+)\s*\(([^;{]*?)\)\s*;", text, flags=re.S)
+    assert len(decls) > 40
+    missing, wrong = [], []
+    for name, params in decls:
+        params = params.strip()
+        n = 0 if params in ("", "void") else len([p for p in params.split(",") if p.strip()])
+        fn = getattr(lib, name, None)
+        assert fn is not None, f"{name} is declared but not exported"
+        if fn.argtypes is None:
+            missing.append(name)
+        elif len(fn.argtypes) != n:
+            wrong.append((name, n, len(fn.argtypes)))
+    assert not wrong, wrong
+    # functions without a ctypes signature would be called with default int conversions: none may be left
+    assert not missing, missing
