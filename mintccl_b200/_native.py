@@ -103,13 +103,18 @@ def lib():
     sig("mt_comm_nlocal", i32, vp)
     sig("mt_ipc_export", i32, vp, C.c_char_p, C.POINTER(u64), C.POINTER(u64))
     sig("mt_ipc_open", vp, C.c_char_p)
+    sig("mt_ipc_close", i32, C.c_char_p)
     sig("mt_ipc_close_all", i32)
+    sig("mt_reg_start", i32, vp, cp, cp)
+    sig("mt_reg_stop", i32, vp)
+    sig("mt_reg_share", i32, cp, cp, i32, C.c_char_p, u64, C.POINTER(u64), i32)
+    sig("mt_reg_unshare", i32, cp, cp, i32, C.c_char_p, i32)
     sig("mt_fd_listen", i32, cp)
     sig("mt_fd_accept", i32, i32, ip, i32)
     sig("mt_fd_send", i32, cp, i32, i32, i32)
     sig("mt_fd_close", None, i32)
     sig("mt_ring", i32, vp, vp, i32, i32, i32, pp, pp, u64, i32, i32, ip, i32, i32)
-    sig("mt_direct", i32, vp, vp, i32, i32, pp, pp, u64, u64, u64, i32, i32, i32, i32)
+    sig("mt_direct", i32, vp, vp, i32, i32, i32, pp, pp, C.POINTER(u64), C.POINTER(u64), u64, u64, u64, i32, i32, i32, i32)
     sig("mt_ll_allreduce", i32, vp, vp, i32, pp, pp, u64)
     sig("mt_ll_capacity", u64, vp)
     sig("mt_p2p", i32, vp, vp, i32, i32, vp, vp, u64, i32, i32)
@@ -147,4 +152,11 @@ def ptr_array(ptrs) -> "C.Array":
     arr = (C.c_void_p * MT_MAX_RANKS)()
     for i, p in enumerate(ptrs):
         arr[i] = p
+    return arr
+
+
+def u64_array(vals) -> "C.Array":
+    arr = (C.c_uint64 * MT_MAX_RANKS)()
+    for i, v in enumerate(vals):
+        arr[i] = v
     return arr

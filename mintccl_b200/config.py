@@ -92,6 +92,9 @@ class Config:
     wait_timeout_ms: int = 10000
     heap_kind: str = "auto"               # vmm | ipc | auto
     nvls: str = "auto"                    # on | off | auto
+    auto_register: bool = True            # MINTCCL_AUTO_REGISTER: share ordinary tensors with the peers (CUDA IPC) on
+                                          # first use so that they take the one-hop kernels; off: FIFO ring unless
+                                          # the tensor was passed to Communicator.share()
     debug: str = "warn"                   # warn | info | trace
     # thresholds of the automatic choice (bytes)
     ll_max_bytes: int = 32 << 10
@@ -143,6 +146,7 @@ class Config:
             wait_timeout_ms=env_int("MINTCCL_WAIT_TIMEOUT_MS", 10000),
             heap_kind=env_str("MINTCCL_HEAP", "auto", ("vmm", "ipc", "auto")),
             nvls=env_str("MINTCCL_NVLS", "auto", ("on", "off", "auto")),
+            auto_register=env_bool("MINTCCL_AUTO_REGISTER", True),
             debug=env_str("MINTCCL_DEBUG", "warn", ("warn", "info", "trace")),
             ll_max_bytes=env_int("MINTCCL_LL_MAX_BYTES", 32 << 10),
             ll128_max_bytes=env_int("MINTCCL_LL128_MAX_BYTES", 512 << 10),

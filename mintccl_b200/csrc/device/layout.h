@@ -54,12 +54,22 @@ struct MtConnCtrl {
   uint64_t _pad1[14];
 };
 
-// Cross-rank barrier slot: arrive[p] is written remotely by rank p, epoch is local.
+// Cross-rank barrier slot: arrive[p] is written remotely by rank p, epoch is local.  pin[p] / pout[p] carry
+// what rank p announced with its arrival at the entry barrier of a one-hop collective: where ITS input and
+// output live in MY address space (a plain address, or MT_PUB_HEAP_TAG | offset inside p's heap).  They are
+// written before arrive[p] (release) and read after it (acquire), and not overwritten before the exit barrier
+// of the same call has passed on both sides.
 struct MtBarSlot {
   uint64_t arrive[MT_MAX_RANKS];
   uint64_t epoch;
   uint64_t _pad[7];
+  uint64_t pin[MT_MAX_RANKS];
+  uint64_t _pad1[8];
+  uint64_t pout[MT_MAX_RANKS];
+  uint64_t _pad2[8];
 };
+// Announced buffer addresses: bit 63 set means "offset into the announcing rank's symmetric heap".
+#define MT_PUB_HEAP_TAG 0x8000000000000000ull
 
 // Point-to-point signal words between a pair of ranks (direct send/recv handshakes).
 struct MtSigSlot {
@@ -109,7 +119,7 @@ struct MtDevComm {
 #ifdef __cplusplus
 static_assert(sizeof(MtStatus) == 64, "MtStatus is one 64-byte record");
 static_assert(sizeof(MtConnCtrl) == 256, "MtConnCtrl is two 128-byte lines");
-static_assert(sizeof(MtBarSlot) == 128, "MtBarSlot is one 128-byte line");
+static_assert(sizeof(MtBarSlot) == 384, "MtBarSlot is three 128-byte lines");
 static_assert(sizeof(MtSigSlot) == 128, "MtSigSlot is one 128-byte line");
 #endif
 

@@ -240,4 +240,50 @@ __device__ __forceinline__ bool rank_barrier(const MtDevComm& c, int slot, int* 
   return *s_fail == 0;
 }
 
+// The same barrier, used as the entry barrier of a one-hop collective: with its arrival every rank also
+// announces where its input and output buffers are, as seen from each peer.  Thread t < nranks talks to rank
+// t, so `pub_in` / `pub_out` are per-thread values: what to announce to rank threadIdx.x (an address valid in
+// that rank's address space, or MT_PUB_HEAP_TAG | offset inside my heap, or 0 for "none").
+// On return `s_in[q]` / `s_out[q]` (shared memory, MT_MAX_RANKS entries) hold rank q's buffers as addresses
+// that are valid here; entry `rank` holds `local_in` / `local_out`.  This is what lets the one-hop kernels
+// run on ordinary device allocations registered through CUDA IPC, and on heap tensors whose offsets differ
+// between ranks: nothing but this exchange depends on where a peer's buffer is.
+__device__ __forceinline__ bool rank_barrier_xchg(const MtDevComm& c, int slot, int* s_fail, uint64_t pub_in,
+                                                  uint64_t pub_out, const void* local_in, void* local_out,
+                                                  const uint8_t** s_in, uint8_t** s_out) {
+  __syncthreads();
+  MtBarSlot* mine = (MtBarSlot*)(c.heap[c.rank] + c.L.bar_off) + slot;
+  const int t = threadIdx.x;
+  if (t == 0) *s_fail = 0;
+  __syncthreads();
+  if (t < c.nranks) {
+    uint64_t e = load64(&mine->epoch) + 1;
+    fence_acq_rel_sys();
+    MtBarSlot* theirs = (MtBarSlot*)(c.heap[t] + c.L.bar_off) + slot;
+    if (t != c.rank) {
+      store64_relaxed_sys(&theirs->pin[c.rank], pub_in);
+      store64_relaxed_sys(&theirs->pout[c.rank], pub_out);
+    }
+    store64_release_sys(&theirs->arrive[c.rank], e);
+    const uint64_t* w = &mine->arrive[t];
+    bool ok = bounded_wait(
+        c, [&] { return load64_acquire_sys(w) >= e; }, MT_ERR_TIMEOUT_BARRIER, slot, MT_WHERE_BARRIER, e, 0,
+        (const volatile uint64_t*)w);
+    if (!ok) {
+      atomicExch(s_fail, 1);
+    } else if (t == c.rank) {
+      s_in[t] = (const uint8_t*)local_in;
+      s_out[t] = (uint8_t*)local_out;
+    } else {
+      const uint64_t vi = load64_relaxed_sys(&mine->pin[t]), vo = load64_relaxed_sys(&mine->pout[t]);
+      s_in[t] = (vi & MT_PUB_HEAP_TAG) ? c.heap[t] + (vi & ~MT_PUB_HEAP_TAG) : (const uint8_t*)(uintptr_t)vi;
+      s_out[t] = (vo & MT_PUB_HEAP_TAG) ? c.heap[t] + (vo & ~MT_PUB_HEAP_TAG) : (uint8_t*)(uintptr_t)vo;
+    }
+  }
+  __syncthreads();
+  if (t == 0 && *s_fail == 0) store64(&mine->epoch, load64(&mine->epoch) + 1);
+  __syncthreads();
+  return *s_fail == 0;
+}
+
 }  // namespace mt

@@ -8,6 +8,8 @@
 
 #include "../mintccl.h"
 
+struct MtRegService;  // host/regsrv.cpp
+
 struct MtComm {
   int rank = 0, nranks = 1, device = 0, nlocal = 1;
   bool emulated = false;
@@ -36,6 +38,7 @@ struct MtComm {
   int ll_grid = 4;
   uint64_t gemm_epoch[2] = {0, 0};         // call counters of the fused GEMM flag sets (AG, RS)
   std::vector<void*> emu_allocs;
+  MtRegService* reg = nullptr;             // thread that maps the peers' ordinary allocations on request
 };
 
 namespace mthost {

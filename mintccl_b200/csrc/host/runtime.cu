@@ -247,6 +247,7 @@ void mt_comm_destroy(MtComm* c) {
   if (!c) return;
   cudaSetDevice(c->device);
   cudaDeviceSynchronize();
+  mt_reg_stop(c);
   auto p_unmap = drv<decltype(&cuMemUnmap)>("cuMemUnmap");
   auto p_release = drv<decltype(&cuMemRelease)>("cuMemRelease");
   auto p_free = drv<decltype(&cuMemAddressFree)>("cuMemAddressFree");
@@ -453,8 +454,15 @@ int mt_comm_clear_status(MtComm* c) {
 }
 
 // ---- registration of ordinary allocations ---------------------------------------------------------
+// One mapping per CUDA IPC handle and process (the runtime refuses to open a handle twice), counted so that the
+// users of a handle (Communicator.register, the registration services of several communicators) can close
+// independently.
+struct IpcMapping {
+  void* base;
+  int refs;
+};
 static std::mutex g_ipc_mu;
-static std::map<std::string, void*> g_ipc_cache;
+static std::map<std::string, IpcMapping> g_ipc_cache;
 
 int mt_ipc_export(const void* ptr, unsigned char handle[64], uint64_t* offset, uint64_t* alloc_bytes) {
   DRV(cuMemGetAddressRange);
@@ -473,22 +481,37 @@ void* mt_ipc_open(const unsigned char handle[64]) {
   std::lock_guard<std::mutex> lk(g_ipc_mu);
   std::string key((const char*)handle, 64);
   auto it = g_ipc_cache.find(key);
-  if (it != g_ipc_cache.end()) return it->second;
+  if (it != g_ipc_cache.end()) {
+    ++it->second.refs;
+    return it->second.base;
+  }
   cudaIpcMemHandle_t h;
   memcpy(&h, handle, 64);
   void* p = nullptr;
   cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
   if (e != cudaSuccess) {
+    cudaGetLastError();
     fail(std::string("cudaIpcOpenMemHandle: ") + cudaGetErrorString(e));
     return nullptr;
   }
-  g_ipc_cache[key] = p;
+  g_ipc_cache[key] = IpcMapping{p, 1};
   return p;
+}
+
+int mt_ipc_close(const unsigned char handle[64]) {
+  std::lock_guard<std::mutex> lk(g_ipc_mu);
+  auto it = g_ipc_cache.find(std::string((const char*)handle, 64));
+  if (it == g_ipc_cache.end()) return 0;
+  if (--it->second.refs <= 0) {
+    cudaIpcCloseMemHandle(it->second.base);
+    g_ipc_cache.erase(it);
+  }
+  return 0;
 }
 
 int mt_ipc_close_all(void) {
   std::lock_guard<std::mutex> lk(g_ipc_mu);
-  for (auto& kv : g_ipc_cache) cudaIpcCloseMemHandle(kv.second);
+  for (auto& kv : g_ipc_cache) cudaIpcCloseMemHandle(kv.second.base);
   g_ipc_cache.clear();
   return 0;
 }
@@ -545,27 +568,47 @@ int mt_ring(MtComm* c, void* stream, int proto, int dtype, int op, const void* c
   return 0;
 }
 
-int mt_direct(MtComm* c, void* stream, int dtype, int op, const void* const* in, void* const* out, uint64_t in_off,
-              uint64_t out_off, uint64_t nbytes, int root, int variant, int nvls, int nctas) {
+int mt_direct(MtComm* c, void* stream, int dtype, int out_dtype, int op, const void* const* in, void* const* out,
+              const uint64_t* pub_in, const uint64_t* pub_out, uint64_t mc_in_off, uint64_t mc_out_off, uint64_t nbytes,
+              int root, int variant, int nvls, int nctas) {
   if (check_ready(c)) return -1;
   if (nctas < 1 || nctas > 148) return fail("nctas out of range");
   if (c->emulated && nctas * c->nlocal > 148) return fail("emulated world: CTAs * ranks must be <= 148");
   if (nvls && !c->mc) return fail("NVLS requested but no multicast mapping");
+  if (nvls && ((nbytes | mc_in_off | mc_out_off) & 15))
+    return fail("NVLS needs heap offsets and a byte count that are multiples of 16");
   if (nbytes % mt::dtype_size(dtype)) return fail("byte count is not a multiple of the element size");
+  if (root < 0 || root >= c->nranks) return fail("bad root");
+  if (dtype != out_dtype) {
+    if (op != mt::DOP_REDUCESCATTER && op != mt::DOP_ALLREDUCE && op != mt::DOP_REDUCE)
+      return fail("only reducing collectives convert between element types");
+    if (nvls || (op == mt::DOP_REDUCE && variant == 2))
+      return fail("the NVLS variants do not convert between element types");
+    const bool widen = (dtype == mt::DT_F16 || dtype == mt::DT_BF16) && out_dtype == mt::DT_F32;
+    const bool narrow = dtype == mt::DT_F32 && (out_dtype == mt::DT_F16 || out_dtype == mt::DT_BF16);
+    if (!widen && !narrow) return fail("conversions: fp16/bf16 -> fp32 and fp32 -> fp16/bf16");
+  }
+  if (!c->emulated && c->nranks > 1 && (!pub_in || !pub_out)) return fail("peer views of the buffers are missing");
   mt::DirectArgs a;
   memset(&a, 0, sizeof(a));
   for (int lr = 0; lr < c->nlocal; ++lr) {
     a.in[lr] = in ? in[lr] : nullptr;
     a.out[lr] = out ? out[lr] : nullptr;
   }
-  a.in_off = in_off;
-  a.out_off = out_off;
+  a.pub_local = c->emulated || c->nranks == 1;
+  if (!a.pub_local)
+    for (int p = 0; p < c->nranks; ++p) {
+      a.pub_in[p] = pub_in[p];
+      a.pub_out[p] = pub_out[p];
+    }
+  a.mc_in_off = mc_in_off;
+  a.mc_out_off = mc_out_off;
   a.nbytes = nbytes;
   a.op = op;
   a.root = root;
   a.variant = variant;
   a.nvls = nvls;
-  cudaError_t e = mt::launch_direct(dtype, c->d_comms, a, nctas, c->nlocal, (cudaStream_t)stream);
+  cudaError_t e = mt::launch_direct(dtype, out_dtype, c->d_comms, a, nctas, c->nlocal, (cudaStream_t)stream);
   if (e != cudaSuccess) return fail(std::string("direct launch: ") + cudaGetErrorString(e));
   mthost::stat_add(nvls ? mthost::ST_NVLS : mthost::ST_DIRECT, nbytes);
   return 0;

@@ -4,19 +4,29 @@
 #include "p2p_engine.cuh"
 
 namespace mt {
-template <class T>
+template <class TI, class TO>
 static cudaError_t go_direct(const MtDevComm* comms, const DirectArgs& a, int nctas, int nlocal, cudaStream_t s) {
   DirectArgs args = a;
   void* p[] = {(void*)&comms, (void*)&args};
-  return launch_any((const void*)direct_kernel<T, kDirectThreads>, dim3(nctas, nlocal), dim3(kDirectThreads), p, s,
+  return launch_any((const void*)direct_kernel<TI, TO, kDirectThreads>, dim3(nctas, nlocal), dim3(kDirectThreads), p, s,
                     nlocal > 1);
 }
-cudaError_t launch_direct(int dtype, const MtDevComm* comms, const DirectArgs& a, int nctas, int nlocal, cudaStream_t s) {
+// dtype: elements of the input; out_dtype: elements of the output (the same, or fp32 for a 16-bit input, or a
+// 16-bit type for an fp32 input: the sum is rounded once, into the output type).
+cudaError_t launch_direct(int dtype, int out_dtype, const MtDevComm* comms, const DirectArgs& a, int nctas, int nlocal,
+                          cudaStream_t s) {
+  if (dtype != out_dtype) {
+    if (dtype == DT_F16 && out_dtype == DT_F32) return go_direct<F16, F32>(comms, a, nctas, nlocal, s);
+    if (dtype == DT_BF16 && out_dtype == DT_F32) return go_direct<BF16, F32>(comms, a, nctas, nlocal, s);
+    if (dtype == DT_F32 && out_dtype == DT_F16) return go_direct<F32, F16>(comms, a, nctas, nlocal, s);
+    if (dtype == DT_F32 && out_dtype == DT_BF16) return go_direct<F32, BF16>(comms, a, nctas, nlocal, s);
+    return cudaErrorInvalidValue;
+  }
   switch (dtype) {
-    case DT_F32: return go_direct<F32>(comms, a, nctas, nlocal, s);
-    case DT_F16: return go_direct<F16>(comms, a, nctas, nlocal, s);
-    case DT_BF16: return go_direct<BF16>(comms, a, nctas, nlocal, s);
-    default: return go_direct<U8>(comms, a, nctas, nlocal, s);
+    case DT_F32: return go_direct<F32, F32>(comms, a, nctas, nlocal, s);
+    case DT_F16: return go_direct<F16, F16>(comms, a, nctas, nlocal, s);
+    case DT_BF16: return go_direct<BF16, BF16>(comms, a, nctas, nlocal, s);
+    default: return go_direct<U8, U8>(comms, a, nctas, nlocal, s);
   }
 }
 cudaError_t launch_p2p(const MtDevComm* comms, const P2pArgs& a, int nctas, int nlocal, cudaStream_t s) {

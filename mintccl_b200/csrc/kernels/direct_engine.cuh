@@ -7,10 +7,20 @@
 // ("two-shot"), all-to-all pushes block p to peer p.  With NVLS the switch does the summing
 // (multimem.ld_reduce) and the replication (multimem.st).
 //
-// Buffers that peers touch must live in the symmetric heap (same offset on every rank).  CTA i of
-// every rank works on the same slice of the message, so the only cross-rank dependencies are between
-// CTAs with equal index; each CTA brackets its work with a bounded cross-rank barrier on its slot.
+// Buffers that peers touch must be mapped by the peers: tensors of the symmetric heap (any offset), or
+// ordinary device allocations registered through CUDA IPC.  Where they are is announced rank to rank with
+// the arrival at the entry barrier (rank_barrier_xchg), so the kernels only ever see "rank q's input /
+// output as an address valid here".  The NVLS variants go through the multicast alias of the heap and
+// therefore need heap tensors at the same offset on every rank.  CTA i of every rank works on the same
+// slice of the message, so the only cross-rank dependencies are between CTAs with equal index; each CTA
+// brackets its work with a bounded cross-rank barrier on its slot.
+//
+// The reducing operations are templated on the element type of the input and of the output: 16-bit input
+// with fp32 output and fp32 input with 16-bit output sum in fp32 registers and round once, into the output
+// type (the reference sums fp16 into fp16 only, primitive.py:230-247; other types are on its roadmap,
+// README.md:58-60).  Byte counts and offsets are in input bytes throughout.
 #pragma once
+#include <type_traits>
 #include "../device/proto_ll128.cuh"
 
 namespace mt {
@@ -27,43 +37,97 @@ enum DirectOp : int {
 struct DirectArgs {
   const void* in[MT_MAX_RANKS];  // local view of the input, per local rank
   void* out[MT_MAX_RANKS];       // local view of the output, per local rank
-  uint64_t in_off;               // heap offset of the input when peers read it
-  uint64_t out_off;              // heap offset of the output when peers write it
-  uint64_t nbytes;               // AG/RS/A2A: bytes per shard; others: message bytes
+  uint64_t pub_in[MT_MAX_RANKS];   // what this rank announces to peer p as its input (see rank_barrier_xchg)
+  uint64_t pub_out[MT_MAX_RANKS];  // ... and as its output
+  uint64_t mc_in_off;            // NVLS: heap offset of the input (the same on every rank)
+  uint64_t mc_out_off;           // NVLS: heap offset of the output
+  uint64_t nbytes;               // AG/RS/A2A: bytes per shard; others: message bytes (input bytes)
   int32_t op;
   int32_t root;
   int32_t variant;               // all-reduce: 0 two-shot, 1 one-shot; all-gather/all-to-all: 0 push, 1 pull;
                                  // broadcast: 0 root pushes, 1 peers pull, 2 pull + replicate (every rank reads 1/n from the root and stores it to all);
-                                 // reduce: 0 root sums, 2 reduce-scatter + gather into the root
+                                 // reduce: 0 root sums, 2 NVLS reduce-scatter + gather into the root, 3 the others sum and store into the root
   int32_t nvls;                  // use multimem instructions
+  int32_t pub_local;             // one address space (emulated world): announce in[] / out[] themselves
 };
+
+// Element types of a reducing kernel: input TI, output TO.
+template <class TI, class TO>
+struct CastInfo {
+  static constexpr bool kSame = std::is_same<TI, TO>::value;
+  static constexpr int kSI = (int)sizeof(typename TI::elem), kSO = (int)sizeof(typename TO::elem);
+  static_assert(kSame || (kSI == 2 && kSO == 4) || (kSI == 4 && kSO == 2), "16-bit <-> fp32 only");
+  // output byte offset of the element that starts at input byte offset o
+  static __device__ __forceinline__ uint64_t out_off(uint64_t o) { return kSame ? o : (kSI == 2 ? o * 2 : o / 2); }
+  // alignment the output address of a 16-byte input vector needs
+  static constexpr uint64_t kOutAlignMask = (!kSame && kSI == 4) ? 7 : 15;
+};
+
+// Store the fp32 sums of one 16-byte input vector at input offset o of the message whose output starts at
+// `out_base`, rounded once into TO.
+template <class TI, class TO, bool REMOTE>
+__device__ __forceinline__ void store_acc(uint8_t* out_base, uint64_t o, const Acc128<TI>& acc) {
+  using CI = CastInfo<TI, TO>;
+  if constexpr (CI::kSame) {
+    const u128 r = acc.get();
+    if (REMOTE) store128_relaxed_sys(out_base + o, r);
+    else *reinterpret_cast<u128*>(out_base + o) = r;
+  } else if constexpr (CI::kSI == 2) {  // 8 sums -> 32 bytes of fp32
+    u128 lo, hi;
+    lo.x = F32::pack(acc.f);
+    lo.y = F32::pack(acc.f + 2);
+    hi.x = F32::pack(acc.f + 4);
+    hi.y = F32::pack(acc.f + 6);
+    uint8_t* d = out_base + o * 2;
+    if (REMOTE) {
+      store128_relaxed_sys(d, lo);
+      store128_relaxed_sys(d + 16, hi);
+    } else {
+      *reinterpret_cast<u128*>(d) = lo;
+      *reinterpret_cast<u128*>(d + 16) = hi;
+    }
+  } else {  // 4 sums -> 8 bytes of a 16-bit type
+    const uint64_t r = TO::pack(acc.f);
+    uint8_t* d = out_base + o / 2;
+    if (REMOTE) store64_relaxed_sys(d, r);
+    else *reinterpret_cast<uint64_t*>(d) = r;
+  }
+}
 
 static constexpr int kDirectUnroll = 4;
 
 // Alignment of the boundaries between the slices of different CTAs.
 static constexpr uint64_t kSplitAlignDirect = 128;
 
-// out[i] = sum over ranks of peer_in[rank][i] for message bytes [byte_lo, byte_hi); the result is
-// stored to `local_out` and, if PUSH, to the same offset of every peer's output.  Offset o of the
-// message lands at local_out + (o - local_base).  FIXED_ORDER sums ranks 0..n-1 in that order on every
-// rank (bitwise identical results everywhere, needed when several ranks reduce the same element);
-// otherwise each rank starts at itself so that the n readers spread over the n memories.
-template <class T, int NTHREADS, bool PUSH, bool FIXED_ORDER, int NR>
-__device__ __forceinline__ void pull_reduce_range_n(const MtDevComm& c, uint64_t in_off, uint64_t out_off,
-                                                    uint8_t* local_out, uint64_t byte_lo, uint64_t byte_hi,
-                                                    uint64_t local_base) {
+// Every rank's input and output as addresses valid on this rank (filled by the entry barrier).
+struct PeerBufs {
+  const uint8_t* const* in;
+  uint8_t* const* out;
+};
+
+// out[i] = sum over ranks of in_q[i] for message bytes [byte_lo, byte_hi); the result is stored to
+// `local_out` and, if PUSH, to the same offset of every peer's output.  Input offset o of the message lands
+// at local_out + out_off(o - local_base).  FIXED_ORDER sums ranks 0..n-1 in that order on every rank (bitwise
+// identical results everywhere, needed when several ranks reduce the same element); otherwise each rank
+// starts at itself so that the n readers spread over the n memories.
+template <class TI, class TO, int NTHREADS, bool PUSH, bool FIXED_ORDER, int NR>
+__device__ __forceinline__ void pull_reduce_range_n(const MtDevComm& c, const PeerBufs& P, uint8_t* local_out,
+                                                    uint64_t byte_lo, uint64_t byte_hi, uint64_t local_base) {
+  using CI = CastInfo<TI, TO>;
   // NR > 0: the rank count is a compile-time constant, so the loop over peers unrolls and all
   // NR x kU remote loads of a thread are in flight together
   const int n = NR > 0 ? NR : c.nranks;
   // vectors per thread and pass: bounded so that NR x kU 16-byte registers fit without spilling
   constexpr int kU = NR >= 8 ? 2 : kDirectUnroll;
-  // 16-byte vectors need every address involved to be 16-byte aligned; heaps are, so only the offsets
-  // count (a shard offset rank * B is unaligned when B is not a multiple of 16).
-  const bool vec_ok = (((in_off + byte_lo) | (PUSH ? out_off + byte_lo : 0) |
-                        (uint64_t)(uintptr_t)(local_out + (byte_lo - local_base))) & 15) == 0;
-  const uint64_t nvec = vec_ok ? (byte_hi - byte_lo) >> 4 : 0;
+  // 16-byte vectors need every address involved to be aligned
+  uint64_t mis = (uint64_t)(uintptr_t)(local_out + CI::out_off(byte_lo - local_base)) & CI::kOutAlignMask;
+  for (int p = 0; p < n; ++p) {
+    mis |= (uint64_t)(uintptr_t)(P.in[p] + byte_lo) & 15;
+    if (PUSH && p != c.rank) mis |= (uint64_t)(uintptr_t)(P.out[p] + CI::out_off(byte_lo)) & CI::kOutAlignMask;
+  }
+  const uint64_t nvec = mis == 0 ? (byte_hi - byte_lo) >> 4 : 0;
   for (uint64_t base = 0; base < nvec; base += (uint64_t)NTHREADS * kU) {
-    Acc128<T> acc[kU];
+    Acc128<TI> acc[kU];
     if (NR > 0) {
       u128 v[NR > 0 ? NR : 1][kU];
 #pragma unroll
@@ -72,7 +136,7 @@ __device__ __forceinline__ void pull_reduce_range_n(const MtDevComm& c, uint64_t
 #pragma unroll
         for (int u = 0; u < kU; ++u) {
           const uint64_t i = base + (uint64_t)u * NTHREADS + threadIdx.x;
-          if (i < nvec) v[d][u] = load128_relaxed_sys(c.heap[p] + in_off + byte_lo + (i << 4));
+          if (i < nvec) v[d][u] = load128_relaxed_sys(P.in[p] + byte_lo + (i << 4));
         }
       }
 #pragma unroll
@@ -90,7 +154,7 @@ __device__ __forceinline__ void pull_reduce_range_n(const MtDevComm& c, uint64_t
 #pragma unroll
         for (int u = 0; u < kU; ++u) {
           const uint64_t i = base + (uint64_t)u * NTHREADS + threadIdx.x;
-          if (i < nvec) v[u] = load128_relaxed_sys(c.heap[p] + in_off + byte_lo + (i << 4));
+          if (i < nvec) v[u] = load128_relaxed_sys(P.in[p] + byte_lo + (i << 4));
         }
         if (d == 0) {
 #pragma unroll
@@ -105,46 +169,42 @@ __device__ __forceinline__ void pull_reduce_range_n(const MtDevComm& c, uint64_t
     for (int u = 0; u < kU; ++u) {
       const uint64_t i = base + (uint64_t)u * NTHREADS + threadIdx.x;
       if (i < nvec) {
-        const u128 r = acc[u].get();
         const uint64_t o = byte_lo + (i << 4);
-        *reinterpret_cast<u128*>(local_out + (o - local_base)) = r;
+        store_acc<TI, TO, false>(local_out, o - local_base, acc[u]);
         if (PUSH) {
-          for (int d = 1; d < n; ++d) {
-            const int p = (c.rank + d) % n;
-            store128_relaxed_sys(c.heap[p] + out_off + o, r);
-          }
+          for (int d = 1; d < n; ++d) store_acc<TI, TO, true>(P.out[(c.rank + d) % n], o, acc[u]);
         }
       }
     }
   }
   // what the vectors did not cover (a tail of < 16 bytes, or everything when unaligned), element-wise
-  using E = typename T::elem;
+  using EI = typename TI::elem;
+  using EO = typename TO::elem;
   const uint64_t done = byte_lo + (nvec << 4);
-  const uint64_t nel = (byte_hi - done) / sizeof(E);
+  const uint64_t nel = (byte_hi - done) / sizeof(EI);
   for (uint64_t e_i = threadIdx.x; e_i < nel; e_i += NTHREADS) {
-    const uint64_t o = done + e_i * sizeof(E);
+    const uint64_t o = done + e_i * sizeof(EI);
     float acc = 0.f;
     for (int d = 0; d < n; ++d) {
       const int p = FIXED_ORDER ? d : (c.rank + d) % n;
-      const E x = *reinterpret_cast<const volatile E*>(c.heap[p] + in_off + o);
-      acc += elem_to_float<T>(x);
+      const EI x = *reinterpret_cast<const volatile EI*>(P.in[p] + o);
+      acc += elem_to_float<TI>(x);
     }
-    const E e = float_to_elem<T>(acc);
-    *reinterpret_cast<E*>(local_out + (o - local_base)) = e;
+    const EO e = float_to_elem<TO>(acc);
+    *reinterpret_cast<EO*>(local_out + CI::out_off(o - local_base)) = e;
     if (PUSH)
-      for (int d = 1; d < n; ++d) *reinterpret_cast<volatile E*>(c.heap[(c.rank + d) % n] + out_off + o) = e;
+      for (int d = 1; d < n; ++d) *reinterpret_cast<volatile EO*>(P.out[(c.rank + d) % n] + CI::out_off(o)) = e;
   }
 }
 
-template <class T, int NTHREADS, bool PUSH, bool FIXED_ORDER>
-__device__ __forceinline__ void pull_reduce_range(const MtDevComm& c, uint64_t in_off, uint64_t out_off,
-                                                  uint8_t* local_out, uint64_t byte_lo, uint64_t byte_hi,
-                                                  uint64_t local_base) {
+template <class TI, class TO, int NTHREADS, bool PUSH, bool FIXED_ORDER>
+__device__ __forceinline__ void pull_reduce_range(const MtDevComm& c, const PeerBufs& P, uint8_t* local_out,
+                                                  uint64_t byte_lo, uint64_t byte_hi, uint64_t local_base) {
   switch (c.nranks) {
-    case 2: pull_reduce_range_n<T, NTHREADS, PUSH, FIXED_ORDER, 2>(c, in_off, out_off, local_out, byte_lo, byte_hi, local_base); break;
-    case 4: pull_reduce_range_n<T, NTHREADS, PUSH, FIXED_ORDER, 4>(c, in_off, out_off, local_out, byte_lo, byte_hi, local_base); break;
-    case 8: pull_reduce_range_n<T, NTHREADS, PUSH, FIXED_ORDER, 8>(c, in_off, out_off, local_out, byte_lo, byte_hi, local_base); break;
-    default: pull_reduce_range_n<T, NTHREADS, PUSH, FIXED_ORDER, 0>(c, in_off, out_off, local_out, byte_lo, byte_hi, local_base); break;
+    case 2: pull_reduce_range_n<TI, TO, NTHREADS, PUSH, FIXED_ORDER, 2>(c, P, local_out, byte_lo, byte_hi, local_base); break;
+    case 4: pull_reduce_range_n<TI, TO, NTHREADS, PUSH, FIXED_ORDER, 4>(c, P, local_out, byte_lo, byte_hi, local_base); break;
+    case 8: pull_reduce_range_n<TI, TO, NTHREADS, PUSH, FIXED_ORDER, 8>(c, P, local_out, byte_lo, byte_hi, local_base); break;
+    default: pull_reduce_range_n<TI, TO, NTHREADS, PUSH, FIXED_ORDER, 0>(c, P, local_out, byte_lo, byte_hi, local_base); break;
   }
 }
 
@@ -192,7 +252,7 @@ __device__ __forceinline__ u128 mc_ld_reduce<U8>(const void* p) { return load128
 // NVLS loops with several multimem operations in flight per thread (a multimem round trip through the
 // switch is several microseconds, so the depth matters more than for plain peer loads).
 static constexpr int kNvlsUnroll = 4;
-// dst[i] = sum over all ranks of mc_src[i]; dst is local memory, or the multicast alias when TO_MC.
+// dst[i] = sum over all ranks of mc_src[i]; dst is local or peer memory, or the multicast alias when TO_MC.
 template <class T, int NTHREADS, bool TO_MC>
 __device__ __forceinline__ void nvls_reduce_range(const uint8_t* mc_src, uint8_t* dst, uint64_t nvec) {
   for (uint64_t base = 0; base < nvec; base += (uint64_t)NTHREADS * kNvlsUnroll) {
@@ -231,12 +291,17 @@ __device__ __forceinline__ void nvls_bcast_range(const uint8_t* src, uint8_t* mc
   }
 }
 
-// dst_off of every peer (and local_dst unless skip_local) = src, reading each vector once.
+// Bytes [lo, lo + nbytes) of every peer's output (and of the local one unless skip_local) = src, reading
+// each vector once.  Any alignment: 16-byte vectors when src and every destination allow it, bytes otherwise
+// and for the tail.
 template <int NTHREADS>
-__device__ __forceinline__ void bcast_fanout(const MtDevComm& c, const uint8_t* src, uint64_t dst_off, uint8_t* local_dst,
+__device__ __forceinline__ void bcast_fanout(const MtDevComm& c, const uint8_t* src, const PeerBufs& P, uint64_t lo,
                                              uint64_t nbytes, bool skip_local) {
   const int n = c.nranks;
-  const uint64_t nvec = nbytes >> 4;
+  uint64_t mis = (uint64_t)(uintptr_t)src & 15;
+  for (int p = 0; p < n; ++p) mis |= (uint64_t)(uintptr_t)(P.out[p] + lo) & 15;
+  const uint64_t nvec = mis == 0 ? nbytes >> 4 : 0;
+  uint8_t* local_dst = P.out[c.rank] + lo;
   for (uint64_t base = 0; base < nvec; base += (uint64_t)NTHREADS * kDirectUnroll) {
     u128 v[kDirectUnroll];
 #pragma unroll
@@ -248,50 +313,64 @@ __device__ __forceinline__ void bcast_fanout(const MtDevComm& c, const uint8_t* 
     for (int u = 0; u < kDirectUnroll; ++u) {
       const uint64_t i = base + (uint64_t)u * NTHREADS + threadIdx.x;
       if (i < nvec) {
-        for (int d = 1; d < n; ++d) store128_relaxed_sys(c.heap[(c.rank + d) % n] + dst_off + (i << 4), v[u]);
+        for (int d = 1; d < n; ++d) store128_relaxed_sys(P.out[(c.rank + d) % n] + lo + (i << 4), v[u]);
         if (!skip_local) *reinterpret_cast<u128*>(local_dst + (i << 4)) = v[u];
       }
     }
   }
+  for (uint64_t o = (nvec << 4) + threadIdx.x; o < nbytes; o += NTHREADS) {
+    const uint8_t b = *reinterpret_cast<const volatile uint8_t*>(src + o);
+    for (int d = 1; d < n; ++d) *reinterpret_cast<volatile uint8_t*>(P.out[(c.rank + d) % n] + lo + o) = b;
+    if (!skip_local) local_dst[o] = b;
+  }
 }
 
-template <class T, int NTHREADS>
-__device__ void direct_body(const MtDevComm& c, const DirectArgs& a, int lr, int cta, int ncta, int* s_fail) {
+template <class TI, class TO, int NTHREADS>
+__device__ void direct_body(const MtDevComm& c, const DirectArgs& a, int lr, int cta, int ncta, int* s_fail,
+                            const uint8_t** s_in, uint8_t** s_out) {
+  using T = TI;
+  constexpr bool kSame = CastInfo<TI, TO>::kSame;
   const int n = c.nranks, me = c.rank;
   const uint8_t* in = (const uint8_t*)a.in[lr];
   uint8_t* out = (uint8_t*)a.out[lr];
   const uint64_t B = a.nbytes;
 
-  if (!rank_barrier(c, cta, s_fail)) return;
+  {
+    const int t = threadIdx.x & (MT_MAX_RANKS - 1);
+    const uint64_t vin = a.pub_local ? (uint64_t)(uintptr_t)in : a.pub_in[t];
+    const uint64_t vout = a.pub_local ? (uint64_t)(uintptr_t)out : a.pub_out[t];
+    if (!rank_barrier_xchg(c, cta, s_fail, vin, vout, in, out, s_in, s_out)) return;
+  }
+  const PeerBufs P{s_in, s_out};
 
   switch (a.op) {
     case DOP_ALLGATHER: {
-      const MtRange r = mt_split(B, ncta, cta, kSplitAlignDirect);
-      if (r.hi > r.lo) {
-        if (a.nvls) {
-          // one multimem store lands in every rank's output (mine included)
-          uint8_t* mdst = c.mc + a.out_off + (uint64_t)me * B;
-          const uint64_t nvec = (r.hi - r.lo) >> 4;
-          nvls_bcast_range<NTHREADS>(in + r.lo, mdst + r.lo, nvec);
-          // a tail cannot be sent with 16-byte multimem stores
-          for (uint64_t o = r.lo + (nvec << 4) + threadIdx.x; o < r.hi; o += NTHREADS)
-            for (int p = 0; p < n; ++p) *(volatile uint8_t*)(c.heap[p] + a.out_off + (uint64_t)me * B + o) = in[o];
-        } else if (a.variant == 0) {
-          for (int d = 0; d < n; ++d) {
-            const int p = (me + d) % n;
-            uint8_t* dst = (p == me ? out : c.heap[p] + a.out_off) + (uint64_t)me * B;
-            if (p == me && in == dst) continue;
-            copy_range<NTHREADS, false, true>(in + r.lo, dst + r.lo, r.hi - r.lo);
-          }
-        } else {
-          for (int d = 0; d < n; ++d) {
-            const int p = (me + d) % n;
-            if (p == me) {
-              if (in != out + (uint64_t)me * B) copy_range<NTHREADS, false, false>(in + r.lo, out + (uint64_t)me * B + r.lo, r.hi - r.lo);
-            } else {
-              // in_off == ~0: every rank's contribution is row `rank` of its own (symmetric) output buffer
-              const uint64_t src_off = a.in_off == ~0ull ? a.out_off + (uint64_t)p * B : a.in_off;
-              copy_range<NTHREADS, true, false>(c.heap[p] + src_off + r.lo, out + (uint64_t)p * B + r.lo, r.hi - r.lo);
+      if constexpr (kSame) {
+        const MtRange r = mt_split(B, ncta, cta, kSplitAlignDirect);
+        if (r.hi > r.lo) {
+          if (a.nvls) {
+            // one multimem store lands in every rank's output (mine included)
+            uint8_t* mdst = c.mc + a.mc_out_off + (uint64_t)me * B;
+            const uint64_t nvec = (r.hi - r.lo) >> 4;
+            nvls_bcast_range<NTHREADS>(in + r.lo, mdst + r.lo, nvec);
+            // a tail cannot be sent with 16-byte multimem stores
+            for (uint64_t o = r.lo + (nvec << 4) + threadIdx.x; o < r.hi; o += NTHREADS)
+              for (int p = 0; p < n; ++p) *(volatile uint8_t*)(P.out[p] + (uint64_t)me * B + o) = in[o];
+          } else if (a.variant == 0) {
+            for (int d = 0; d < n; ++d) {
+              const int p = (me + d) % n;
+              uint8_t* dst = P.out[p] + (uint64_t)me * B;
+              if (p == me && in == dst) continue;
+              copy_range<NTHREADS, false, true>(in + r.lo, dst + r.lo, r.hi - r.lo);
+            }
+          } else {
+            for (int d = 0; d < n; ++d) {
+              const int p = (me + d) % n;
+              if (p == me) {
+                if (in != out + (uint64_t)me * B) copy_range<NTHREADS, false, false>(in + r.lo, out + (uint64_t)me * B + r.lo, r.hi - r.lo);
+              } else {
+                copy_range<NTHREADS, true, false>(P.in[p] + r.lo, out + (uint64_t)p * B + r.lo, r.hi - r.lo);
+              }
             }
           }
         }
@@ -299,16 +378,18 @@ __device__ void direct_body(const MtDevComm& c, const DirectArgs& a, int lr, int
       break;
     }
     case DOP_ALLTOALL: {
-      const MtRange r = mt_split(B, ncta, cta, kSplitAlignDirect);
-      if (r.hi > r.lo) {
-        for (int d = 0; d < n; ++d) {
-          const int p = (me + d) % n;
-          if (a.variant == 0) {  // push block p of my input into slot `me` of p's output
-            uint8_t* dst = (p == me ? out : c.heap[p] + a.out_off) + (uint64_t)me * B;
-            copy_range<NTHREADS, false, true>(in + (uint64_t)p * B + r.lo, dst + r.lo, r.hi - r.lo);
-          } else {  // pull block `me` of p's input into slot p of my output
-            const uint8_t* src = (p == me ? in : c.heap[p] + a.in_off) + (uint64_t)me * B;
-            copy_range<NTHREADS, true, false>(src + r.lo, out + (uint64_t)p * B + r.lo, r.hi - r.lo);
+      if constexpr (kSame) {
+        const MtRange r = mt_split(B, ncta, cta, kSplitAlignDirect);
+        if (r.hi > r.lo) {
+          for (int d = 0; d < n; ++d) {
+            const int p = (me + d) % n;
+            if (a.variant == 0) {  // push block p of my input into slot `me` of p's output
+              uint8_t* dst = P.out[p] + (uint64_t)me * B;
+              copy_range<NTHREADS, false, true>(in + (uint64_t)p * B + r.lo, dst + r.lo, r.hi - r.lo);
+            } else {  // pull block `me` of p's input into slot p of my output
+              const uint8_t* src = P.in[p] + (uint64_t)me * B;
+              copy_range<NTHREADS, true, false>(src + r.lo, out + (uint64_t)p * B + r.lo, r.hi - r.lo);
+            }
           }
         }
       }
@@ -318,14 +399,16 @@ __device__ void direct_body(const MtDevComm& c, const DirectArgs& a, int lr, int
       const MtRange r = mt_split(B, ncta, cta, kSplitAlignDirect);
       if (r.hi > r.lo) {
         const uint64_t so = (uint64_t)me * B;
-        if (a.nvls) {
-          const uint8_t* msrc = c.mc + a.in_off + so;
-          const uint64_t nvec = (r.hi - r.lo) >> 4;
-          nvls_reduce_range<T, NTHREADS, false>(msrc + r.lo, out + r.lo, nvec);
-          if (r.lo + (nvec << 4) < r.hi)
-            pull_reduce_range<T, NTHREADS, false, false>(c, a.in_off, 0, out, so + r.lo + (nvec << 4), so + r.hi, so);
+        if (kSame && a.nvls) {
+          if constexpr (kSame) {
+            const uint8_t* msrc = c.mc + a.mc_in_off + so;
+            const uint64_t nvec = (r.hi - r.lo) >> 4;
+            nvls_reduce_range<T, NTHREADS, false>(msrc + r.lo, out + r.lo, nvec);
+            if (r.lo + (nvec << 4) < r.hi)
+              pull_reduce_range<TI, TO, NTHREADS, false, false>(c, P, out, so + r.lo + (nvec << 4), so + r.hi, so);
+          }
         } else {
-          pull_reduce_range<T, NTHREADS, false, false>(c, a.in_off, 0, out, so + r.lo, so + r.hi, so);
+          pull_reduce_range<TI, TO, NTHREADS, false, false>(c, P, out, so + r.lo, so + r.hi, so);
         }
       }
       break;
@@ -334,19 +417,21 @@ __device__ void direct_body(const MtDevComm& c, const DirectArgs& a, int lr, int
       const MtRange r = mt_split(B, ncta, cta, kSplitAlignDirect);
       if (r.hi > r.lo) {
         if (a.variant == 1) {  // one-shot: everybody sums everything, writes locally only
-          pull_reduce_range<T, NTHREADS, false, true>(c, a.in_off, 0, out, r.lo, r.hi, 0);
+          pull_reduce_range<TI, TO, NTHREADS, false, true>(c, P, out, r.lo, r.hi, 0);
         } else {
           // two-shot: inside this CTA's slice, rank `me` owns sub-slice `me`
           const MtRange s = mt_split(r.hi - r.lo, n, me, 16);
           const uint64_t lo = r.lo + s.lo, hi = r.lo + s.hi;
           if (hi > lo) {
-            if (a.nvls) {
-              const uint64_t nvec = (hi - lo) >> 4;
-              nvls_reduce_range<T, NTHREADS, true>(c.mc + a.in_off + lo, c.mc + a.out_off + lo, nvec);
-              if (lo + (nvec << 4) < hi)
-                pull_reduce_range<T, NTHREADS, true, false>(c, a.in_off, a.out_off, out, lo + (nvec << 4), hi, 0);
+            if (kSame && a.nvls) {
+              if constexpr (kSame) {
+                const uint64_t nvec = (hi - lo) >> 4;
+                nvls_reduce_range<T, NTHREADS, true>(c.mc + a.mc_in_off + lo, c.mc + a.mc_out_off + lo, nvec);
+                if (lo + (nvec << 4) < hi)
+                  pull_reduce_range<TI, TO, NTHREADS, true, false>(c, P, out, lo + (nvec << 4), hi, 0);
+              }
             } else {
-              pull_reduce_range<T, NTHREADS, true, false>(c, a.in_off, a.out_off, out, lo, hi, 0);
+              pull_reduce_range<TI, TO, NTHREADS, true, false>(c, P, out, lo, hi, 0);
             }
           }
         }
@@ -354,46 +439,47 @@ __device__ void direct_body(const MtDevComm& c, const DirectArgs& a, int lr, int
       break;
     }
     case DOP_BROADCAST: {
-      const MtRange r = mt_split(B, ncta, cta, kSplitAlignDirect);
-      if (a.variant == 2) {
-        // pull + replicate: rank j fetches sub-slice j straight from the root's buffer and replicates it
-        // to everybody (one multimem.st per vector, or plain stores to every peer).  The root's link only
-        // carries each byte once, the replication is spread over all ranks (a single source of multicast
-        // stores tops out near 400 GB/s), and there is no phase in which only the root's link is busy.
-        const uint64_t len = r.hi - r.lo;
-        const MtRange sm = mt_split(len, n, me, 16);
-        if (sm.hi > sm.lo) {
-          const uint8_t* src = (me == a.root ? in : c.heap[a.root] + a.in_off) + r.lo + sm.lo;
-          const uint64_t nb = sm.hi - sm.lo;
-          if (a.nvls) {
-            if (me == a.root) nvls_bcast_range<NTHREADS, false>(src, c.mc + a.out_off + r.lo + sm.lo, nb >> 4);
-            else nvls_bcast_range<NTHREADS, true>(src, c.mc + a.out_off + r.lo + sm.lo, nb >> 4);
-          } else {
-            bcast_fanout<NTHREADS>(c, src, a.out_off + r.lo + sm.lo, out + r.lo + sm.lo, nb, me == a.root && in == out);
-          }
-        }
-        break;
-      }
-      if (r.hi > r.lo) {
-        if (a.nvls) {
-          if (me == a.root) {
-            const uint64_t nvec = (r.hi - r.lo) >> 4;
-            nvls_bcast_range<NTHREADS>(in + r.lo, c.mc + a.out_off + r.lo, nvec);
-            for (uint64_t o = r.lo + (nvec << 4) + threadIdx.x; o < r.hi; o += NTHREADS)
-              for (int p = 0; p < n; ++p) *(volatile uint8_t*)(c.heap[p] + a.out_off + o) = in[o];
-          }
-        } else if (a.variant == 0) {
-          if (me == a.root) {
-            for (int d = 0; d < n; ++d) {
-              const int p = (me + d) % n;
-              uint8_t* dst = (p == me ? out : c.heap[p] + a.out_off);
-              if (p == me && in == out) continue;
-              copy_range<NTHREADS, false, true>(in + r.lo, dst + r.lo, r.hi - r.lo);
+      if constexpr (kSame) {
+        const MtRange r = mt_split(B, ncta, cta, kSplitAlignDirect);
+        if (a.variant == 2) {
+          // pull + replicate: rank j fetches sub-slice j straight from the root's buffer and replicates it
+          // to everybody (one multimem.st per vector, or plain stores to every peer).  The root's link only
+          // carries each byte once, the replication is spread over all ranks (a single source of multicast
+          // stores tops out near 400 GB/s), and there is no phase in which only the root's link is busy.
+          const uint64_t len = r.hi - r.lo;
+          const MtRange sm = mt_split(len, n, me, 16);
+          if (sm.hi > sm.lo) {
+            const uint8_t* src = (me == a.root ? in : P.in[a.root]) + r.lo + sm.lo;
+            const uint64_t nb = sm.hi - sm.lo;
+            if (a.nvls) {
+              if (me == a.root) nvls_bcast_range<NTHREADS, false>(src, c.mc + a.mc_out_off + r.lo + sm.lo, nb >> 4);
+              else nvls_bcast_range<NTHREADS, true>(src, c.mc + a.mc_out_off + r.lo + sm.lo, nb >> 4);
+            } else {
+              bcast_fanout<NTHREADS>(c, src, P, r.lo + sm.lo, nb, me == a.root && in == out);
             }
           }
-        } else {
-          if (me != a.root) copy_range<NTHREADS, true, false>(c.heap[a.root] + a.in_off + r.lo, out + r.lo, r.hi - r.lo);
-          else if (in != out) copy_range<NTHREADS, false, false>(in + r.lo, out + r.lo, r.hi - r.lo);
+          break;
+        }
+        if (r.hi > r.lo) {
+          if (a.nvls) {
+            if (me == a.root) {
+              const uint64_t nvec = (r.hi - r.lo) >> 4;
+              nvls_bcast_range<NTHREADS>(in + r.lo, c.mc + a.mc_out_off + r.lo, nvec);
+              for (uint64_t o = r.lo + (nvec << 4) + threadIdx.x; o < r.hi; o += NTHREADS)
+                for (int p = 0; p < n; ++p) *(volatile uint8_t*)(P.out[p] + o) = in[o];
+            }
+          } else if (a.variant == 0) {
+            if (me == a.root) {
+              for (int d = 0; d < n; ++d) {
+                const int p = (me + d) % n;
+                if (p == me && in == out) continue;
+                copy_range<NTHREADS, false, true>(in + r.lo, P.out[p] + r.lo, r.hi - r.lo);
+              }
+            }
+          } else {
+            if (me != a.root) copy_range<NTHREADS, true, false>(P.in[a.root] + r.lo, out + r.lo, r.hi - r.lo);
+            else if (in != out) copy_range<NTHREADS, false, false>(in + r.lo, out + r.lo, r.hi - r.lo);
+          }
         }
       }
       break;
@@ -401,17 +487,18 @@ __device__ void direct_body(const MtDevComm& c, const DirectArgs& a, int lr, int
     case DOP_REDUCE: {
       const MtRange r = mt_split(B, ncta, cta, kSplitAlignDirect);
       if (a.variant == 2) {
-        // reduce-scatter + gather: rank j sums sub-slice j (in the switch, or by pulling from every peer)
-        // and stores the result straight into the root's output, so the summing is spread over all ranks
-        // and the root only receives.
-        const MtRange sm = mt_split(r.hi - r.lo, n, me, 16);
-        if (sm.hi > sm.lo) {
-          const uint64_t lo = r.lo + sm.lo, hi = r.lo + sm.hi;
-          uint8_t* dst = me == a.root ? out : c.heap[a.root] + a.out_off;
-          if (a.nvls) {
-            nvls_reduce_range<T, NTHREADS, false>(c.mc + a.in_off + lo, dst + lo, (hi - lo) >> 4);
-          } else {
-            pull_reduce_range<T, NTHREADS, false, false>(c, a.in_off, 0, dst, lo, hi, 0);
+        // reduce-scatter + gather: rank j sums sub-slice j in the switch and stores the result straight into
+        // the root's output, so the summing is spread over all ranks and the root only receives.
+        if constexpr (kSame) {
+          const MtRange sm = mt_split(r.hi - r.lo, n, me, 16);
+          if (sm.hi > sm.lo) {
+            const uint64_t lo = r.lo + sm.lo, hi = r.lo + sm.hi;
+            uint8_t* dst = P.out[a.root];
+            if (a.nvls) {
+              nvls_reduce_range<T, NTHREADS, false>(c.mc + a.mc_in_off + lo, dst + lo, (hi - lo) >> 4);
+            } else {
+              pull_reduce_range<TI, TO, NTHREADS, false, false>(c, P, dst, lo, hi, 0);
+            }
           }
         }
         break;
@@ -424,19 +511,20 @@ __device__ void direct_body(const MtDevComm& c, const DirectArgs& a, int lr, int
           const int idx = mt_mod(me - a.root - 1, n);
           const MtRange sm = mt_split(r.hi - r.lo, n - 1, idx, 16);
           if (sm.hi > sm.lo)
-            pull_reduce_range<T, NTHREADS, false, false>(c, a.in_off, 0, c.heap[a.root] + a.out_off, r.lo + sm.lo,
-                                                         r.lo + sm.hi, 0);
+            pull_reduce_range<TI, TO, NTHREADS, false, false>(c, P, P.out[a.root], r.lo + sm.lo, r.lo + sm.hi, 0);
         }
         break;
       }
       if (r.hi > r.lo && me == a.root) {
-        if (a.nvls) {
-          const uint64_t nvec = (r.hi - r.lo) >> 4;
-          nvls_reduce_range<T, NTHREADS, false>(c.mc + a.in_off + r.lo, out + r.lo, nvec);
-          if (r.lo + (nvec << 4) < r.hi)
-            pull_reduce_range<T, NTHREADS, false, false>(c, a.in_off, 0, out, r.lo + (nvec << 4), r.hi, 0);
+        if (kSame && a.nvls) {
+          if constexpr (kSame) {
+            const uint64_t nvec = (r.hi - r.lo) >> 4;
+            nvls_reduce_range<T, NTHREADS, false>(c.mc + a.mc_in_off + r.lo, out + r.lo, nvec);
+            if (r.lo + (nvec << 4) < r.hi)
+              pull_reduce_range<TI, TO, NTHREADS, false, false>(c, P, out, r.lo + (nvec << 4), r.hi, 0);
+          }
         } else {
-          pull_reduce_range<T, NTHREADS, false, false>(c, a.in_off, 0, out, r.lo, r.hi, 0);
+          pull_reduce_range<TI, TO, NTHREADS, false, false>(c, P, out, r.lo, r.hi, 0);
         }
       }
       break;
@@ -447,11 +535,13 @@ __device__ void direct_body(const MtDevComm& c, const DirectArgs& a, int lr, int
   rank_barrier(c, cta, s_fail);
 }
 
-template <class T, int NTHREADS>
+template <class TI, class TO, int NTHREADS>
 __global__ void __launch_bounds__(NTHREADS, 1) direct_kernel(const MtDevComm* comms, DirectArgs a) {
   __shared__ int s_fail;
+  __shared__ const uint8_t* s_in[MT_MAX_RANKS];
+  __shared__ uint8_t* s_out[MT_MAX_RANKS];
   const int lr = blockIdx.y;
-  direct_body<T, NTHREADS>(comms[lr], a, lr, blockIdx.x, gridDim.x, &s_fail);
+  direct_body<TI, TO, NTHREADS>(comms[lr], a, lr, blockIdx.x, gridDim.x, &s_fail, s_in, s_out);
 }
 
 }  // namespace mt

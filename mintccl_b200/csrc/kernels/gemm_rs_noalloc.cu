@@ -106,3 +106,18 @@ extern "C" int mt_gemm_rs_single_noalloc(void* stream, const void* A, const void
   if (e != cudaSuccess) return mthost::fail(std::string("mt_gemm_rs_single_noalloc launch: ") + cudaGetErrorString(e));
   return 0;
 }
+
+// A wait inside the kernel that ran out of time leaves its record in the scratch array, not in any
+// communicator: this reads it back (and clears it on request).  Synchronises the device.
+extern "C" int mt_gemm_rs_single_noalloc_status(MtStatus* out, int clear) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+    return mthost::fail("mt_gemm_rs_single_noalloc_status: no usable current device");
+  unsigned char* scratch = nullptr;
+  if (setup(dev, &scratch)) return -1;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e == cudaSuccess && out) e = cudaMemcpy(out, scratch + kStatusOff, sizeof(MtStatus), cudaMemcpyDeviceToHost);
+  if (e == cudaSuccess && clear) e = cudaMemset(scratch + kStatusOff, 0, sizeof(MtStatus));
+  if (e != cudaSuccess) return mthost::fail(std::string("mt_gemm_rs_single_noalloc_status: ") + cudaGetErrorString(e));
+  return 0;
+}

@@ -9,6 +9,7 @@
 // the library image, so it needs no communicator and calls no allocating routine.
 #pragma once
 #include <stdint.h>
+#include "../device/layout.h"
 
 #ifdef __cplusplus
 extern "C" {
@@ -34,6 +35,13 @@ extern "C" {
 //  * Calls no cudaMalloc / cudaFree and no allocating library routine.
 // Returns 0 on success, -1 on error.
 int mt_gemm_rs_single_noalloc(void* stream, const void* A, const void* B, void* out, int M, int N, int K);
+
+// The kernel's waits are bounded: one that runs out of time records {code, where, expected, seen} and raises
+// `abort` in a status record that lives in the same built-in array (the call itself has long returned 0, and
+// `out` is then incomplete).  This copies the record of the current device to `*out` after synchronising the
+// device, and zeroes it when `clear` is non-zero; code == 0 and abort == 0 mean every call so far completed.
+// Allocates nothing.  Returns 0 on success, -1 on error.
+int mt_gemm_rs_single_noalloc_status(MtStatus* out, int clear);
 
 #ifdef __cplusplus
 }

@@ -21,7 +21,7 @@ void count_launch();
 
 cudaError_t launch_ring_simple(int dtype, const MtDevComm* comms, const RingArgs& a, int nch, int nlocal, cudaStream_t s);
 cudaError_t launch_ring_ll128(int dtype, const MtDevComm* comms, const RingArgs& a, int nch, int nlocal, cudaStream_t s);
-cudaError_t launch_direct(int dtype, const MtDevComm* comms, const DirectArgs& a, int nctas, int nlocal, cudaStream_t s);
+cudaError_t launch_direct(int dtype, int out_dtype, const MtDevComm* comms, const DirectArgs& a, int nctas, int nlocal, cudaStream_t s);
 cudaError_t launch_p2p(const MtDevComm* comms, const P2pArgs& a, int nctas, int nlocal, cudaStream_t s);
 cudaError_t launch_ll_allreduce(int dtype, const MtDevComm* comms, const LLArgs& a, int nctas, int nlocal, cudaStream_t s);
 // one-rank communicators: every collective is this copy (invalid value: pointers not co-aligned, use the ring kernel)

@@ -69,8 +69,18 @@ int mt_comm_nlocal(MtComm* c);
 
 // ---- registration of ordinary device allocations (cudaIpc with base + offset) ---------------------
 int mt_ipc_export(const void* ptr, unsigned char handle[64], uint64_t* offset, uint64_t* alloc_bytes);
-void* mt_ipc_open(const unsigned char handle[64]);             // returns the mapped allocation base (cached)
+void* mt_ipc_open(const unsigned char handle[64]);             // returns the mapped allocation base (cached, counted)
+int mt_ipc_close(const unsigned char handle[64]);              // drops one reference; the last one unmaps
 int mt_ipc_close_all(void);
+// Registration service (host/regsrv.cpp): a thread per communicator that opens the peers' IPC handles on request,
+// so that an owner can make an allocation addressable everywhere without the peers' main threads taking part.
+int mt_reg_start(MtComm* c, const char* sock_name, const char* secret);
+int mt_reg_stop(MtComm* c);                                    // also closes what the service opened
+// Ask the service listening at `peer_sock` to map the allocation behind `handle`; *va = its base over there.
+int mt_reg_share(const char* peer_sock, const char* secret, int my_rank, const unsigned char handle[64], uint64_t size,
+                 uint64_t* va, int timeout_ms);
+int mt_reg_unshare(const char* peer_sock, const char* secret, int my_rank, const unsigned char handle[64],
+                   int timeout_ms);
 
 // ---- file-descriptor passing over abstract unix sockets --------------------------------------------
 int mt_fd_listen(const char* name);                            // returns a listening socket
@@ -85,8 +95,14 @@ void mt_fd_close(int fd);
 int mt_ring(MtComm* c, void* stream, int proto, int dtype, int op, const void* const* in, void* const* out,
             uint64_t nbytes, int root, int spatial, const int* chain, int chain_len, int nchannels);
 // op (direct): 0 allgather 1 reducescatter 2 allreduce 3 alltoall 4 broadcast 5 reduce.
-int mt_direct(MtComm* c, void* stream, int dtype, int op, const void* const* in, void* const* out, uint64_t in_off,
-              uint64_t out_off, uint64_t nbytes, int root, int variant, int nvls, int nctas);
+// pub_in[p] / pub_out[p] (nranks entries; ignored in an emulated world): where this rank's input / output is as
+// rank p addresses it, either an address valid in p's process (a CUDA IPC mapping, mt_reg_share) or
+// MT_PUB_HEAP_TAG | offset inside this rank's heap; 0 where peers never touch the buffer.  mc_in_off / mc_out_off:
+// heap offsets for the NVLS variants (the same on every rank).  out_dtype != dtype (reducing ops, not NVLS):
+// fp16/bf16 -> fp32 or fp32 -> fp16/bf16, summed in fp32 and rounded once.  nbytes counts input bytes.
+int mt_direct(MtComm* c, void* stream, int dtype, int out_dtype, int op, const void* const* in, void* const* out,
+              const uint64_t* pub_in, const uint64_t* pub_out, uint64_t mc_in_off, uint64_t mc_out_off, uint64_t nbytes,
+              int root, int variant, int nvls, int nctas);
 int mt_ll_allreduce(MtComm* c, void* stream, int dtype, const void* const* in, void* const* out, uint64_t nbytes);
 uint64_t mt_ll_capacity(MtComm* c);
 // Direct copy between two ranks.  Real mode: `local_rank_role` 1 = this rank copies, 2 = passive.

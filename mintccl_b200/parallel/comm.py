@@ -16,6 +16,7 @@ multi-rank protocol path.  In that mode every tensor argument is a list with one
 """
 from __future__ import annotations
 
+import bisect
 import ctypes as C
 import os
 import uuid
@@ -32,6 +33,17 @@ from .rendezvous import ControlPlane, SingleControl, connect, local_rank_default
 TensorOrList = Union[torch.Tensor, Sequence[torch.Tensor]]
 
 _DT = {torch.float32: N.DT_F32, torch.float16: N.DT_F16, torch.bfloat16: N.DT_BF16}
+_HEAP_TAG = 1 << 63   # MT_PUB_HEAP_TAG: "offset inside the announcing rank's symmetric heap"
+
+
+class _Segment:
+    """One device allocation of this process that every peer has mapped (CUDA IPC), with its base address in each
+    peer's address space.  ``keep`` holds a storage inside the allocation, so the caching allocator cannot hand
+    the allocation back to the driver while peers still map it."""
+    __slots__ = ("base", "size", "handle", "peer_base", "keep")
+
+    def __init__(self, base, size, handle, peer_base, keep):
+        self.base, self.size, self.handle, self.peer_base, self.keep = base, size, handle, peer_base, keep
 
 
 class CollectiveError(RuntimeError):
@@ -73,6 +85,11 @@ class Communicator:
         self._allocs: dict[int, int] = {}
         self._free: list[tuple[int, int]] = []
         self._registered: dict = {}
+        self._segs: dict[int, _Segment] = {}     # allocation base -> shared allocation
+        self._seg_bases: list[int] = []          # sorted keys of _segs
+        self._unsharable: set[int] = set()       # allocation bases CUDA IPC refused
+        self._reg_secret = ""
+        self._reg_token = None
         self._plans: dict = {}
         self._rec_key = None
         self._tuning = TuningTable.from_env()   # MINTCCL_TUNING_FILE: measured choices, or None
@@ -134,6 +151,8 @@ class Communicator:
                 self._try_nvls()
                 if self.cfg.nvls == "on" and not self.nvls:
                     raise RuntimeError("MINTCCL_NVLS=on but the multicast object could not be set up")
+            if n > 1:
+                self._start_registration_service()
         ring = self._choose_ring()
         arr = (C.c_int * N.MT_MAX_RANKS)(*ring)
         N.check(L.mt_comm_finalize(self._handle, arr), "mt_comm_finalize")
@@ -167,8 +186,10 @@ class Communicator:
                     if p != self.rank:
                         N.check(L.mt_comm_import_ipc(self._handle, p, h), f"import_ipc({p})")
             else:
-                token = self.control.bcast(uuid.uuid4().hex[:12], 0)
-                self._sock_token = token
+                # the socket name is public (/proc/net/unix); the key travels over the control plane only and comes
+                # back in the tag of every descriptor, next to the sender's rank
+                token, key = self.control.bcast((uuid.uuid4().hex[:12], uuid.uuid4().int & 0x3fffff), 0)
+                self._sock_token, self._sock_key = token, key
                 sock = L.mt_fd_listen(f"mintccl-{token}-{self.rank}".encode())
                 if sock < 0:
                     raise RuntimeError("cannot listen on the fd-passing socket")
@@ -178,14 +199,20 @@ class Communicator:
                 try:
                     for p in range(n):
                         if p != self.rank:
-                            N.check(L.mt_fd_send(f"mintccl-{token}-{p}".encode(), self.rank, fd, 20000), f"fd_send({p})")
-                    for _ in range(n - 1):
+                            N.check(L.mt_fd_send(f"mintccl-{token}-{p}".encode(), (key << 8) | self.rank, fd, 20000),
+                                    f"fd_send({p})")
+                    seen = set()
+                    while len(seen) < n - 1:
                         tag = C.c_int(-1)
                         rfd = L.mt_fd_accept(sock, C.byref(tag), 20000)
                         if rfd < 0:
                             raise RuntimeError("did not receive a peer's heap descriptor")
                         try:
-                            N.check(L.mt_comm_import_fd(self._handle, tag.value, rfd), f"import_fd({tag.value})")
+                            src = tag.value & 0xff
+                            if tag.value >> 8 != key or src >= n or src == self.rank or src in seen:
+                                continue   # not one of this communicator's peers, or a repeat: ignore it
+                            N.check(L.mt_comm_import_fd(self._handle, src, rfd), f"import_fd({src})")
+                            seen.add(src)
                         finally:
                             L.mt_fd_close(rfd)
                 finally:
@@ -193,6 +220,18 @@ class Communicator:
             return True, ""
         except RuntimeError as e:  # reported to all ranks by the caller's allgather
             return False, str(e)
+
+    def _start_registration_service(self) -> None:
+        """One thread per communicator that maps a peer's ordinary allocation into this process when the peer asks
+        (``csrc/host/regsrv.cpp``).  Socket name and secret come from rank 0 over the control plane."""
+        token, secret = self.control.bcast((uuid.uuid4().hex[:12], uuid.uuid4().hex[:30]), 0)
+        self._reg_token, self._reg_secret = token, secret
+        ok = self.lib.mt_reg_start(self._handle, self._reg_sock(self.rank), secret.encode()) == 0
+        if not all(self.control.allgather(ok)):
+            raise RuntimeError(f"could not start the registration service: {N.last_error()}")
+
+    def _reg_sock(self, rank: int) -> bytes:
+        return f"mintccl-{self._reg_token}-reg-{rank}".encode()
 
     def _try_nvls(self) -> None:
         L, n = self.lib, self.world_size
@@ -204,12 +243,13 @@ class Communicator:
             if self.rank == 0:
                 fd = N.check(L.mt_comm_mc_create(self._handle), "mc_create")
                 for p in range(1, n):
-                    N.check(L.mt_fd_send(f"mintccl-{self._sock_token}-{p}".encode(), 1000, fd, 20000), "mc fd_send")
+                    N.check(L.mt_fd_send(f"mintccl-{self._sock_token}-{p}".encode(), (self._sock_key << 8) | 0xff, fd, 20000),
+                            "mc fd_send")
                 L.mt_fd_close(fd)
             else:
                 tag = C.c_int(-1)
                 rfd = L.mt_fd_accept(self._sock, C.byref(tag), 20000)
-                if rfd < 0 or tag.value != 1000:
+                if rfd < 0 or tag.value != ((self._sock_key << 8) | 0xff):
                     raise RuntimeError("did not receive the multicast descriptor")
                 N.check(L.mt_comm_mc_import(self._handle, rfd), "mc_import")
                 L.mt_fd_close(rfd)
@@ -271,7 +311,12 @@ class Communicator:
     def close(self) -> None:
         if self._handle:
             torch.cuda.synchronize(self.device)
+            self.control.barrier()             # nobody still runs a kernel that touches a peer's memory
+            self.lib.mt_reg_stop(self._handle)  # unmap what this rank opened for its peers
             self.control.barrier()
+            self._segs.clear()
+            self._seg_bases.clear()
+            self._plans.clear()
             self.lib.mt_comm_destroy(self._handle)
             self._handle = None
             if getattr(self, "_sock", None) is not None:
@@ -429,15 +474,132 @@ class Communicator:
         self._run(self.lib.mt_ring, (proto, dtype, op, inp, outp, nbytes, root, 1 if spatial else 0, ch_arr,
                                      len(chain or []), nch))
 
-    def _launch_direct(self, dop, ins, outs, in_off, out_off, nbytes, dtype, root=0, variant=0, nvls=False, nctas=None):
+    # ---------------------------------------------------------------- ordinary tensors as peer memory
+    def share(self, t: torch.Tensor) -> List[int]:
+        """Make an ordinary CUDA tensor addressable by every peer and return, for every rank, the address of THIS
+        rank's tensor in that rank's address space.  One-sided: only the caller takes part (the peers' registration
+        services answer), so ranks may call it at different times.  The allocation that contains the tensor is
+        exported once through CUDA IPC (base + offset: the reference sends the handle of the block and drops the
+        offset, common.py:24-26) and stays mapped, and alive, until :meth:`unshare_all` or :meth:`close`."""
+        ptr = t.data_ptr()
+        if self.emulated or self.world_size == 1:
+            return [ptr] * max(1, self.world_size)
+        seg = self._segment_of(ptr, t.numel() * t.element_size())
+        if seg is None:
+            seg = self._share_allocation(t)
+        return [ptr if p == self.rank else seg.peer_base[p] + (ptr - seg.base) for p in range(self.world_size)]
+
+    def _segment_of(self, ptr: int, nbytes: int) -> Optional[_Segment]:
+        i = bisect.bisect_right(self._seg_bases, ptr) - 1
+        if i < 0:
+            return None
+        seg = self._segs[self._seg_bases[i]]
+        return seg if ptr + nbytes <= seg.base + seg.size else None
+
+    def _share_allocation(self, t: torch.Tensor) -> _Segment:
+        buf = C.create_string_buffer(64)
+        off, size = C.c_uint64(0), C.c_uint64(0)
+        ptr = t.data_ptr()
+        if self.lib.mt_ipc_export(ptr, buf, C.byref(off), C.byref(size)) < 0:
+            raise RuntimeError(f"this allocation cannot be exported through CUDA IPC: {N.last_error()}")
+        base = ptr - off.value
+        peer_base = [0] * self.world_size
+        done = []
+        try:
+            for p in range(self.world_size):
+                if p == self.rank:
+                    peer_base[p] = base
+                    continue
+                va = C.c_uint64(0)
+                N.check(self.lib.mt_reg_share(self._reg_sock(p), self._reg_secret.encode(), self.rank, buf.raw,
+                                              size.value, C.byref(va), 20000), f"share with rank {p}")
+                peer_base[p] = va.value
+                done.append(p)
+        except RuntimeError:
+            for p in done:
+                self.lib.mt_reg_unshare(self._reg_sock(p), self._reg_secret.encode(), self.rank, buf.raw, 5000)
+            raise
+        seg = _Segment(base, size.value, buf.raw, peer_base, t.untyped_storage())
+        self._segs[base] = seg
+        bisect.insort(self._seg_bases, base)
+        return seg
+
+    def unshare_all(self) -> None:
+        """Ask every peer to unmap the allocations shared so far and let go of them.  Collective in effect: call it
+        on every rank, with no collective in flight, e.g. before ``torch.cuda.empty_cache()``."""
+        torch.cuda.synchronize(self.device)
+        self.control.barrier()
+        for seg in self._segs.values():
+            for p in range(self.world_size):
+                if p != self.rank:
+                    self.lib.mt_reg_unshare(self._reg_sock(p), self._reg_secret.encode(), self.rank, seg.handle, 5000)
+        self._segs.clear()
+        self._seg_bases.clear()
+        self._unsharable.clear()
+        self._plans.clear()
+        self.control.barrier()
+
+    def _peer_ok(self, ts: List[torch.Tensor]) -> bool:
+        """Can the peers address these tensors?  Heap tensors and (emulation) everything in the one address space:
+        yes.  Ordinary tensors: when automatic registration is on and CUDA IPC takes the allocation."""
+        if self.emulated or self.world_size == 1:
+            return True
+        t = ts[0]
+        if self.symm_offset(t) is not None:
+            return True
+        if self._segment_of(t.data_ptr(), t.numel() * t.element_size()) is not None:
+            return True
+        if not self.cfg.auto_register:
+            return False
+        sbase = t.untyped_storage().data_ptr()
+        if sbase in self._unsharable:
+            return False
+        try:
+            self._share_allocation(t)
+            return True
+        except RuntimeError:
+            self._unsharable.add(sbase)   # e.g. an allocator CUDA IPC cannot export: this memory takes the ring
+            return False
+
+    def _peer_views(self, ts: List[torch.Tensor], extra: int = 0) -> List[int]:
+        """What this rank announces to each peer as the place of ``ts[0]`` (+ ``extra`` bytes)."""
+        t = ts[0]
+        off = self.symm_offset(t)
+        if off is not None:
+            return [_HEAP_TAG | (off + extra)] * self.world_size
+        if self._segment_of(t.data_ptr(), t.numel() * t.element_size()) is None and not self.cfg.auto_register:
+            raise ValueError("this algorithm needs memory the peers can address: a tensor from "
+                             "Communicator.symm_empty, or an ordinary tensor passed to Communicator.share() first")
+        return [v + extra for v in self.share(t)]
+
+    def _launch_direct(self, dop, ins, outs, nbytes, dtype, root=0, variant=0, nvls=False, nctas=None,
+                       peers_read_in=False, peers_write_out=False, out_dtype=None, in_extra=0, in_from_out=False):
+        """One launch of the one-hop kernel.  ``peers_read_in`` / ``peers_write_out``: whether the peers touch this
+        rank's input / output, i.e. whether it must be announced to them (and, for an ordinary tensor, shared).
+        ``in_from_out``: the contribution is a slice of the output buffer, ``in_extra`` bytes into it."""
         nctas = self._direct_ctas(nbytes, nctas if nctas is not None or not nvls else min(self.cfg.nvls_ctas, self._direct_ctas(nbytes, None)))
-        if nvls and (nbytes % 16 or (in_off or 0) % 16 or (out_off or 0) % 16
-                     or any(t is not None and t.data_ptr() % 16 for t in list(ins) + list(outs))):
-            raise ValueError("NVLS algorithms need 16-byte aligned buffers and a byte count that is a multiple of 16")
+        mc_in = mc_out = 0
+        if nvls:
+            mc_in, mc_out = self._symm_off_all(ins), self._symm_off_all(outs)
+            if (nbytes % 16 or (mc_in or 0) % 16 or (mc_out or 0) % 16
+                    or any(t is not None and t.data_ptr() % 16 for t in list(ins) + list(outs))):
+                raise ValueError("NVLS algorithms need 16-byte aligned buffers and a byte count that is a multiple of 16")
+        n = self.world_size
+        if self.emulated or n == 1:
+            pin = pout = None
+        else:
+            pout = self._peer_views(outs) if peers_write_out else [0] * n
+            if not peers_read_in:
+                pin = [0] * n
+            elif in_from_out:
+                pin = self._peer_views(outs, in_extra)
+            else:
+                pin = self._peer_views(ins)
+            pin, pout = N.u64_array(pin), N.u64_array(pout)
         inp = N.ptr_array([t.data_ptr() if t is not None else 0 for t in ins])
         outp = N.ptr_array([t.data_ptr() if t is not None else 0 for t in outs])
-        self._run(self.lib.mt_direct, (dtype, dop, inp, outp, in_off or 0, out_off or 0, nbytes, root, variant,
-                                       1 if nvls else 0, nctas))
+        self._run(self.lib.mt_direct, (dtype, dtype if out_dtype is None else out_dtype, dop, inp, outp, pin, pout,
+                                       mc_in or 0, mc_out or 0, nbytes, root, variant, 1 if nvls else 0, nctas))
 
     _ALGOS = {
         "allreduce": ("auto", "ring", "direct", "nvls", "ll", "oneshot"),
@@ -482,7 +644,9 @@ class Communicator:
 
     # Launch plans: the first call of a collective on given buffers validates the arguments, picks the
     # algorithm and records the native call; later calls with the same buffers replay it directly, which
-    # keeps the host cost of a collective at a few microseconds.
+    # keeps the host cost of a collective at a few microseconds.  The key holds everything the choice depends
+    # on: both buffers (address, size, type), the per-call arguments, and the process-wide settings that may
+    # change between calls (``cfg.algo``, ``cfg.proto``, the route mode).
     def _run(self, fn, args) -> None:
         if fn(self._handle, torch.cuda.current_stream(self.device).cuda_stream, *args) < 0:
             raise RuntimeError(f"{fn.__name__}: {N.last_error()}")
@@ -501,14 +665,32 @@ class Communicator:
             raise RuntimeError(f"{p[0].__name__}: {N.last_error()}")
         return True
 
+    def _key(self, tag, a, b, *rest):
+        return (tag, a.data_ptr(), a.numel(), a.dtype, *((0, 0, None) if b is None else (b.data_ptr(), b.numel(), b.dtype)),
+                self.cfg.algo, self.cfg.proto, *rest)
+
     @staticmethod
-    def _key(tag, a, b, *rest):
-        return (tag, a.data_ptr(), a.numel(), a.dtype, 0 if b is None else b.data_ptr(), *rest)
+    def _nbytes(t: torch.Tensor) -> int:
+        return t.numel() * t.element_size()
+
+    def _check_out(self, what: str, ins, outs, in_numel: int, allow_cast: bool = True) -> None:
+        """``out`` must hold exactly the result: the element count is fixed by the input, the element type is the
+        input's or (reducing one-hop paths) its fp32 / 16-bit counterpart.  Anything else would read or write
+        outside a buffer on the device, here and on the peers."""
+        for i, o in zip(ins, outs):
+            if o.numel() != in_numel:
+                raise ValueError(f"{what}: out has {o.numel()} elements, the result has {in_numel}")
+            if o.dtype != i.dtype:
+                pair = {i.dtype, o.dtype}
+                if not allow_cast or torch.float32 not in pair or not pair <= {torch.float32, torch.float16, torch.bfloat16}:
+                    raise ValueError(f"{what}: out is {o.dtype}, the input is {i.dtype} (conversions: fp16/bf16 <-> fp32 "
+                                     "on the one-hop reducing paths)")
 
     # ------------------------------------------------------------------------------ collectives
     def allreduce(self, x: TensorOrList, out: Optional[TensorOrList] = None, algo: Optional[str] = None,
                   proto: Optional[str] = None, nch: Optional[int] = None) -> None:
-        """Sum over all ranks; in place unless ``out`` is given."""
+        """Sum over all ranks; in place unless ``out`` is given.  ``out`` may be fp32 for a 16-bit ``x`` or 16-bit for
+        an fp32 ``x``: the one-hop kernels then sum in fp32 and round once, into ``out``'s type."""
         if not self.emulated and type(x) is torch.Tensor:
             if self._replay(self._key("allreduce", x, out, algo, proto, nch)):
                 return
@@ -520,35 +702,43 @@ class Communicator:
     def _allreduce_slow(self, x, out, algo, proto, nch):
         ins = self._lists(x)
         outs = self._lists(out) or ins
-        nbytes = ins[0].numel() * ins[0].element_size()
+        self._check_out("allreduce", ins, outs, ins[0].numel())
+        nbytes = self._nbytes(ins[0])
         dt = _dtype_code(ins[0], True)
-        in_off, out_off = self._symm_off_all(ins), self._symm_off_all(outs)
-        algo, nch = self._tuned("allreduce", nbytes, algo, nch, in_off is not None and out_off is not None, ins + outs)
+        odt = _dtype_code(outs[0], True)
+        cast = odt != dt
+        symm = self._symm_off_all(ins) is not None and self._symm_off_all(outs) is not None
+        algo, nch = self._tuned("allreduce", nbytes, algo, nch, symm, ins + outs)
         algo = self._algo(algo, "allreduce")
         if self.world_size == 1:
-            algo = "ring"  # a single rank: the ring kernel degenerates to a local copy
+            algo = "ring" if not cast else "oneshot"  # a single rank: a local copy (converted by the one-hop kernel)
         if algo == "auto":
-            if nbytes <= min(self.cfg.ll_max_bytes, self.ll_capacity):
+            if nbytes <= min(self.cfg.ll_max_bytes, self.ll_capacity) and not cast:
                 algo = "ll"
-            elif in_off is not None and out_off is not None:
-                algo = "nvls" if self._want_nvls(nbytes, ins + outs) else "direct"
+            elif symm and not cast and self._want_nvls(nbytes, ins + outs):
+                algo = "nvls"
+            elif self._peer_ok(ins) and self._peer_ok(outs):
+                algo = "direct"
+            elif cast and self._peer_ok(ins):
+                algo = "oneshot"
             else:
                 algo = "ring"
+        if cast and algo not in ("direct", "oneshot"):
+            raise ValueError(f"allreduce into another element type runs on the one-hop paths (direct, oneshot), not {algo}")
         if algo == "ll":
             if nbytes > self.ll_capacity:
                 raise ValueError("message too large for the one-shot path")
             self._run(self.lib.mt_ll_allreduce, (dt, N.ptr_array([t.data_ptr() for t in ins]),
                                                  N.ptr_array([t.data_ptr() for t in outs]), nbytes))
         elif algo in ("direct", "nvls", "oneshot"):
-            if in_off is None or (out_off is None and algo != "oneshot"):
-                raise ValueError(f"algo={algo} needs tensors from the symmetric heap (Communicator.symm_empty)")
-            if algo == "nvls" and not self.nvls:
-                raise ValueError("NVLS is not available on this communicator")
+            if algo == "nvls" and not (self.nvls and symm):
+                raise ValueError("algo=nvls needs the multicast mapping and tensors from the symmetric heap "
+                                 "(Communicator.symm_empty) at the same offset on every rank")
             variant = 1 if algo == "oneshot" else 0
-            if variant == 1 and in_off == out_off:
+            if variant == 1 and any(i.data_ptr() == o.data_ptr() for i, o in zip(ins, outs)):
                 raise ValueError("one-shot all-reduce cannot run in place")
-            self._launch_direct(N.DOP_ALLREDUCE, ins, outs, in_off, out_off, nbytes, dt, variant=variant,
-                                nvls=algo == "nvls", nctas=nch)
+            self._launch_direct(N.DOP_ALLREDUCE, ins, outs, nbytes, dt, variant=variant, nvls=algo == "nvls", nctas=nch,
+                                peers_read_in=True, peers_write_out=variant == 0, out_dtype=odt)
         elif algo == "ring":
             self._launch_ring(N.OP_ALLREDUCE, ins, outs, nbytes, dt, self._pick_proto(nbytes, proto), nch=nch)
         else:
@@ -573,30 +763,27 @@ class Communicator:
             raise ValueError("first dimension must equal the world size")
         ranks = range(n) if self.emulated else [self.rank]
         ins = self._lists(inp) or [o[r] for o, r in zip(outs, ranks)]
-        B = ins[0].numel() * ins[0].element_size()
-        if B * n != outs[0].numel() * outs[0].element_size():
-            raise ValueError("contribution and buffer sizes do not match")
+        B = self._nbytes(ins[0])
+        if B * n != self._nbytes(outs[0]) or ins[0].dtype != outs[0].dtype:
+            raise ValueError("contribution and buffer sizes (or element types) do not match")
         dt = _dtype_code(outs[0], False)
-        out_off = self._symm_off_all(outs)
-        algo, nch = self._tuned("allgather", B * n, algo, nch, out_off is not None, ins + outs, B)
+        symm = self._symm_off_all(outs) is not None
+        algo, nch = self._tuned("allgather", B * n, algo, nch, symm, ins + outs, B)
         algo = self._algo(algo, "allgather")
         if n == 1:
             algo = "ring"
         if algo == "auto":
-            algo = "direct" if out_off is not None else "ring"
-            if algo == "direct" and self._want_nvls(B, ins + outs):
+            if symm and self._want_nvls(B, ins + outs):
                 algo = "nvls"
+            else:
+                algo = "direct" if self._peer_ok(outs) else "ring"
         if algo in ("direct", "nvls", "pull"):
-            in_off = self._symm_off_all(ins)
-            if algo == "pull":
-                if inp is None and out_off is not None:
-                    in_off = (1 << 64) - 1  # contributions are the rows of the symmetric buffer itself
-                if in_off is None:
-                    raise ValueError("pull all-gather needs a symmetric input")
-            elif out_off is None:
-                raise ValueError(f"algo={algo} needs a symmetric output buffer")
-            self._launch_direct(N.DOP_ALLGATHER, ins, outs, in_off, out_off, B, dt, variant=1 if algo == "pull" else 0,
-                                nvls=algo == "nvls", nctas=nch)
+            if algo == "nvls" and not (self.nvls and symm):
+                raise ValueError("algo=nvls needs the multicast mapping and a symmetric output buffer")
+            pull = algo == "pull"
+            self._launch_direct(N.DOP_ALLGATHER, ins, outs, B, dt, variant=1 if pull else 0, nvls=algo == "nvls",
+                                nctas=nch, peers_read_in=pull, peers_write_out=not pull,
+                                in_from_out=pull and inp is None, in_extra=self.rank * B)
         else:
             self._launch_ring(N.OP_ALLGATHER, ins, outs, B, dt, self._pick_proto(B * (n - 1), proto),
                               spatial=mode == "spatial", nch=nch)
@@ -604,7 +791,8 @@ class Communicator:
     def reducescatter(self, buff: TensorOrList, out: Optional[TensorOrList] = None, mode: str = "temporal",
                       algo: Optional[str] = None, proto: Optional[str] = None, nch: Optional[int] = None) -> None:
         """``buff`` is ``[world, ...]``; the sum over ranks of row ``rank`` lands in row ``rank`` of the
-        local ``buff`` (or in ``out``), as in the reference (7_reducescatter.py:105-117)."""
+        local ``buff`` (or in ``out``, whose element type may be the fp32 / 16-bit counterpart of ``buff``'s),
+        as in the reference (7_reducescatter.py:105-117)."""
         if not self.emulated and type(buff) is torch.Tensor:
             if self._replay(self._key("reducescatter", buff, out, mode, algo, proto, nch)):
                 return
@@ -620,21 +808,28 @@ class Communicator:
             raise ValueError("first dimension must equal the world size")
         ranks = range(n) if self.emulated else [self.rank]
         outs = self._lists(out) or [i[r] for i, r in zip(ins, ranks)]
-        B = outs[0].numel() * outs[0].element_size()
+        self._check_out("reducescatter", ins, outs, ins[0].numel() // n)
+        B = self._nbytes(ins[0]) // n
         dt = _dtype_code(ins[0], True)
-        in_off = self._symm_off_all(ins)
-        algo, nch = self._tuned("reducescatter", B * n, algo, nch, in_off is not None, ins + outs, B)
+        odt = _dtype_code(outs[0], True)
+        cast = odt != dt
+        symm = self._symm_off_all(ins) is not None
+        algo, nch = self._tuned("reducescatter", B * n, algo, nch, symm, ins + outs, B)
         algo = self._algo(algo, "reducescatter")
         if n == 1:
-            algo = "ring"
+            algo = "ring" if not cast else "direct"
         if algo == "auto":
-            algo = "direct" if in_off is not None else "ring"
-            if algo == "direct" and self._want_nvls(B, ins + outs):
+            if symm and not cast and self._want_nvls(B, ins + outs):
                 algo = "nvls"
+            else:
+                algo = "direct" if self._peer_ok(ins) else "ring"
+        if cast and algo != "direct":
+            raise ValueError(f"reducescatter into another element type runs on the one-hop path (direct), not {algo}")
         if algo in ("direct", "nvls"):
-            if in_off is None:
-                raise ValueError(f"algo={algo} needs a symmetric input buffer")
-            self._launch_direct(N.DOP_REDUCESCATTER, ins, outs, in_off, 0, B, dt, nvls=algo == "nvls", nctas=nch)
+            if algo == "nvls" and not (self.nvls and symm):
+                raise ValueError("algo=nvls needs the multicast mapping and a symmetric input buffer")
+            self._launch_direct(N.DOP_REDUCESCATTER, ins, outs, B, dt, nvls=algo == "nvls", nctas=nch,
+                                peers_read_in=True, out_dtype=odt)
         else:
             self._launch_ring(N.OP_REDUCESCATTER, ins, outs, B, dt, self._pick_proto(B * (n - 1), proto),
                               spatial=mode == "spatial", nch=nch)
@@ -652,40 +847,46 @@ class Communicator:
 
     def _broadcast_slow(self, buff, root, algo, proto, nch):
         ts = self._lists(buff)
-        nbytes = ts[0].numel() * ts[0].element_size()
+        nbytes = self._nbytes(ts[0])
         dt = _dtype_code(ts[0], False)
+        if not 0 <= root < self.world_size:
+            raise ValueError("bad root")
         if self.world_size == 1:
             return
-        off = self._symm_off_all(ts)
-        algo, nch = self._tuned("broadcast", nbytes, algo, nch, off is not None, ts)
+        symm = self._symm_off_all(ts) is not None
+        algo, nch = self._tuned("broadcast", nbytes, algo, nch, symm, ts)
         algo = self._algo(algo, "broadcast")
         if algo == "auto":
             # A wide pipelined ring (algo="ring", 48+ channels) moves more bytes per second when broadcasts
             # follow each other back to back (631 against 528 GB/s at 1 GiB on 4 GPUs), but a single broadcast
             # then pays the fill time of the chain before the last rank has its data.  The multicast variant
             # finishes on every rank at the same time, so it is the default.
-            if off is not None and self._want_nvls(nbytes, ts):
+            if symm and self._want_nvls(nbytes, ts):
                 algo = "nvls"
-            elif off is not None and self.world_size == 2 and nbytes > (64 << 10):
-                algo = "direct"   # two ranks: the root pushes once, nothing to pipeline
+            elif nbytes > (64 << 10) and self._peer_ok(ts):
+                algo = "direct"   # one hop: the root pushes (two ranks) or everybody pulls a part and replicates it
             else:
-                algo = "ring"     # LL128 chain for small messages, pipelined Simple ring for large ones
+                algo = "ring"     # LL128 chain for small messages
         if algo in ("direct", "nvls", "pull", "push", "nvls1"):
-            if off is None:
-                raise ValueError(f"algo={algo} needs a symmetric buffer")
+            if algo in ("nvls", "nvls1") and not (self.nvls and symm):
+                raise ValueError(f"algo={algo} needs the multicast mapping and a symmetric buffer")
             # "direct"/"nvls": pull + replicate (every rank reads one sub-slice from the root and stores it to
             # all ranks, through the switch's multicast with "nvls"); "push": the root writes everything to
             # everybody; "pull": everybody reads the root; "nvls1": only the root issues multicast stores.
-            # With two ranks pull + replicate is the plain push.
-            variant = {"pull": 1, "push": 0, "nvls1": 0}.get(algo, 2 if (self.world_size > 2 and nbytes % 16 == 0) else 0)
-            self._launch_direct(N.DOP_BROADCAST, ts, ts, off, off, nbytes, dt, root=root, variant=variant,
-                                nvls=algo in ("nvls", "nvls1"), nctas=nch)
+            # With two ranks pull + replicate is the plain push.  The multicast stores of pull + replicate move
+            # whole 16-byte vectors; the plain variant takes any size and alignment.
+            replicate = self.world_size > 2 and (algo == "direct" or nbytes % 16 == 0)
+            variant = {"pull": 1, "push": 0, "nvls1": 0}.get(algo, 2 if replicate else 0)
+            self._launch_direct(N.DOP_BROADCAST, ts, ts, nbytes, dt, root=root, variant=variant,
+                                nvls=algo in ("nvls", "nvls1"), nctas=nch, peers_read_in=variant != 0,
+                                peers_write_out=variant != 1)
         else:
             self._launch_ring(N.OP_BROADCAST, ts, ts, nbytes, dt, self._pick_proto(nbytes, proto), root=root, nch=nch)
 
     def reduce(self, buff: TensorOrList, root: int = 0, out: Optional[TensorOrList] = None, algo: Optional[str] = None,
                proto: Optional[str] = None, nch: Optional[int] = None) -> None:
-        """Sum of ``buff`` over all ranks, stored in ``buff`` (or ``out``) of ``root`` (5_reduce.py:99-121)."""
+        """Sum of ``buff`` over all ranks, stored in ``buff`` (or ``out``) of ``root`` (5_reduce.py:99-121).  ``out``
+        may be the fp32 / 16-bit counterpart of ``buff``'s element type (one-hop paths)."""
         if not self.emulated and type(buff) is torch.Tensor:
             if self._replay(self._key("reduce", buff, out, root, algo, proto, nch)):
                 return
@@ -697,43 +898,49 @@ class Communicator:
     def _reduce_slow(self, buff, root, out, algo, proto, nch):
         ins = self._lists(buff)
         outs = self._lists(out) or ins
-        nbytes = ins[0].numel() * ins[0].element_size()
+        self._check_out("reduce", ins, outs, ins[0].numel())
+        if not 0 <= root < self.world_size:
+            raise ValueError("bad root")
+        nbytes = self._nbytes(ins[0])
         dt = _dtype_code(ins[0], True)
-        off = self._symm_off_all(ins)
+        odt = _dtype_code(outs[0], True)
+        cast = odt != dt
+        symm = self._symm_off_all(ins) is not None
         separate = all(o.data_ptr() != i.data_ptr() for i, o in zip(ins, outs))
-        algo, nch = self._tuned("reduce", nbytes, algo, nch, off is not None and separate, ins + outs)
+        algo, nch = self._tuned("reduce", nbytes, algo, nch, symm and separate, ins + outs)
         algo = self._algo(algo, "reduce")
         if self.world_size == 1:
-            algo = "ring"
+            algo = "ring" if not cast else "direct1"
         if algo == "auto":
-            separate = all(o.data_ptr() != i.data_ptr() for i, o in zip(ins, outs))
-            if off is not None and separate and self._want_nvls(nbytes, ins + outs):
+            if symm and separate and not cast and self._want_nvls(nbytes, ins + outs):
                 algo = "nvls"
-            elif off is not None and separate and self.world_size == 2 and nbytes > (64 << 10):
+            elif separate and (cast or nbytes > (64 << 10)) and self._peer_ok(ins):
                 algo = "direct"
             else:
                 algo = "ring"
+        if cast and algo not in ("direct", "direct1"):
+            raise ValueError(f"reduce into another element type runs on the one-hop paths (direct, direct1), not {algo}")
         if algo in ("direct", "nvls", "direct1", "nvls1"):
-            if off is None:
-                raise ValueError(f"algo={algo} needs a symmetric buffer")
+            if algo.startswith("nvls") and not (self.nvls and symm):
+                raise ValueError(f"algo={algo} needs the multicast mapping and a symmetric buffer")
             # the root reads every peer's buffer and writes its own: not safe in place
-            if any(o.data_ptr() == i.data_ptr() for i, o in zip(ins, outs)):
+            if not separate:
                 raise ValueError("direct/NVLS reduce needs a separate output on the root (pass out=)")
-            # with a symmetric output every rank sums one sub-slice and stores it into the root's buffer
+            # when the peers can address the root's output every rank sums one sub-slice and stores it there
             # ("reduce-scatter + gather"); otherwise ("direct1"/"nvls1" force this) the root sums everything
-            out_off = self._symm_off_all(outs)
-            spread = out_off is not None and not algo.endswith("1") and self.world_size > 2 and nbytes % 16 == 0
+            spread = (not algo.endswith("1") and self.world_size > 2 and nbytes % 16 == 0 and self._peer_ok(outs))
             # NVLS: every rank sums 1/n in the switch; plain loads: the n - 1 other ranks sum 1/(n-1) each
             variant = 0 if not spread else (2 if algo.startswith("nvls") else 3)
-            self._launch_direct(N.DOP_REDUCE, ins, outs, off, out_off if spread else 0, nbytes, dt, root=root,
-                                variant=variant, nvls=algo.startswith("nvls"), nctas=nch)
+            self._launch_direct(N.DOP_REDUCE, ins, outs, nbytes, dt, root=root, variant=variant,
+                                nvls=algo.startswith("nvls"), nctas=nch, peers_read_in=True, peers_write_out=spread,
+                                out_dtype=odt)
         else:
             self._launch_ring(N.OP_REDUCE, ins, outs, nbytes, dt, self._pick_proto(nbytes, proto), root=root, nch=nch)
 
     def alltoall(self, inp: TensorOrList, out: TensorOrList, algo: Optional[str] = None,
                  nch: Optional[int] = None) -> None:
-        """Row ``p`` of ``inp`` goes to rank ``p``; row ``p`` of ``out`` comes from rank ``p``.  ``out`` must be
-        symmetric for the default push variant, ``inp`` for ``algo="pull"``."""
+        """Row ``p`` of ``inp`` goes to rank ``p``; row ``p`` of ``out`` comes from rank ``p``.  The default pushes
+        into the peers' ``out``; ``algo="pull"`` reads the peers' ``inp``."""
         if not self.emulated and type(inp) is torch.Tensor:
             if self._replay(self._key("alltoall", inp, out, algo, nch)):
                 return
@@ -747,16 +954,20 @@ class Communicator:
         n = self.world_size
         if ins[0].shape[0] != n or outs[0].shape[0] != n:
             raise ValueError("first dimension must equal the world size")
-        B = ins[0].numel() * ins[0].element_size() // n
+        if self._nbytes(ins[0]) != self._nbytes(outs[0]) or ins[0].dtype != outs[0].dtype:
+            raise ValueError("alltoall: inp and out must have the same size and element type")
+        B = self._nbytes(ins[0]) // n
         dt = _dtype_code(ins[0], False)
         if n == 1:
             outs[0].copy_(ins[0])
             return
-        in_off, out_off = self._symm_off_all(ins), self._symm_off_all(outs)
-        pull = (algo == "pull") or (algo in (None, "auto") and out_off is None and in_off is not None)
-        if pull and in_off is None or (not pull and out_off is None):
-            raise ValueError("alltoall needs a symmetric output (push) or a symmetric input (pull)")
-        self._launch_direct(N.DOP_ALLTOALL, ins, outs, in_off, out_off, B, dt, variant=1 if pull else 0, nctas=nch)
+        if algo not in (None, "auto", "push", "pull", "direct"):
+            raise ValueError("alltoall: algo is push (default) or pull")
+        pull = (algo == "pull") or (algo in (None, "auto") and not self._peer_ok(outs) and self._peer_ok(ins))
+        if not self._peer_ok(ins if pull else outs):
+            raise ValueError("alltoall needs an output (push) or an input (pull) the peers can address")
+        self._launch_direct(N.DOP_ALLTOALL, ins, outs, B, dt, variant=1 if pull else 0, nctas=nch,
+                            peers_read_in=pull, peers_write_out=not pull)
 
     # ------------------------------------------------------------------------------ point to point
     def sendrecv_route(self, route: Sequence[int], src: Optional[TensorOrList], dst: Optional[TensorOrList],

@@ -15,11 +15,106 @@ def gen(rank, numel, dtype, seed0=0):
     return torch.randn(numel, generator=g, device="cuda", dtype=torch.float32).to(dtype)
 
 
-def close(got, ref32, dtype, hops=1):
-    tol = 1e-2 if dtype != torch.bfloat16 else max(1e-2, 4e-3 * hops)
-    if dtype == torch.float32:
-        tol = 1e-5 * max(1, hops)
-    torch.testing.assert_close(got.float(), ref32.to(dtype).float(), rtol=tol, atol=4 * tol)
+def close(got, srcs, dtype, hops=1):
+    """Element-wise bound from the arithmetic: one rounding of an fp32 sum for the one-hop paths, `hops` roundings
+    of partial sums (each at most sum |x_r|) for a ring; see tests/test_gpu_emulated.py::assert_sum_close."""
+    ref = sum(s.float() for s in srcs)
+    absum = sum(s.float().abs() for s in srcs)
+    half = torch.finfo(dtype).eps / 2
+    acc_err = len(srcs) * 2.0 ** -22 * absum
+    bound = (1.01 * half * ref.abs() if hops <= 1 or dtype == torch.float32 else 1.01 * half * hops * absum) + acc_err
+    bound = bound + torch.finfo(dtype).smallest_normal * torch.finfo(dtype).eps
+    err = (got.float() - ref).abs()
+    assert not bool((err > bound).any()), f"outside the bound by {float((err - bound).max()):.3e} ({dtype}, hops={hops})"
+
+
+def ordinary_and_cast(c, rank, n):
+    """Ordinary `torch.empty` tensors (shared with the peers through CUDA IPC on first use, at a different address
+    and offset on every rank), heap tensors at offsets that differ between ranks, and reductions into another
+    element type: all of them on the one-hop kernels, checked by the launch counters."""
+    from mintccl_b200.utils import stats
+    stats.reset()
+    for dtype in (torch.float16, torch.float32):
+        for numel in (1000, 262144 + 8, 3_000_001):
+            srcs = [gen(r, numel, dtype, seed0=200) for r in range(n)]
+            x = torch.empty(numel + 64, device="cuda", dtype=dtype)[8 * rank:8 * rank + numel]
+            y = torch.empty(numel + 64, device="cuda", dtype=dtype)[8 * (n - rank):8 * (n - rank) + numel]
+            x.copy_(srcs[rank])
+            c.allreduce(x, out=y, algo="direct")
+            c.check()
+            close(y, srcs, dtype, 1)
+            c.allreduce(x)                      # automatic choice, in place (one-shot LL below 32 KiB)
+            c.check()
+            close(x, srcs, dtype, 1)
+            gb = torch.zeros(n, numel, device="cuda", dtype=dtype)
+            gb[rank].copy_(srcs[rank])
+            c.allgather(gb)
+            c.check()
+            assert torch.equal(gb, torch.stack(srcs)), "allgather on an ordinary tensor"
+            gb.zero_()
+            c.allgather(gb, inp=srcs[rank].clone(), algo="pull")
+            c.check()
+            assert torch.equal(gb, torch.stack(srcs)), "pull allgather on ordinary tensors"
+            full = [gen(r, n * numel, dtype, seed0=210).view(n, numel) for r in range(n)]
+            rs_in = full[rank].clone()
+            shard = torch.empty(numel, device="cuda", dtype=dtype)
+            c.reducescatter(rs_in, out=shard)
+            c.check()
+            close(shard, [f[rank] for f in full], dtype, 1)
+            a2a = torch.empty(n, numel, device="cuda", dtype=dtype)
+            c.alltoall(rs_in, a2a)
+            c.check()
+            for p in range(n):
+                assert torch.equal(a2a[p], full[p][rank]), "alltoall on ordinary tensors"
+            b = torch.empty(numel + 1, device="cuda", dtype=dtype)[1:]      # odd element offset: not 16-byte aligned
+            b.copy_(srcs[rank])
+            c.broadcast(b, root=n - 1, algo="direct")
+            c.check()
+            assert torch.equal(b, srcs[n - 1]), "broadcast on an ordinary tensor"
+            rin = srcs[rank].clone()
+            rout = torch.zeros(numel, device="cuda", dtype=dtype)
+            c.reduce(rin, root=0, out=rout, algo="direct")
+            c.check()
+            if rank == 0:
+                close(rout, srcs, dtype, 1)
+            # heap tensors whose offsets differ from rank to rank (the allocator is used unevenly on purpose)
+            pad = c.symm_empty(4096 * (rank + 1), torch.uint8)
+            hx = c.symm_empty(numel, dtype)
+            hy = c.symm_empty(numel, dtype)
+            hx.copy_(srcs[rank])
+            c.allreduce(hx, out=hy, algo="direct")
+            c.check()
+            close(hy, srcs, dtype, 1)
+            for t in (hy, hx, pad):
+                c.symm_free(t)
+            torch.cuda.synchronize()
+            c.control.barrier()
+    seen = stats.snapshot()
+    assert seen["ring_simple"]["calls"] == 0 and seen["ring_ll128"]["calls"] == 0 and seen["direct"]["calls"] > 0, seen
+    # 16-bit -> fp32 and fp32 -> 16-bit
+    for narrow in (torch.bfloat16, torch.float16):
+        numel = 500_000
+        srcs = [gen(r, numel, narrow, seed0=220) for r in range(n)]
+        x = srcs[rank].clone()
+        o32 = torch.zeros(numel, device="cuda", dtype=torch.float32)
+        c.allreduce(x, out=o32, algo="oneshot")
+        c.check()
+        assert torch.equal(o32, sum(s.float() for s in srcs)), "fixed-order fp32 sum must match the oracle bit for bit"
+        c.allreduce(x, out=o32)
+        c.check()
+        close(o32, srcs, torch.float32, 1)
+        s32 = [gen(r, n * numel, torch.float32, seed0=230).view(n, numel) for r in range(n)]
+        shard = torch.zeros(numel, device="cuda", dtype=narrow)
+        c.reducescatter(s32[rank].clone(), out=shard)
+        c.check()
+        close(shard, [f[rank] for f in s32], narrow, 1)
+        rout = torch.zeros(numel, device="cuda", dtype=torch.float32)
+        c.reduce(x, root=n - 1, out=rout)
+        c.check()
+        if rank == n - 1:
+            close(rout, srcs, torch.float32, 1)
+    torch.cuda.synchronize()
+    c.control.barrier()
 
 
 def main():
@@ -36,7 +131,6 @@ def main():
     for dtype in dtypes:
         for numel in sizes:
             srcs = [gen(r, numel, dtype) for r in range(n)]
-            ref = sum(s.float() for s in srcs)
             for a in algos_ar:
                 if a == "ll" and numel * srcs[0].element_size() > c.ll_capacity:
                     continue
@@ -55,7 +149,7 @@ def main():
                     c.allreduce(x, algo=a)
                     got, hops = x, 1
                 c.check()
-                close(got, ref, dtype, hops)
+                close(got, srcs, dtype, hops)
                 c.symm_free(x)
                 c.symm_free(y)
             # all-gather / reduce-scatter / all-to-all / broadcast / reduce
@@ -70,7 +164,6 @@ def main():
                 assert torch.equal(gb, torch.stack(srcs)), f"allgather {algo} {mode} {dtype} {numel}"
                 c.symm_free(gb)
             full = [gen(r, n * numel, dtype, seed0=100).view(n, numel) for r in range(n)]
-            ref2 = sum(f.float() for f in full)
             for mode, algo, proto in [("temporal", "ring", "simple"), ("spatial", "ring", "ll128"), ("temporal", "direct", None)] + \
                     ([("temporal", "nvls", None)] if c.nvls and (numel * srcs[0].element_size()) % 16 == 0 else []):
                 gb = c.symm_empty((n, numel), dtype)
@@ -80,7 +173,7 @@ def main():
                 c.control.barrier()
                 c.reducescatter(gb, out=out, mode=mode, algo=algo, proto=proto)
                 c.check()
-                close(out, ref2[rank], dtype, n if algo == "ring" else 1)
+                close(out, [f[rank] for f in full], dtype, n if algo == "ring" else 1)
                 c.symm_free(gb)
             gi = c.symm_empty((n, numel), dtype)
             go = c.symm_empty((n, numel), dtype)
@@ -111,7 +204,7 @@ def main():
                 c.reduce(b, root=0, out=o, algo=algo)
                 c.check()
                 if rank == 0:
-                    close(o, ref, dtype, n if algo == "ring" else 1)
+                    close(o, srcs, dtype, n if algo == "ring" else 1)
                 if algo in ("direct", "nvls"):  # symmetric output: summing spread over all ranks
                     so = c.symm_zeros(numel, dtype)
                     torch.cuda.synchronize()
@@ -119,10 +212,11 @@ def main():
                     c.reduce(b, root=n - 1, out=so, algo=algo)
                     c.check()
                     if rank == n - 1:
-                        close(so, ref, dtype, 1)
+                        close(so, srcs, dtype, 1)
                     c.control.barrier()
                     c.symm_free(so)
                 c.symm_free(b)
+    ordinary_and_cast(c, rank, n)
     # fused GEMM + collective kernels against the unfused fp32 reference
     from mintccl_b200.ops.gemm import AllGatherGemm, GemmReduceScatter
     M, Nn, K = 128 * n * 2, 512, 256

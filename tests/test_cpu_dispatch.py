@@ -11,8 +11,10 @@ from mintccl_b200.parallel.comm import Communicator
 
 class Recorder(Communicator):
     def __init__(self, world=8, nvls=True, rank=0, **cfg):   # no device, no native communicator
+        cfg.setdefault("auto_register", False)      # ordinary tensors: FIFO ring unless a test shares them
         self.cfg = Config.from_env(**cfg)
         self.lib = N.lib()
+        self._segs, self._seg_bases, self._unsharable, self.shared = {}, [], set(), []
         self.world_size, self.rank, self.nlocal, self.emulated, self.nvls = world, rank, 1, False, nvls
         self.device = 0
         self._plans, self._rec_key, self._pending = {}, None, []
@@ -34,6 +36,18 @@ class Recorder(Communicator):
             return None
         return [t] if isinstance(t, torch.Tensor) else list(t)
 
+    # stands in for CUDA IPC + the peers' registration services
+    def _share_allocation(self, t):
+        from mintccl_b200.parallel.comm import _Segment
+        import bisect
+        base = t.untyped_storage().data_ptr()
+        seg = _Segment(base, t.untyped_storage().nbytes(), b"h" * 64,
+                       [base if p == self.rank else 0x7000_0000_0000 + (p << 40) for p in range(self.world_size)], None)
+        self._segs[base] = seg
+        bisect.insort(self._seg_bases, base)
+        self.shared.append(base)
+        return seg
+
     def _run(self, fn, args):
         self.calls.append((fn.__name__, args))
         self._rec_key = None
@@ -41,7 +55,9 @@ class Recorder(Communicator):
     def last(self):
         name, a = self.calls[-1]
         if name == "mt_direct":
-            return dict(fn=name, dtype=a[0], op=a[1], nbytes=a[6], root=a[7], variant=a[8], nvls=a[9], nctas=a[10])
+            return dict(fn=name, dtype=a[0], out_dtype=a[1], op=a[2], pub_in=None if a[5] is None else list(a[5]),
+                        pub_out=None if a[6] is None else list(a[6]), mc_in=a[7], mc_out=a[8], nbytes=a[9], root=a[10],
+                        variant=a[11], nvls=a[12], nctas=a[13])
         if name == "mt_ring":
             return dict(fn=name, proto=a[0], dtype=a[1], op=a[2], nbytes=a[5], root=a[6], spatial=a[7], nch=a[10])
         return dict(fn=name, args=a)
@@ -201,16 +217,21 @@ def test_emulated_world_takes_one_tensor_per_rank():
     c.emulated, c.nlocal = True, n
     c.heap_base = [c.heap.data_ptr()] * n           # every emulated rank's heap: same offsets
     xs = [c.sym(1 << 16) for _ in range(n)]
-    # the ranks' tensors sit at different offsets of one slab here, so they do not count as symmetric: ring
+    # one address space: every tensor is addressable by every emulated rank, wherever it lies, so the one-hop
+    # kernels run and announce the local pointers themselves (no per-peer views)
     c.allreduce(xs)
+    assert c.last()["fn"] == "mt_direct" and c.last()["nctas"] <= 148 // n and c.last()["pub_in"] is None
+    c.allreduce(xs, algo="ring")
     assert c.last()["fn"] == "mt_ring" and c.last()["nch"] <= 148 // n
     bufs = [torch.zeros(n, 1024, dtype=torch.float16) for _ in range(n)]
     c.allgather(bufs)
+    assert c.last()["fn"] == "mt_direct" and c.last()["op"] == N.DOP_ALLGATHER
+    c.allgather(bufs, algo="ring")
     assert c.last()["fn"] == "mt_ring" and c.last()["op"] == N.OP_ALLGATHER
-    c.reducescatter(bufs, out=[torch.zeros(1024, dtype=torch.float16) for _ in range(n)])
+    c.reducescatter(bufs, out=[torch.zeros(1024, dtype=torch.float16) for _ in range(n)], algo="ring")
     assert c.last()["op"] == N.OP_REDUCESCATTER
     c.broadcast([torch.zeros(100) for _ in range(n)], root=2)
-    assert c.last()["op"] == N.OP_BROADCAST and c.last()["root"] == 2
+    assert c.last()["fn"] == "mt_ring" and c.last()["op"] == N.OP_BROADCAST and c.last()["root"] == 2   # small: LL128 chain
     c.reduce([torch.zeros(100) for _ in range(n)], root=1, out=[torch.zeros(100) for _ in range(n)])
     assert c.last()["op"] == N.OP_REDUCE
 
@@ -255,3 +276,92 @@ def test_ring_and_routes_follow_the_topology(tmp_path, monkeypatch):
     m.ring = [0, 1, 2, 3, 7, 6, 5, 4]
     monkeypatch.setenv("MINTCCL_ROUTE", "ring")
     assert m.route(2, 6) == [2, 3, 7, 6]
+
+
+def test_ordinary_tensors_take_the_one_hop_kernels_once_shared():
+    """With automatic registration an ordinary tensor is shared with the peers on first use (here: recorded) and the
+    call goes to the one-hop kernel with one announced address per peer; heap tensors announce a tagged offset."""
+    c = Recorder(world=8, auto_register=True, rank=3)
+    x, y = torch.zeros(1 << 20, dtype=torch.float16), torch.zeros(1 << 20, dtype=torch.float16)
+    c.allreduce(x, out=y)
+    l = c.last()
+    assert l["fn"] == "mt_direct" and l["op"] == N.DOP_ALLREDUCE and l["nvls"] == 0 and l["variant"] == 0
+    assert len(c.shared) == 2 and l["pub_in"][3] == x.data_ptr() and l["pub_out"][3] == y.data_ptr()
+    assert l["pub_in"][5] == 0x7000_0000_0000 + (5 << 40) + (x.data_ptr() - x.untyped_storage().data_ptr())
+    c.allreduce(x, out=y)
+    assert len(c.shared) == 2                                      # the allocation is shared once
+    h = c.sym(1 << 20)
+    c.allreduce(h, algo="direct")
+    l = c.last()
+    off = h.data_ptr() - c.heap.data_ptr()
+    assert l["pub_in"] == [(1 << 63) | off] * 8 and l["pub_out"] == [(1 << 63) | off] * 8
+    buf = torch.zeros(8, 4096, dtype=torch.float32)
+    c.allgather(buf)
+    l = c.last()
+    assert l["fn"] == "mt_direct" and l["op"] == N.DOP_ALLGATHER and l["variant"] == 0 and l["pub_in"] == [0] * 8
+    c.allgather(buf, algo="pull")                                  # the contribution is row `rank` of the buffer
+    l = c.last()
+    assert l["variant"] == 1 and l["pub_in"][3] == buf.data_ptr() + 3 * 4096 * 4 and l["pub_out"] == [0] * 8
+    c.reducescatter(buf, out=torch.zeros(4096, dtype=torch.float32))
+    assert c.last()["fn"] == "mt_direct" and c.last()["pub_out"] == [0] * 8    # the shard stays local: not shared
+    big = torch.zeros(1 << 20, dtype=torch.float16)
+    c.broadcast(big, root=2)
+    assert c.last()["fn"] == "mt_direct" and c.last()["variant"] == 2 and c.last()["nvls"] == 0
+    c.reduce(big, root=2, out=torch.zeros(1 << 20, dtype=torch.float16))
+    assert c.last()["fn"] == "mt_direct" and c.last()["variant"] == 3           # the other ranks sum, the root receives
+    with pytest.raises(ValueError):
+        c.allreduce(x, algo="nvls")                                # the multicast alias covers the heap only
+
+
+def test_unaligned_views_never_reach_vector_only_paths():
+    """A heap view whose address is not a multiple of 16 takes the plain pull + replicate broadcast (any alignment
+    in the kernel) and never the multicast variant."""
+    c = Recorder(world=4)
+    x = c.sym(1 << 20)
+    c.broadcast(x[4:], root=0)                                     # 8 bytes into a 256-byte aligned allocation
+    l = c.last()
+    assert l["fn"] == "mt_direct" and l["nvls"] == 0
+    with pytest.raises(ValueError):
+        c.broadcast(x[4:], root=0, algo="nvls")
+
+
+def test_output_size_and_type_are_checked_before_launch():
+    c = Recorder(world=4)
+    x = c.sym(1 << 16)
+    n0 = len(c.calls)
+    with pytest.raises(ValueError):
+        c.allreduce(x, out=c.sym(1 << 15))                         # short output
+    with pytest.raises(ValueError):
+        c.reduce(x, root=0, out=c.sym((1 << 16) + 8))
+    with pytest.raises(ValueError):
+        c.reducescatter(x.view(4, -1), out=c.sym(1 << 13))         # the shard has 1 << 14 elements
+    with pytest.raises(ValueError):
+        c.allreduce(x, out=c.sym(1 << 16, torch.bfloat16))         # fp16 -> bf16 is not a supported conversion
+    with pytest.raises(ValueError):
+        c.allgather(c.sym(4 << 10).view(4, -1), inp=c.sym(1 << 10, torch.float32))
+    assert len(c.calls) == n0                                      # nothing was launched
+    # a different out of the same address but another size is a different plan
+    k1 = c._key("allreduce", x, c.heap[:64].view(torch.float16))
+    k2 = c._key("allreduce", x, c.heap[:128].view(torch.float16))
+    assert k1 != k2
+
+
+def test_reductions_into_another_element_type():
+    c = Recorder(world=8)
+    x = c.sym(1 << 20, torch.bfloat16)
+    o32 = c.sym(1 << 20, torch.float32)
+    c.allreduce(x, out=o32)
+    l = c.last()
+    assert l["fn"] == "mt_direct" and (l["dtype"], l["out_dtype"]) == (N.DT_BF16, N.DT_F32) and l["nvls"] == 0
+    assert l["nbytes"] == (1 << 20) * 2                            # counted in input bytes
+    f = c.sym(1 << 18, torch.float32)
+    c.reducescatter(f.view(8, -1), out=c.sym(1 << 15, torch.float16))
+    l = c.last()
+    assert (l["dtype"], l["out_dtype"], l["op"]) == (N.DT_F32, N.DT_F16, N.DOP_REDUCESCATTER)
+    c.reduce(x, root=1, out=o32)
+    assert c.last()["variant"] == 3 and c.last()["out_dtype"] == N.DT_F32
+    with pytest.raises(ValueError):
+        c.allreduce(x, out=o32, algo="ring")
+    small = c.sym(64, torch.float16)
+    c.allreduce(small, out=c.sym(64, torch.float32))               # small and converting: the one-hop kernel, not LL
+    assert c.last()["fn"] == "mt_direct"

@@ -28,21 +28,45 @@ def rand(n, numel, dtype, seed0=0):
     return out
 
 
+class Oracle:
+    """fp32 sum of the ranks' inputs plus the sum of their magnitudes, which scales the error bounds."""
+
+    def __init__(self, ref, absum):
+        self.ref, self.absum = ref, absum
+
+    def __getitem__(self, i):
+        return Oracle(self.ref[i], self.absum[i])
+
+    def view(self, *shape):
+        return Oracle(self.ref.view(*shape), self.absum.view(*shape))
+
+
 def oracle_sum(ts):
     acc = torch.zeros_like(ts[0], dtype=torch.float32)
+    mag = torch.zeros_like(acc)
     for t in ts:
         acc += t.float()
-    return acc
+        mag += t.float().abs()
+    return Oracle(acc, mag)
 
 
-def assert_sum_close(got, ref32, dtype, hops=1):
-    """Direct / NVLS / one-shot paths accumulate in fp32 and round once (hops=1): rtol 1e-2 holds for every
-    dtype.  A ring rounds the partial sum to the storage type at every hop, so for bf16 (8-bit mantissa,
-    half an ulp = 0.2 %) the bound grows with the number of hops."""
-    tol = 1e-2 if dtype != torch.bfloat16 else max(1e-2, 4e-3 * hops)
-    if dtype == torch.float32:
-        tol = 1e-5 * max(1, hops)
-    torch.testing.assert_close(got.float(), ref32.to(dtype).float(), rtol=tol, atol=tol * 4)
+def assert_sum_close(got, oracle, dtype, hops=1, nranks=8):
+    """Element-wise bound that follows from the arithmetic, not a blanket tolerance.  One-hop paths (direct, NVLS,
+    one-shot) add all ranks in fp32 and round once into `dtype`: the error is at most half an ulp of the result
+    plus the fp32 accumulation error.  A ring rounds the partial sum into `dtype` at each of its `hops` combines,
+    and a partial sum is at most sum |x_r|: at most hops half-ulps of that.  A dropped or doubled contribution, a
+    wrong rounding mode or a sum in 16-bit arithmetic falls outside these bounds."""
+    half = torch.finfo(dtype).eps / 2
+    ref, absum = oracle.ref, oracle.absum
+    acc_err = nranks * 2.0 ** -22 * absum                       # fp32 accumulation, any order
+    if hops <= 1 or dtype == torch.float32:
+        bound = 1.01 * half * ref.abs() + acc_err
+    else:
+        bound = 1.01 * half * hops * absum + acc_err
+    err = (got.float() - ref).abs()
+    bad = err > bound + torch.finfo(dtype).smallest_normal * torch.finfo(dtype).eps   # subnormal results
+    assert not bool(bad.any()), (f"{int(bad.sum())} of {bad.numel()} elements outside the bound; worst excess "
+                                 f"{float((err - bound).max()):.3e} ({dtype}, hops={hops})")
 
 
 SIZES = [1, 7, 120, 1000, 4099, 65536 + 3, 1_500_000]
@@ -256,6 +280,142 @@ def test_direct_collectives(n, numel):
         assert_sum_close(ob[0].view(-1), oracle_sum(full), dtype)
         w.symm_free(gb)
         w.symm_free(ob)
+
+
+@pytest.mark.parametrize("n", [2, 4, 8])
+@pytest.mark.parametrize("numel", [3, 1000, 262144 + 8, 1_000_003])
+def test_one_hop_collectives_on_ordinary_tensors(n, numel):
+    """Ordinary `torch.empty` tensors (no symmetric heap, a different address on every rank, odd offsets): the
+    automatic choice is the one-hop kernel, which learns where every rank's buffers are at its entry barrier."""
+    from mintccl_b200.utils import stats
+    w = world(n)
+    stats.reset()
+    for dtype in (torch.float16, torch.float32):
+        pad = 16 // torch.empty((), dtype=dtype).element_size()
+        src = rand(n, numel, dtype, seed0=41)
+        ref = oracle_sum(src)
+        # all-reduce out of place and in place; rank r's buffers start r elements into their allocation
+        xs = [torch.empty(numel + n, device="cuda", dtype=dtype)[r:r + numel] for r in range(n)]
+        ys = [torch.empty(numel + pad * n, device="cuda", dtype=dtype)[pad * r:pad * r + numel] for r in range(n)]
+        for x, s_ in zip(xs, src):
+            x.copy_(s_)
+        w.allreduce(xs, out=ys, algo="direct" if numel * 4 <= 65536 else None)
+        w.check()
+        for y in ys:
+            assert_sum_close(y, ref, dtype, nranks=n)
+        for y in ys[1:]:
+            assert torch.equal(y, ys[0])
+        w.allreduce(xs, algo="direct")
+        w.check()
+        for x in xs:
+            assert torch.equal(x, ys[0])
+        # all-gather, in place convention and with a separate contribution
+        bufs = [torch.zeros(n, numel, device="cuda", dtype=dtype) for _ in range(n)]
+        for r in range(n):
+            bufs[r][r].copy_(src[r])
+        w.allgather(bufs)
+        w.check()
+        want = torch.stack(src)
+        for b in bufs:
+            assert torch.equal(b, want)
+        for b in bufs:
+            b.zero_()
+        w.allgather(bufs, inp=src, algo="pull")
+        w.check()
+        for b in bufs:
+            assert torch.equal(b, want)
+        # reduce-scatter into a separate shard, all-to-all
+        full = rand(n, n * numel, dtype, seed0=43)
+        ins = [f.clone().view(n, numel) for f in full]
+        outs = [torch.empty(numel, device="cuda", dtype=dtype) for _ in range(n)]
+        w.reducescatter(ins, out=outs)
+        w.check()
+        ref2 = oracle_sum(full).view(n, numel)
+        for r in range(n):
+            assert_sum_close(outs[r], ref2[r], dtype, nranks=n)
+        a2a = [torch.empty(n, numel, device="cuda", dtype=dtype) for _ in range(n)]
+        w.alltoall(ins, a2a)
+        w.check()
+        for r in range(n):
+            for p in range(n):
+                assert torch.equal(a2a[r][p], full[p].view(n, numel)[r])
+        # broadcast (views at an odd element offset: no 16-byte alignment on any rank) and reduce
+        bs = [torch.empty(numel + 1, device="cuda", dtype=dtype)[1:] for _ in range(n)]
+        for b, s_ in zip(bs, src):
+            b.copy_(s_)
+        w.broadcast(bs, root=n - 1, algo="direct")
+        w.check()
+        for b in bs:
+            assert torch.equal(b, src[n - 1])
+        rin = [s_.clone() for s_ in src]
+        rout = [torch.zeros(numel, device="cuda", dtype=dtype) for _ in range(n)]
+        w.reduce(rin, root=n // 2, out=rout, algo="direct")
+        w.check()
+        assert_sum_close(rout[n // 2], ref, dtype, nranks=n)
+    seen = stats.snapshot()
+    assert seen["direct"]["calls"] >= 16 and seen["ring_simple"]["calls"] == 0 and seen["ring_ll128"]["calls"] == 0
+
+
+@pytest.mark.parametrize("n", [2, 4, 8])
+@pytest.mark.parametrize("numel", [8, 1001, 300_000])
+def test_reductions_into_another_element_type(n, numel):
+    """16-bit input with fp32 output and fp32 input with 16-bit output: the one-hop kernels sum in fp32 and round
+    once, into the output type.  With fp32 output and a fixed summation order the result is the oracle's, bit for
+    bit."""
+    w = world(n)
+    for narrow in (torch.bfloat16, torch.float16):
+        # widening
+        src = rand(n, numel, narrow, seed0=51)
+        ref = oracle_sum(src)
+        o32 = [torch.zeros(numel, device="cuda", dtype=torch.float32) for _ in range(n)]
+        w.allreduce(src, out=o32, algo="oneshot")          # every rank adds ranks 0..n-1 in that order, like the oracle
+        w.check()
+        for o in o32:
+            assert torch.equal(o, ref.ref)
+        for o in o32:
+            o.zero_()
+        w.allreduce(src, out=o32, algo="direct")           # two-shot: each rank starts the sum at itself
+        w.check()
+        for o in o32:
+            assert_sum_close(o, ref, torch.float32, nranks=n)
+            assert torch.equal(o, o32[0])
+        full = rand(n, n * numel, narrow, seed0=53)
+        shards = [torch.zeros(numel, device="cuda", dtype=torch.float32) for _ in range(n)]
+        w.reducescatter([f.view(n, numel) for f in full], out=shards)
+        w.check()
+        ref2 = oracle_sum(full).view(n, numel)
+        for r in range(n):
+            assert_sum_close(shards[r], ref2[r], torch.float32, nranks=n)
+        rout = [torch.zeros(numel, device="cuda", dtype=torch.float32) for _ in range(n)]
+        w.reduce(src, root=n - 1, out=rout)
+        w.check()
+        assert_sum_close(rout[n - 1], ref, torch.float32, nranks=n)
+        # narrowing
+        src32 = rand(n, numel, torch.float32, seed0=55)
+        ref32 = oracle_sum(src32)
+        on = [torch.zeros(numel, device="cuda", dtype=narrow) for _ in range(n)]
+        w.allreduce(src32, out=on, algo="oneshot")
+        w.check()
+        for o in on:
+            assert torch.equal(o, ref32.ref.to(narrow))    # one rounding of the exact fp32 sum
+        for o in on:
+            o.zero_()
+        w.allreduce(src32, out=on)
+        w.check()
+        for o in on:
+            assert_sum_close(o, ref32, narrow, nranks=n)
+        full32 = rand(n, n * numel, torch.float32, seed0=57)
+        sn = [torch.zeros(numel, device="cuda", dtype=narrow) for _ in range(n)]
+        w.reducescatter([f.view(n, numel) for f in full32], out=sn, algo="direct")
+        w.check()
+        ref4 = oracle_sum(full32).view(n, numel)
+        for r in range(n):
+            assert_sum_close(sn[r], ref4[r], narrow, nranks=n)
+        w.reduce(src32, root=0, out=on, algo="direct1")
+        w.check()
+        assert_sum_close(on[0], ref32, narrow, nranks=n)
+    with pytest.raises(ValueError):
+        w.allreduce(rand(n, 64, torch.float16), out=[torch.zeros(64, device="cuda") for _ in range(n)], algo="ring")
 
 
 def test_direct_sendrecv_symmetric():

@@ -22,14 +22,17 @@ def _entry():
     fn = lib.mt_gemm_rs_single_noalloc
     fn.restype = C.c_int
     fn.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]
-    return N, fn
+    st = lib.mt_gemm_rs_single_noalloc_status
+    st.restype = C.c_int
+    st.argtypes = [C.POINTER(N.MtStatus), C.c_int]
+    return N, fn, st
 
 
 def test_noalloc_entry_matches_regular_entry_twice():
     import mintccl_b200
     from mintccl_b200 import Config
     from mintccl_b200.ops.gemm import GemmReduceScatter
-    N, fn = _entry()
+    N, fn, status = _entry()
     torch.cuda.set_device(0)
     cfg = Config.from_env(max_channels=2, num_blocks=2, buff_size=1 << 20, heap_bytes=128 << 20, scratch_bytes=1 << 20,
                           wait_timeout_ms=4000)
@@ -47,7 +50,10 @@ def test_noalloc_entry_matches_regular_entry_twice():
                 rc = fn(stream, a.data_ptr(), w.data_ptr(), got.data_ptr(), M, Nn, K)
                 assert rc == 0, N.last_error()
                 torch.cuda.synchronize()
-                world.check()
+                world.check()                       # the regular entry point's communicator
+                own = N.MtStatus()                  # the entry point's own record, in its built-in array
+                assert status(C.byref(own), 0) == 0, N.last_error()
+                assert own.code == 0 and own.abort == 0, (own.code, own.where, own.expected, own.seen)
                 torch.testing.assert_close(got.float(), want.float(), rtol=1.6e-2, atol=2e-2)
                 ref = (a.float() @ w.float().t())
                 torch.testing.assert_close(got.float(), ref, rtol=2e-2, atol=3e-2)
@@ -58,7 +64,7 @@ def test_noalloc_entry_matches_regular_entry_twice():
 
 
 def test_noalloc_entry_rejects_sizes_beyond_its_scratch():
-    N, fn = _entry()
+    N, fn, _ = _entry()
     x = torch.zeros(16, device="cuda", dtype=torch.bfloat16)
     assert fn(0, x.data_ptr(), x.data_ptr(), x.data_ptr(), 4096, 256, 64) == -1
     assert "exceeds the built-in scratch" in N.last_error()
