@@ -7,8 +7,11 @@ Run with one process per GPU::
 
 Sizes follow the nccl-tests convention (all-gather: total output bytes; reduce-scatter: total input
 bytes).  Every number is the device time (CUDA events, warm-up first, one event pair around `iters`
-back-to-back calls) as the maximum over ranks; buffers are rotated through a pool larger than the L2
-so that large-message numbers are not served from cache.  The reference publishes no numbers
+back-to-back calls, maximum over ranks), taken `--repeats` times; the median is reported, with the fastest
+and slowest repeat beside it.  Buffers are rotated through a pool larger than the L2 so that large-message
+numbers are not served from cache.  `--memory ordinary` runs this library on plain `torch.empty` tensors
+(shared with the peers through CUDA IPC on first use) instead of tensors of its symmetric heap; NCCL always
+runs on plain tensors that are not registered with it.  The reference publishes no numbers
 (README.md has none), so NCCL on the same box is the yardstick.
 """
 from __future__ import annotations
@@ -48,6 +51,9 @@ def main() -> None:
     ap.add_argument("--chain-steps", default="",
                     help="comma list of MINTCCL_CHAIN_STEP_BYTES values (0 = whole slots) to try for this library's "
                          "broadcast and reduce (they only matter for algo=ring over the Simple protocol)")
+    ap.add_argument("--repeats", type=int, default=5, help="timed blocks per point; the median is reported")
+    ap.add_argument("--memory", default="heap", choices=["heap", "ordinary"],
+                    help="where this library's buffers live: its symmetric heap, or ordinary torch tensors")
     ap.add_argument("--out", default="")
     a = ap.parse_args()
 
@@ -79,24 +85,36 @@ def main() -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX, group=gloo)
         return float(t[0])
 
+    spread = {}
+
     def timed(fn, iters):
+        """Median over `--repeats` blocks of `iters` calls (ms per call, maximum over ranks per block)."""
         for _ in range(max(3, iters // 10)):
             fn()
-        torch.cuda.synchronize()
-        dist.barrier(group=gloo)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(iters):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        return maxr(e0.elapsed_time(e1) / iters)
+        blocks = []
+        for _ in range(max(1, a.repeats)):
+            torch.cuda.synchronize()
+            dist.barrier(group=gloo)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(iters):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            blocks.append(maxr(e0.elapsed_time(e1) / iters))
+        blocks.sort()
+        spread["min"], spread["max"] = blocks[0], blocks[-1]
+        return blocks[len(blocks) // 2]
 
     # rotating pools: inputs and outputs of successive calls do not sit in L2
     sym_in = comm.symm_empty(pool_bytes // esz, dtype)
     sym_out = comm.symm_empty(pool_bytes // esz, dtype)
     sym_in.normal_()
-    plain_in = torch.randn(pool_bytes // esz, device="cuda", dtype=torch.float32).to(dtype) if False else sym_in
+    if a.memory == "ordinary":
+        own_in = torch.empty(pool_bytes // esz, device="cuda", dtype=dtype).normal_()
+        own_out = torch.empty(pool_bytes // esz, device="cuda", dtype=dtype)
+    else:
+        own_in, own_out = sym_in, sym_out
     results = []
     state = {"k": 0}
 
@@ -107,7 +125,7 @@ def main() -> None:
         cnt = max(1, min(64, pool_bytes // per))
         ne = per // esz
         k = max(1, nbytes // esz)
-        return [(sym_in[j * ne: j * ne + k], sym_out[j * ne: j * ne + k]) for j in range(cnt)]
+        return [(own_in[j * ne: j * ne + k], own_out[j * ne: j * ne + k]) for j in range(cnt)]
 
     fence_in = comm.symm_empty(4, torch.float16)
     fence_in.fill_(1.0)
@@ -152,7 +170,8 @@ def main() -> None:
                             elif coll == "reduce":
                                 comm.reduce(i, root=0, out=o, **kw)
                             elif coll == "alltoall":
-                                comm.alltoall(i.view(n, -1), o.view(n, -1), nch=kw.get("nch"))
+                                comm.alltoall(i.view(n, -1), o.view(n, -1), nch=kw.get("nch"),
+                                              algo=algo if algo in ("bulk", "pull") else None)
                         else:
                             if coll == "allreduce":
                                 dist.all_reduce(o)
@@ -182,6 +201,8 @@ def main() -> None:
                         continue
                     bus = busbw_factor(coll, n) * nbytes / (ms * 1e-3) / 1e9
                     row = {"collective": coll, "bytes": nbytes, "impl": impl, "algo": algo, "ctas": ctas, "us": round(ms * 1e3, 2),
+                           "us_min": round(spread.get("min", ms) * 1e3, 2), "us_max": round(spread.get("max", ms) * 1e3, 2),
+                           "repeats": a.repeats, "memory": a.memory if impl == "mintccl" else "ordinary, not registered",
                            "algbw_GBps": round(nbytes / (ms * 1e-3) / 1e9, 3), "busbw_GBps": round(bus, 3), "n": n,
                            "dtype": a.dtype, "sync": bool(fence)}
                     if chain_step is not None:

@@ -134,3 +134,4 @@ static_assert(sizeof(MtSigSlot) == 128, "MtSigSlot is one 128-byte line");
 #define MT_WHERE_LL_ONESHOT 8
 #define MT_WHERE_GEMM_FLAG 9
 #define MT_WHERE_TEST 10
+#define MT_WHERE_BULK 11

@@ -73,10 +73,11 @@ void* driver_entry(const char* name) { return (void*)drv<void*>(name); }
 
 namespace mt {
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
-cudaError_t launch_any(const void* fn, dim3 grid, dim3 block, void** args, cudaStream_t s, bool cooperative) {
+cudaError_t launch_any(const void* fn, dim3 grid, dim3 block, void** args, cudaStream_t s, bool cooperative,
+                       size_t dyn_smem) {
   count_launch();
-  if (cooperative) return cudaLaunchCooperativeKernel(fn, grid, block, args, 0, s);
-  return cudaLaunchKernel(fn, grid, block, args, 0, s);
+  if (cooperative) return cudaLaunchCooperativeKernel(fn, grid, block, args, dyn_smem, s);
+  return cudaLaunchKernel(fn, grid, block, args, dyn_smem, s);
 }
 }  // namespace mt
 

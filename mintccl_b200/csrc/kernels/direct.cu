@@ -8,8 +8,18 @@ template <class TI, class TO>
 static cudaError_t go_direct(const MtDevComm* comms, const DirectArgs& a, int nctas, int nlocal, cudaStream_t s) {
   DirectArgs args = a;
   void* p[] = {(void*)&comms, (void*)&args};
-  return launch_any((const void*)direct_kernel<TI, TO, kDirectThreads>, dim3(nctas, nlocal), dim3(kDirectThreads), p, s,
-                    nlocal > 1);
+  const void* fn = (const void*)direct_kernel<TI, TO, kDirectThreads>;
+  size_t smem = 0;
+  if (a.variant == 4) {  // the copy-engine variants stage their pieces in dynamic shared memory
+    static bool raised = false;   // per instantiation; the attribute belongs to the function, not to a device
+    if (!raised) {
+      cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBulkSmemBytes);
+      if (e != cudaSuccess) return e;
+      raised = true;
+    }
+    smem = kBulkSmemBytes;
+  }
+  return launch_any(fn, dim3(nctas, nlocal), dim3(kDirectThreads), p, s, nlocal > 1, smem);
 }
 // dtype: elements of the input; out_dtype: elements of the output (the same, or fp32 for a 16-bit input, or a
 // 16-bit type for an fp32 input: the sum is rounded once, into the output type).

@@ -22,6 +22,7 @@
 #pragma once
 #include <type_traits>
 #include "../device/proto_ll128.cuh"
+#include "../device/tc_prims.cuh"
 
 namespace mt {
 
@@ -44,7 +45,8 @@ struct DirectArgs {
   uint64_t nbytes;               // AG/RS/A2A: bytes per shard; others: message bytes (input bytes)
   int32_t op;
   int32_t root;
-  int32_t variant;               // all-reduce: 0 two-shot, 1 one-shot; all-gather/all-to-all: 0 push, 1 pull;
+  int32_t variant;               // all-reduce: 0 two-shot, 1 one-shot; all-gather/all-to-all: 0 push, 1 pull, 4 bulk push;
+                                 // broadcast: 4 bulk pull + replicate (the copy engine variants need dynamic shared memory);
                                  // broadcast: 0 root pushes, 1 peers pull, 2 pull + replicate (every rank reads 1/n from the root and stores it to all);
                                  // reduce: 0 root sums, 2 NVLS reduce-scatter + gather into the root, 3 the others sum and store into the root
   int32_t nvls;                  // use multimem instructions
@@ -325,9 +327,111 @@ __device__ __forceinline__ void bcast_fanout(const MtDevComm& c, const uint8_t* 
   }
 }
 
+// ---- copy-engine variants ---------------------------------------------------------------------------
+// One thread per CTA drives bulk copies (cp.async.bulk): a piece of the source is fetched into a ring of
+// shared-memory slots and stored from there to every destination, so that each byte is read from HBM (or
+// pulled over NVLink) once however many peers receive it, a CTA keeps up to kBulkSlots x kBulkPiece bytes in
+// flight without holding them in registers, and a few tens of CTAs saturate the link.  Loads run kBulkLag
+// pieces ahead of the stores.  Nothing here replicates a load across a cluster; the only multi-destination
+// operation is the loop over peers issuing one store each.  Every wait is bounded.
+constexpr uint32_t kBulkPiece = 32768;
+constexpr int kBulkSlots = 6, kBulkLag = 3;
+constexpr uint32_t kBulkSmemBytes = kBulkSlots * kBulkPiece + 1024;   // + room to align the ring to 1024 bytes
+
+struct BulkJob {
+  const uint8_t* src;
+  uint64_t nbytes;                 // multiple of 16
+  int32_t ndst;
+  uint8_t* dst[MT_MAX_RANKS];
+};
+struct BulkCtl {
+  uint64_t full[kBulkSlots];
+  int abort;
+  int njobs;
+  BulkJob jobs[MT_MAX_RANKS];
+};
+
+__device__ __forceinline__ bool bulk_mbar_wait(uint64_t* bar, uint32_t parity, uint64_t timeout_ns) {
+  uint32_t spins = 0;
+  uint64_t t0 = 0;
+  while (!tc::mbar_try_wait(bar, parity)) {
+    if ((++spins & 0x3ffu) == 0) {
+      const uint64_t now = globaltimer();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > timeout_ns) return false;
+    }
+  }
+  return true;
+}
+
+// Runs the jobs of ctl (thread 0 of the CTA only).  Returns false if a load never completed.
+static __device__ bool bulk_run(BulkCtl* ctl, uint8_t* ring, uint64_t timeout_ns) {
+  using namespace tc;
+  for (int s = 0; s < kBulkSlots; ++s) mbar_init(&ctl->full[s], 1);
+  fence_barrier_init();
+  uint32_t total = 0;
+  for (int j = 0; j < ctl->njobs; ++j) total += (uint32_t)mt_div_up(ctl->jobs[j].nbytes, kBulkPiece);
+  // two cursors over (job, piece): `l` for loads, `t` for stores
+  int lj = 0, tj = 0;
+  uint64_t lo = 0, to = 0;
+  bool ok = true;
+  for (uint32_t i = 0; ok && i < total + kBulkLag; ++i) {
+    if (i < total) {
+      while (lo >= ctl->jobs[lj].nbytes) {
+        ++lj;
+        lo = 0;
+      }
+      const BulkJob& J = ctl->jobs[lj];
+      const uint64_t left = J.nbytes - lo;
+      const uint32_t nb = (uint32_t)(left < kBulkPiece ? left : kBulkPiece);
+      const uint32_t slot = i % kBulkSlots;
+      // the stores that last used this slot (piece i - kBulkSlots) must have finished reading it
+      if (i >= kBulkSlots) asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kBulkSlots - kBulkLag - 1) : "memory");
+      mbar_expect_tx(&ctl->full[slot], nb);
+      bulk_load_1d(ring + (uint64_t)slot * kBulkPiece, J.src + lo, nb, &ctl->full[slot]);
+      lo += nb;
+    }
+    if (i >= kBulkLag) {
+      const uint32_t k = i - kBulkLag;
+      while (to >= ctl->jobs[tj].nbytes) {
+        ++tj;
+        to = 0;
+      }
+      const BulkJob& J = ctl->jobs[tj];
+      const uint64_t left = J.nbytes - to;
+      const uint32_t nb = (uint32_t)(left < kBulkPiece ? left : kBulkPiece);
+      const uint32_t slot = k % kBulkSlots;
+      if (!bulk_mbar_wait(&ctl->full[slot], (k / kBulkSlots) & 1, timeout_ns)) {
+        ok = false;
+        break;
+      }
+      for (int d = 0; d < J.ndst; ++d)
+        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(J.dst[d] + to),
+                     "r"(smem_u32(ring + (uint64_t)slot * kBulkPiece)), "r"(nb)
+                     : "memory");
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      to += nb;
+    }
+  }
+  // every store has completed (not merely left shared memory) before the CTA goes on to the exit barrier,
+  // whose release publishes them
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  return ok;
+}
+
+// Are all the addresses of the jobs multiples of 16?  (Sizes are cut to multiples of 16 by the caller.)
+__device__ __forceinline__ bool bulk_aligned(const BulkCtl* ctl) {
+  uint64_t mis = 0;
+  for (int j = 0; j < ctl->njobs; ++j) {
+    mis |= (uint64_t)(uintptr_t)ctl->jobs[j].src;
+    for (int d = 0; d < ctl->jobs[j].ndst; ++d) mis |= (uint64_t)(uintptr_t)ctl->jobs[j].dst[d];
+  }
+  return (mis & 15) == 0;
+}
+
 template <class TI, class TO, int NTHREADS>
 __device__ void direct_body(const MtDevComm& c, const DirectArgs& a, int lr, int cta, int ncta, int* s_fail,
-                            const uint8_t** s_in, uint8_t** s_out) {
+                            const uint8_t** s_in, uint8_t** s_out, BulkCtl* ctl, uint8_t* ring) {
   using T = TI;
   constexpr bool kSame = CastInfo<TI, TO>::kSame;
   const int n = c.nranks, me = c.rank;
@@ -356,12 +460,45 @@ __device__ void direct_body(const MtDevComm& c, const DirectArgs& a, int lr, int
             // a tail cannot be sent with 16-byte multimem stores
             for (uint64_t o = r.lo + (nvec << 4) + threadIdx.x; o < r.hi; o += NTHREADS)
               for (int p = 0; p < n; ++p) *(volatile uint8_t*)(P.out[p] + (uint64_t)me * B + o) = in[o];
-          } else if (a.variant == 0) {
-            for (int d = 0; d < n; ++d) {
-              const int p = (me + d) % n;
-              uint8_t* dst = P.out[p] + (uint64_t)me * B;
-              if (p == me && in == dst) continue;
-              copy_range<NTHREADS, false, true>(in + r.lo, dst + r.lo, r.hi - r.lo);
+          } else if (a.variant == 0 || a.variant == 4) {
+            bool done = false;
+            if (a.variant == 4) {
+              // copy engine: each piece of my shard is read once and stored to every rank from shared memory
+              if (threadIdx.x == 0) {
+                BulkJob& J = ctl->jobs[0];
+                J.src = in + r.lo;
+                J.nbytes = (r.hi - r.lo) & ~15ull;
+                J.ndst = 0;
+                for (int d = 1; d <= n; ++d) {   // the peers first, my own copy last
+                  const int p = (me + d) % n;
+                  uint8_t* dst = P.out[p] + (uint64_t)me * B;
+                  if (p == me && in == dst) continue;
+                  J.dst[J.ndst++] = dst + r.lo;
+                }
+                ctl->njobs = 1;
+                ctl->abort = bulk_aligned(ctl) ? 0 : 2;   // 2: not aligned, the threads copy instead
+                if (ctl->abort == 0 && !bulk_run(ctl, ring, c.timeout_ns)) {
+                  ctl->abort = 1;
+                  report_error(c, MT_ERR_TIMEOUT_FLAG, cta, MT_WHERE_BULK, 0, 0, 0);
+                }
+              }
+              __syncthreads();
+              done = ctl->abort != 2;
+              if (done && ctl->abort == 0) {   // the last < 16 bytes
+                for (uint64_t o = r.lo + ((r.hi - r.lo) & ~15ull) + threadIdx.x; o < r.hi; o += NTHREADS)
+                  for (int p = 0; p < n; ++p) {
+                    uint8_t* dst = P.out[p] + (uint64_t)me * B;
+                    if (!(p == me && in == dst)) *(volatile uint8_t*)(dst + o) = in[o];
+                  }
+              }
+            }
+            if (!done) {
+              for (int d = 0; d < n; ++d) {
+                const int p = (me + d) % n;
+                uint8_t* dst = P.out[p] + (uint64_t)me * B;
+                if (p == me && in == dst) continue;
+                copy_range<NTHREADS, false, true>(in + r.lo, dst + r.lo, r.hi - r.lo);
+              }
             }
           } else {
             for (int d = 0; d < n; ++d) {
@@ -380,10 +517,36 @@ __device__ void direct_body(const MtDevComm& c, const DirectArgs& a, int lr, int
     case DOP_ALLTOALL: {
       if constexpr (kSame) {
         const MtRange r = mt_split(B, ncta, cta, kSplitAlignDirect);
-        if (r.hi > r.lo) {
+        bool done = false;
+        if (r.hi > r.lo && a.variant == 4) {
+          // copy engine: one stream per peer, block p of my input into slot `me` of p's output
+          if (threadIdx.x == 0) {
+            for (int d = 0; d < n; ++d) {
+              const int p = (me + 1 + d) % n;
+              BulkJob& J = ctl->jobs[d];
+              J.src = in + (uint64_t)p * B + r.lo;
+              J.nbytes = (r.hi - r.lo) & ~15ull;
+              J.ndst = 1;
+              J.dst[0] = P.out[p] + (uint64_t)me * B + r.lo;
+            }
+            ctl->njobs = n;
+            ctl->abort = bulk_aligned(ctl) ? 0 : 2;
+            if (ctl->abort == 0 && !bulk_run(ctl, ring, c.timeout_ns)) {
+              ctl->abort = 1;
+              report_error(c, MT_ERR_TIMEOUT_FLAG, cta, MT_WHERE_BULK, 0, 0, 0);
+            }
+          }
+          __syncthreads();
+          done = ctl->abort != 2;
+          if (done && ctl->abort == 0) {
+            for (uint64_t o = r.lo + ((r.hi - r.lo) & ~15ull) + threadIdx.x; o < r.hi; o += NTHREADS)
+              for (int p = 0; p < n; ++p) *(volatile uint8_t*)(P.out[p] + (uint64_t)me * B + o) = in[(uint64_t)p * B + o];
+          }
+        }
+        if (r.hi > r.lo && !done) {
           for (int d = 0; d < n; ++d) {
             const int p = (me + d) % n;
-            if (a.variant == 0) {  // push block p of my input into slot `me` of p's output
+            if (a.variant == 0 || a.variant == 4) {  // push block p of my input into slot `me` of p's output
               uint8_t* dst = P.out[p] + (uint64_t)me * B;
               copy_range<NTHREADS, false, true>(in + (uint64_t)p * B + r.lo, dst + r.lo, r.hi - r.lo);
             } else {  // pull block `me` of p's input into slot p of my output
@@ -441,7 +604,7 @@ __device__ void direct_body(const MtDevComm& c, const DirectArgs& a, int lr, int
     case DOP_BROADCAST: {
       if constexpr (kSame) {
         const MtRange r = mt_split(B, ncta, cta, kSplitAlignDirect);
-        if (a.variant == 2) {
+        if (a.variant == 2 || a.variant == 4) {
           // pull + replicate: rank j fetches sub-slice j straight from the root's buffer and replicates it
           // to everybody (one multimem.st per vector, or plain stores to every peer).  The root's link only
           // carries each byte once, the replication is spread over all ranks (a single source of multicast
@@ -455,7 +618,34 @@ __device__ void direct_body(const MtDevComm& c, const DirectArgs& a, int lr, int
               if (me == a.root) nvls_bcast_range<NTHREADS, false>(src, c.mc + a.mc_out_off + r.lo + sm.lo, nb >> 4);
               else nvls_bcast_range<NTHREADS, true>(src, c.mc + a.mc_out_off + r.lo + sm.lo, nb >> 4);
             } else {
-              bcast_fanout<NTHREADS>(c, src, P, r.lo + sm.lo, nb, me == a.root && in == out);
+              bool done = false;
+              if (a.variant == 4) {
+                // copy engine: the sub-slice crosses the root's link once (a bulk load from the root's memory)
+                // and is stored to every rank from shared memory
+                const bool skip_self = me == a.root && in == out;
+                if (threadIdx.x == 0) {
+                  BulkJob& J = ctl->jobs[0];
+                  J.src = src;
+                  J.nbytes = nb & ~15ull;
+                  J.ndst = 0;
+                  for (int d = 1; d <= n; ++d) {
+                    const int p = (me + d) % n;
+                    if (p == me && skip_self) continue;
+                    J.dst[J.ndst++] = P.out[p] + r.lo + sm.lo;
+                  }
+                  ctl->njobs = 1;
+                  ctl->abort = bulk_aligned(ctl) ? 0 : 2;
+                  if (ctl->abort == 0 && !bulk_run(ctl, ring, c.timeout_ns)) {
+                    ctl->abort = 1;
+                    report_error(c, MT_ERR_TIMEOUT_FLAG, cta, MT_WHERE_BULK, 0, 0, 0);
+                  }
+                }
+                __syncthreads();
+                done = ctl->abort != 2;
+                if (done && ctl->abort == 0 && (nb & 15))
+                  bcast_fanout<NTHREADS>(c, src + (nb & ~15ull), P, r.lo + sm.lo + (nb & ~15ull), nb & 15, skip_self);
+              }
+              if (!done) bcast_fanout<NTHREADS>(c, src, P, r.lo + sm.lo, nb, me == a.root && in == out);
             }
           }
           break;
@@ -537,11 +727,14 @@ __device__ void direct_body(const MtDevComm& c, const DirectArgs& a, int lr, int
 
 template <class TI, class TO, int NTHREADS>
 __global__ void __launch_bounds__(NTHREADS, 1) direct_kernel(const MtDevComm* comms, DirectArgs a) {
+  extern __shared__ uint8_t dyn_smem[];   // kBulkSmemBytes for the copy-engine variants, else nothing
   __shared__ int s_fail;
   __shared__ const uint8_t* s_in[MT_MAX_RANKS];
   __shared__ uint8_t* s_out[MT_MAX_RANKS];
+  __shared__ BulkCtl ctl;
   const int lr = blockIdx.y;
-  direct_body<TI, TO, NTHREADS>(comms[lr], a, lr, blockIdx.x, gridDim.x, &s_fail, s_in, s_out);
+  uint8_t* ring = (uint8_t*)(((uintptr_t)dyn_smem + 1023) & ~(uintptr_t)1023);
+  direct_body<TI, TO, NTHREADS>(comms[lr], a, lr, blockIdx.x, gridDim.x, &s_fail, s_in, s_out, &ctl, ring);
 }
 
 }  // namespace mt

@@ -16,7 +16,8 @@ constexpr int kLLThreads = 256;
 
 // Launch helper: plain launch for one local rank, cooperative launch (all CTAs guaranteed resident)
 // for an emulated world whose ranks wait on each other inside one grid.
-cudaError_t launch_any(const void* fn, dim3 grid, dim3 block, void** args, cudaStream_t s, bool cooperative);
+cudaError_t launch_any(const void* fn, dim3 grid, dim3 block, void** args, cudaStream_t s, bool cooperative,
+                       size_t dyn_smem = 0);
 void count_launch();
 
 cudaError_t launch_ring_simple(int dtype, const MtDevComm* comms, const RingArgs& a, int nch, int nlocal, cudaStream_t s);

@@ -450,6 +450,13 @@ class Communicator:
             n = 32 + (nbytes - (2 << 20)) // (256 << 10)
         return max(1, min(cap, n))
 
+    def _bulk_ctas(self, nbytes: int) -> int:
+        """CTAs of a copy-engine variant: each keeps 192 KiB in flight, so one per 256 KiB up to MINTCCL_BULK_CTAS."""
+        cap = self.cfg.bulk_ctas
+        if self.emulated:
+            cap = min(cap, 148 // self.nlocal)
+        return max(1, min(cap, (nbytes + (256 << 10) - 1) // (256 << 10)))
+
     def _pick_proto(self, nbytes: int, proto: Optional[str]) -> int:
         p = proto or self.cfg.proto
         if self.world_size == 1:
@@ -603,9 +610,9 @@ class Communicator:
 
     _ALGOS = {
         "allreduce": ("auto", "ring", "direct", "nvls", "ll", "oneshot"),
-        "allgather": ("auto", "ring", "direct", "nvls", "pull"),
+        "allgather": ("auto", "ring", "direct", "nvls", "pull", "bulk"),
         "reducescatter": ("auto", "ring", "direct", "nvls"),
-        "broadcast": ("auto", "ring", "direct", "nvls", "pull", "push", "nvls1"),
+        "broadcast": ("auto", "ring", "direct", "nvls", "pull", "push", "nvls1", "bulk"),
         "reduce": ("auto", "ring", "direct", "nvls", "direct1", "nvls1"),
     }
 
@@ -777,11 +784,15 @@ class Communicator:
                 algo = "nvls"
             else:
                 algo = "direct" if self._peer_ok(outs) else "ring"
-        if algo in ("direct", "nvls", "pull"):
+        if algo in ("direct", "nvls", "pull", "bulk"):
             if algo == "nvls" and not (self.nvls and symm):
                 raise ValueError("algo=nvls needs the multicast mapping and a symmetric output buffer")
             pull = algo == "pull"
-            self._launch_direct(N.DOP_ALLGATHER, ins, outs, B, dt, variant=1 if pull else 0, nvls=algo == "nvls",
+            # "bulk": the push through the copy engine (cp.async.bulk), each piece of the shard read once and
+            # stored to every rank from shared memory; few CTAs (nch) are enough
+            if algo == "bulk" and nch is None:
+                nch = self._bulk_ctas(B)
+            self._launch_direct(N.DOP_ALLGATHER, ins, outs, B, dt, variant=1 if pull else (4 if algo == "bulk" else 0), nvls=algo == "nvls",
                                 nctas=nch, peers_read_in=pull, peers_write_out=not pull,
                                 in_from_out=pull and inp is None, in_extra=self.rank * B)
         else:
@@ -867,7 +878,7 @@ class Communicator:
                 algo = "direct"   # one hop: the root pushes (two ranks) or everybody pulls a part and replicates it
             else:
                 algo = "ring"     # LL128 chain for small messages
-        if algo in ("direct", "nvls", "pull", "push", "nvls1"):
+        if algo in ("direct", "nvls", "pull", "push", "nvls1", "bulk"):
             if algo in ("nvls", "nvls1") and not (self.nvls and symm):
                 raise ValueError(f"algo={algo} needs the multicast mapping and a symmetric buffer")
             # "direct"/"nvls": pull + replicate (every rank reads one sub-slice from the root and stores it to
@@ -875,8 +886,10 @@ class Communicator:
             # everybody; "pull": everybody reads the root; "nvls1": only the root issues multicast stores.
             # With two ranks pull + replicate is the plain push.  The multicast stores of pull + replicate move
             # whole 16-byte vectors; the plain variant takes any size and alignment.
-            replicate = self.world_size > 2 and (algo == "direct" or nbytes % 16 == 0)
-            variant = {"pull": 1, "push": 0, "nvls1": 0}.get(algo, 2 if replicate else 0)
+            replicate = self.world_size > 2 and (algo in ("direct", "bulk") or nbytes % 16 == 0)
+            variant = {"pull": 1, "push": 0, "nvls1": 0, "bulk": 4}.get(algo, 2 if replicate else 0)
+            if algo == "bulk" and nch is None:
+                nch = self._bulk_ctas(nbytes)
             self._launch_direct(N.DOP_BROADCAST, ts, ts, nbytes, dt, root=root, variant=variant,
                                 nvls=algo in ("nvls", "nvls1"), nctas=nch, peers_read_in=variant != 0,
                                 peers_write_out=variant != 1)
@@ -961,12 +974,14 @@ class Communicator:
         if n == 1:
             outs[0].copy_(ins[0])
             return
-        if algo not in (None, "auto", "push", "pull", "direct"):
-            raise ValueError("alltoall: algo is push (default) or pull")
+        if algo not in (None, "auto", "push", "pull", "direct", "bulk"):
+            raise ValueError("alltoall: algo is push (default), pull or bulk (push through the copy engine)")
+        if algo == "bulk" and nch is None:
+            nch = self._bulk_ctas(B)
         pull = (algo == "pull") or (algo in (None, "auto") and not self._peer_ok(outs) and self._peer_ok(ins))
         if not self._peer_ok(ins if pull else outs):
             raise ValueError("alltoall needs an output (push) or an input (pull) the peers can address")
-        self._launch_direct(N.DOP_ALLTOALL, ins, outs, B, dt, variant=1 if pull else 0, nctas=nch,
+        self._launch_direct(N.DOP_ALLTOALL, ins, outs, B, dt, variant=1 if pull else (4 if algo == "bulk" else 0), nctas=nch,
                             peers_read_in=pull, peers_write_out=not pull)
 
     # ------------------------------------------------------------------------------ point to point

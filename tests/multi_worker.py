@@ -89,7 +89,7 @@ def ordinary_and_cast(c, rank, n):
                 c.symm_free(t)
             torch.cuda.synchronize()
             c.control.barrier()
-    seen = stats.snapshot()
+    seen = stats.snapshot(skip_idle=False)
     assert seen["ring_simple"]["calls"] == 0 and seen["ring_ll128"]["calls"] == 0 and seen["direct"]["calls"] > 0, seen
     # 16-bit -> fp32 and fp32 -> 16-bit
     for narrow in (torch.bfloat16, torch.float16):
