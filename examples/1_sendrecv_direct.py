@@ -11,6 +11,7 @@ import torch
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 import mintccl_b200 as m  # noqa: E402
+from mintccl_b200.utils import selftest as st  # noqa: E402
 
 rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
 cuda = torch.cuda.is_available()
@@ -37,6 +38,10 @@ else:
     (m.send(buf, 1) if rank == 0 else m.recv(buf, 0)) if rank < 2 else None
     m.sync()
 check("equal", rank != 1 or torch.equal(buf.cpu(), payload))
+if st.enabled() and rank < 2:   # MINTCCL_TEST_MODE: dist.send / dist.recv of the same payload (1_sendrecv_direct.py:93-107)
+    theirs = st.oracle(comm).sendrecv(payload.to(buf.device), 0, 1)
+    if rank == 1:
+        check("oracle", st.compare(rank, "send/recv", buf, theirs, exact=True))
 
 if cuda:
     comm.check()

@@ -11,6 +11,7 @@ import torch
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 import mintccl_b200 as m  # noqa: E402
+from mintccl_b200.utils import selftest as st  # noqa: E402
 
 rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
 cuda = torch.cuda.is_available()
@@ -30,8 +31,11 @@ root = int(os.environ.get("ROOT_TEMP", 0))
 dev = "cuda" if cuda else "cpu"
 want = torch.randn(count, generator=torch.Generator().manual_seed(root))
 buf = torch.randn(count, generator=torch.Generator().manual_seed(rank)).to(dev)
+before = buf.clone()
 m.broadcast(buf, root)
 check("equal", torch.equal(buf.cpu(), want))
+if st.enabled():   # MINTCCL_TEST_MODE: the same broadcast through torch.distributed (4_broadcast.py:110-126)
+    check("oracle", st.compare(rank, "broadcast", buf, st.oracle(comm).broadcast(before, root), exact=True))
 
 if cuda:
     comm.check()

@@ -11,6 +11,7 @@ import torch
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 import mintccl_b200 as m  # noqa: E402
+from mintccl_b200.utils import selftest as st  # noqa: E402
 
 rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
 cuda = torch.cuda.is_available()
@@ -33,6 +34,10 @@ buf = parts[rank].clone().to(dev)
 m.reduce(buf, root)
 ref = sum(p.float() for p in parts)
 check("close", rank != root or torch.allclose(buf.cpu().float(), ref, rtol=1e-2, atol=4e-2))
+if st.enabled():   # MINTCCL_TEST_MODE: dist.reduce(SUM) on the same inputs (5_reduce.py:138-155)
+    theirs = st.oracle(comm).reduce(parts[rank].clone().to(dev), root)
+    if rank == root:
+        check("oracle", st.compare(rank, "reduce", buf, theirs, exact=False, roundings=2 * world))
 
 if cuda:
     comm.check()

@@ -11,6 +11,7 @@ import torch
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 import mintccl_b200 as m  # noqa: E402
+from mintccl_b200.utils import selftest as st  # noqa: E402
 
 rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
 cuda = torch.cuda.is_available()
@@ -34,6 +35,8 @@ for mode in ("temporal", "spatial"):
     buf[rank] = parts[rank].to(dev)
     m.allgather(buf, mode=mode)
     check(mode, torch.equal(buf.cpu(), torch.stack(parts)))
+    if st.enabled():   # MINTCCL_TEST_MODE: dist.all_gather_into_tensor (6_allgather.py:172-179)
+        check("oracle", st.compare(rank, f"allgather {mode}", buf, st.oracle(comm).all_gather(parts[rank].to(dev)), exact=True))
 
 if cuda:
     comm.check()

@@ -11,6 +11,7 @@ import torch
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 import mintccl_b200 as m  # noqa: E402
+from mintccl_b200.utils import selftest as st  # noqa: E402
 
 rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
 cuda = torch.cuda.is_available()
@@ -33,6 +34,9 @@ buf = full[rank].clone().to(dev)
 m.reducescatter(buf)
 ref = sum(f.float() for f in full)[rank]
 check("close", torch.allclose(buf[rank].cpu().float(), ref, rtol=1e-2, atol=4e-2))
+if st.enabled():   # MINTCCL_TEST_MODE: dist.reduce_scatter_tensor on the same inputs (7_reducescatter.py:105-117)
+    check("oracle", st.compare(rank, "reducescatter", buf[rank], st.oracle(comm).reduce_scatter(full[rank].clone().to(dev)),
+                               exact=False, roundings=2 * world))
 
 if cuda:
     comm.check()

@@ -11,6 +11,7 @@ import torch
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 import mintccl_b200 as m  # noqa: E402
+from mintccl_b200.utils import selftest as st  # noqa: E402
 
 rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
 cuda = torch.cuda.is_available()
@@ -30,8 +31,11 @@ dev = "cuda" if cuda else "cpu"
 parts = [torch.randn(count, generator=torch.Generator().manual_seed(r)).to(torch.float16) for r in range(world)]
 ref = sum(p.float() for p in parts)
 buf = parts[rank].clone().to(dev)
-m.allreduce(buf)                                             # ordinary tensor: ring
-check("ring", torch.allclose(buf.cpu().float(), ref, rtol=1e-2, atol=4e-2))
+m.allreduce(buf)                                             # ordinary tensor: shared with the peers on first use
+check("ordinary", torch.allclose(buf.cpu().float(), ref, rtol=1e-2, atol=4e-2))
+if st.enabled():   # MINTCCL_TEST_MODE: dist.all_reduce on the same inputs
+    check("oracle", st.compare(rank, "allreduce", buf, st.oracle(comm).all_reduce(parts[rank].clone().to(dev)),
+                               exact=False, roundings=2 * world))
 if cuda:
     sym = comm.symm_empty(count, torch.float16)              # symmetric tensor: direct or NVLS
     sym.copy_(parts[rank])

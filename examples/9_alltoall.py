@@ -11,6 +11,7 @@ import torch
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 import mintccl_b200 as m  # noqa: E402
+from mintccl_b200.utils import selftest as st  # noqa: E402
 
 rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
 cuda = torch.cuda.is_available()
@@ -34,6 +35,8 @@ out = comm.symm_empty((world, n), torch.float32) if cuda else torch.empty(world,
 m.alltoall(inp, out)
 want = torch.stack([torch.arange(rank * n, (rank + 1) * n, dtype=torch.float32) + 1000 * p for p in range(world)])
 check("equal", torch.equal(out.cpu(), want))
+if st.enabled():   # MINTCCL_TEST_MODE: dist.all_to_all_single on the same input
+    check("oracle", st.compare(rank, "alltoall", out, st.oracle(comm).all_to_all(inp), exact=True))
 
 if cuda:
     comm.check()

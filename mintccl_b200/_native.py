@@ -80,6 +80,7 @@ def lib():
     sig("mt_stats_get", i32, i32, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64))
     sig("mt_stats_reset", None)
     sig("mt_comm_create", vp, i32, i32, i32, C.POINTER(MtConfig))
+    sig("mt_layout_user_off", u64, i32, C.POINTER(MtConfig))
     sig("mt_comm_create_emulated", vp, i32, i32, C.POINTER(MtConfig))
     sig("mt_comm_destroy", None, vp)
     sig("mt_comm_heap_kind", i32, vp)
@@ -118,6 +119,7 @@ def lib():
     sig("mt_ll_allreduce", i32, vp, vp, i32, pp, pp, u64)
     sig("mt_ll_capacity", u64, vp)
     sig("mt_p2p", i32, vp, vp, i32, i32, vp, vp, u64, i32, i32)
+    sig("mt_p2p_mode", i32, vp, vp, i32, i32, vp, vp, u64, i32, i32, i32)
     sig("mt_gemm", i32, vp, vp, vp, vp, i32, i32, i32, i32, i32)
     sig("mt_gemm_mxfp8", i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32)
     sig("mt_sim_direct", i32, i32, i32, i32, C.c_uint32, i32, i32, i32, i32, u64)
@@ -134,6 +136,7 @@ def lib():
     sig("mt_find_ring", i32, C.POINTER(C.c_double), i32, ip)
     sig("mt_find_route", i32, C.POINTER(C.c_double), i32, i32, i32, ip)
     sig("mt_topo_probe", i32, i32, C.POINTER(C.c_double), i32, u64)
+    sig("mt_topo_probe_pair", i32, i32, i32, u64, C.POINTER(C.c_double))
     _lib = L
     return L
 

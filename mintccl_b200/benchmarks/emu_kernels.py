@@ -43,8 +43,10 @@ def main() -> None:
     esz = torch.empty((), dtype=dtype).element_size()
     nbytes = int(a.mib * (1 << 20))
     numel = nbytes // esz // n * n
-    cfg = Config.from_env(max_channels=min(32, 148 // n), num_blocks=min(32, 148 // n), buff_size=1 << 21,
-                          heap_bytes=(192 << 20) + 6 * nbytes, scratch_bytes=1 << 20, wait_timeout_ms=3000)
+    # control region: 16 channels x n peers x (1 MiB Simple + 512 KiB LL128 FIFOs) stays under 128 MiB for n <= 8
+    nchan = min(16, 148 // n)
+    cfg = Config.from_env(max_channels=nchan, num_blocks=nchan, buff_size=1 << 20, heap_bytes=(256 << 20) + 8 * nbytes,
+                          scratch_bytes=1 << 20, wait_timeout_ms=3000)
     w = emulated(n, 0, cfg)
     nch = a.nch or None
     moved = None   # bytes one rank's part of the kernel reads + writes (algorithmic)

@@ -161,6 +161,12 @@ static int check_cfg(const MtConfig* cfg, int nranks) {
   return 0;
 }
 
+uint64_t mt_layout_user_off(int nranks, const MtConfig* cfg) {
+  return mt_make_layout(nranks, cfg->nchannels, cfg->simple_slot_bytes, cfg->simple_slots, cfg->ll128_slot_bytes,
+                        cfg->ll128_slots, cfg->ll_bytes, cfg->scratch_bytes, cfg->heap_bytes)
+      .user_off;
+}
+
 MtComm* mt_comm_create(int rank, int nranks, int device, const MtConfig* cfg) {
   if (check_cfg(cfg, nranks)) return nullptr;
   if (cudaSetDevice(device) != cudaSuccess) {
@@ -226,6 +232,12 @@ MtComm* mt_comm_create_emulated(int nranks, int device, const MtConfig* cfg) {
   c->device = device;
   c->heap_kind = 1;
   fill_layout(c, cfg, nranks);
+  if (c->L.user_off > cfg->heap_bytes) {
+    // the FIFOs and control words alone are larger than the heap: kernels would run off its end
+    fail("heap_bytes smaller than the control region (" + std::to_string(c->L.user_off) + " bytes)");
+    delete c;
+    return nullptr;
+  }
   c->heap_bytes = mt_round_up(cfg->heap_bytes, 2ull << 20);
   c->L.heap_bytes = c->heap_bytes;
   for (int r = 0; r < nranks; ++r) {
@@ -638,7 +650,13 @@ int mt_ll_allreduce(MtComm* c, void* stream, int dtype, const void* const* in, v
 
 int mt_p2p(MtComm* c, void* stream, int src_rank, int dst_rank, const void* src_ptr, void* dst_ptr, uint64_t nbytes,
            int pull, int nctas) {
+  return mt_p2p_mode(c, stream, src_rank, dst_rank, src_ptr, dst_ptr, nbytes, pull, nctas, 0);
+}
+
+int mt_p2p_mode(MtComm* c, void* stream, int src_rank, int dst_rank, const void* src_ptr, void* dst_ptr, uint64_t nbytes,
+                int pull, int nctas, int mode) {
   if (check_ready(c)) return -1;
+  if (mode < 0 || mode > 2) return fail("bad copy mode");
   if (src_rank == dst_rank || src_rank < 0 || dst_rank < 0 || src_rank >= c->nranks || dst_rank >= c->nranks)
     return fail("bad ranks");
   if (nctas < 1 || nctas > 148) return fail("nctas out of range");
@@ -646,6 +664,7 @@ int mt_p2p(MtComm* c, void* stream, int src_rank, int dst_rank, const void* src_
   mt::P2pArgs a;
   memset(&a, 0, sizeof(a));
   a.nbytes = nbytes;
+  a.mode = mode;
   a.copier_reads_remote = pull ? 1 : 0;
   const uint64_t seq = ++c->p2p_seq[copier][passive];
   const uint64_t done = (c->p2p_done[copier][passive] += (uint64_t)nctas);

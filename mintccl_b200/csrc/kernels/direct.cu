@@ -42,7 +42,18 @@ cudaError_t launch_direct(int dtype, int out_dtype, const MtDevComm* comms, cons
 cudaError_t launch_p2p(const MtDevComm* comms, const P2pArgs& a, int nctas, int nlocal, cudaStream_t s) {
   P2pArgs args = a;
   void* p[] = {(void*)&comms, (void*)&args};
-  return launch_any((const void*)p2p_kernel<kP2pThreads>, dim3(nctas, nlocal), dim3(kP2pThreads), p, s, nlocal > 1);
+  const void* fn = (const void*)p2p_kernel<kP2pThreads>;
+  size_t smem = 0;
+  if (a.mode == 2) {
+    static bool raised = false;
+    if (!raised) {
+      cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBulkSmemBytes);
+      if (e != cudaSuccess) return e;
+      raised = true;
+    }
+    smem = kBulkSmemBytes;
+  }
+  return launch_any(fn, dim3(nctas, nlocal), dim3(kP2pThreads), p, s, nlocal > 1, smem);
 }
 template <class T>
 static cudaError_t go_ll(const MtDevComm* comms, const LLArgs& a, int nctas, int nlocal, cudaStream_t s) {

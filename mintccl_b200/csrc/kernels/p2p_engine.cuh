@@ -24,7 +24,36 @@ struct P2pArgs {
   uint64_t seq[MT_MAX_RANKS];      // ready sequence number of this transfer (per ordered pair)
   uint64_t done_target[MT_MAX_RANKS];  // cumulative CTA count the passive side waits for
   int32_t copier_reads_remote;     // pull (1): src is in the peer's memory; push (0): dst is
+  int32_t mode;                    // how the payload moves: 0 system-scope relaxed 16-byte loads / stores,
+                                   // 1 volatile loads and weak stores, 2 bulk copies staged in shared memory
 };
+
+// The same copy with the weakest qualifiers that are still correct for payload that is published by a later
+// release: weak 16-byte stores, volatile (never L1-cached) loads of peer memory.
+template <int NTHREADS, bool REMOTE_SRC>
+__device__ __forceinline__ void copy_range_weak(const uint8_t* src, uint8_t* dst, uint64_t nbytes) {
+  if ((((uintptr_t)src | (uintptr_t)dst) & 15) != 0) {
+    copy_range<NTHREADS, REMOTE_SRC, !REMOTE_SRC>(src, dst, nbytes);
+    return;
+  }
+  const uint64_t nvec = nbytes >> 4;
+  constexpr int kU = 8;
+  for (uint64_t base = 0; base < nvec; base += (uint64_t)NTHREADS * kU) {
+    u128 v[kU];
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      const uint64_t i = base + (uint64_t)u * NTHREADS + threadIdx.x;
+      if (i < nvec) v[u] = REMOTE_SRC ? load128(src + (i << 4)) : load128_stream(src + (i << 4));
+    }
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      const uint64_t i = base + (uint64_t)u * NTHREADS + threadIdx.x;
+      if (i < nvec) *reinterpret_cast<u128*>(dst + (i << 4)) = v[u];
+    }
+  }
+  for (uint64_t o = (nvec << 4) + threadIdx.x; o < nbytes; o += NTHREADS)
+    *reinterpret_cast<volatile uint8_t*>(dst + o) = *reinterpret_cast<const volatile uint8_t*>(src + o);
+}
 
 __device__ __forceinline__ void red_release_sys_add_u64(uint64_t* p, uint64_t v) {
   asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
@@ -32,6 +61,8 @@ __device__ __forceinline__ void red_release_sys_add_u64(uint64_t* p, uint64_t v)
 
 template <int NTHREADS>
 __global__ void __launch_bounds__(NTHREADS, 1) p2p_kernel(const MtDevComm* comms, P2pArgs a) {
+  extern __shared__ uint8_t dyn_smem[];   // kBulkSmemBytes in mode 2
+  __shared__ BulkCtl ctl;
   __shared__ int s_fail;
   const int lr = blockIdx.y;
   const MtDevComm& c = comms[lr];
@@ -69,10 +100,36 @@ __global__ void __launch_bounds__(NTHREADS, 1) p2p_kernel(const MtDevComm* comms
   const uint8_t* src = (const uint8_t*)a.src[lr];
   uint8_t* dst = (uint8_t*)a.dst[lr];
   if (r.hi > r.lo) {
-    if (a.copier_reads_remote) copy_range<NTHREADS, true, false>(src + r.lo, dst + r.lo, r.hi - r.lo);
-    else copy_range<NTHREADS, false, true>(src + r.lo, dst + r.lo, r.hi - r.lo);
+    bool done = false;
+    if (a.mode == 2 && ((((uintptr_t)src | (uintptr_t)dst) + r.lo) & 15) == 0) {
+      if (threadIdx.x == 0) {
+        ctl.jobs[0].src = src + r.lo;
+        ctl.jobs[0].nbytes = (r.hi - r.lo) & ~15ull;
+        ctl.jobs[0].ndst = 1;
+        ctl.jobs[0].dst[0] = dst + r.lo;
+        ctl.njobs = 1;
+        uint8_t* ring = (uint8_t*)(((uintptr_t)dyn_smem + 1023) & ~(uintptr_t)1023);
+        if (!bulk_run(&ctl, ring, c.timeout_ns)) {
+          s_fail = 1;
+          report_error(c, MT_ERR_TIMEOUT_FLAG, blockIdx.x, MT_WHERE_BULK, 0, 0, 0);
+        }
+      }
+      const uint64_t tail = (r.hi - r.lo) & ~15ull;
+      for (uint64_t o = r.lo + tail + threadIdx.x; o < r.hi; o += NTHREADS) *(volatile uint8_t*)(dst + o) = src[o];
+      done = true;
+    }
+    if (!done) {
+      if (a.mode == 1) {
+        if (a.copier_reads_remote) copy_range_weak<NTHREADS, true>(src + r.lo, dst + r.lo, r.hi - r.lo);
+        else copy_range_weak<NTHREADS, false>(src + r.lo, dst + r.lo, r.hi - r.lo);
+      } else {
+        if (a.copier_reads_remote) copy_range<NTHREADS, true, false>(src + r.lo, dst + r.lo, r.hi - r.lo);
+        else copy_range<NTHREADS, false, true>(src + r.lo, dst + r.lo, r.hi - r.lo);
+      }
+    }
   }
   __syncthreads();
+  if (s_fail) return;
   if (threadIdx.x == 0) {
     fence_acq_rel_sys();
     red_release_sys_add_u64(&theirs->done, 1);

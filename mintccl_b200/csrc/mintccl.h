@@ -43,6 +43,9 @@ void mt_stats_reset(void);
 // Real communicator: one rank per process.  Steps: create -> export -> (exchange) -> import peers ->
 // [multicast create/import/bind] -> finalize.
 MtComm* mt_comm_create(int rank, int nranks, int device, const MtConfig* cfg);
+// Bytes of the control region (FIFOs, flow-control words, barrier slots, ...) this configuration needs at the start
+// of the heap; creation fails when heap_bytes is smaller.  Pure arithmetic, no GPU.
+uint64_t mt_layout_user_off(int nranks, const MtConfig* cfg);
 // Emulated world: `nranks` ranks on one GPU in one process; kernels are launched once for all of them
 // (cooperative launch, gridDim.y = nranks).  Used by single-GPU tests and benchmarks.
 MtComm* mt_comm_create_emulated(int nranks, int device, const MtConfig* cfg);
@@ -109,6 +112,10 @@ uint64_t mt_ll_capacity(MtComm* c);
 // pull != 0: the receiver copies (reads the sender's memory); else the sender copies.
 int mt_p2p(MtComm* c, void* stream, int src_rank, int dst_rank, const void* src_ptr, void* dst_ptr, uint64_t nbytes,
            int pull, int nctas);
+// The same with the way the payload moves chosen by the caller: 0 system-scope relaxed 16-byte loads / stores (what
+// mt_p2p does), 1 volatile loads and weak stores, 2 bulk copies (cp.async.bulk) staged in shared memory.
+int mt_p2p_mode(MtComm* c, void* stream, int src_rank, int dst_rank, const void* src_ptr, void* dst_ptr, uint64_t nbytes,
+                int pull, int nctas, int mode);
 
 // ---- tcgen05 GEMM and its fusions with collectives (bf16, fp32 accumulate; B is [N, K] like nn.Linear) ----
 int mt_gemm(void* stream, const void* A, const void* B, void* C, int M, int N, int K, int ldc, int nctas);
@@ -156,6 +163,7 @@ int mt_sim_direct(int nranks, int nctas, int iters, uint32_t seed, int only_op, 
 int mt_find_ring(const double* bw, int n, int* out);                          // returns length (n+1) or 0
 int mt_find_route(const double* bw, int n, int src, int dst, int* out);       // returns length or 0
 int mt_topo_probe(int ndev, double* bw, int measure, uint64_t probe_bytes);   // fills n*n matrix (GB/s or 1.0)
+int mt_topo_probe_pair(int src, int dst, uint64_t probe_bytes, double* gbs);  // one pair: GB/s, 0 without peer access
 
 #ifdef __cplusplus
 }

@@ -62,14 +62,31 @@ def send(buff: torch.Tensor, peer: int) -> None:
     get_comm(buff).send(buff, peer)
 
 
+_profile_next_sync = False
+
+
 def recv(buff: torch.Tensor, peer: int, profile: bool = False) -> None:
+    """Post a receive.  ``profile=True`` brackets the transfer (which runs inside the next :func:`sync`) with a
+    profiler capture range, as 1_sendrecv_direct.py:73-79 does around its kernel."""
+    global _profile_next_sync
+    _profile_next_sync = _profile_next_sync or bool(profile)
     get_comm(buff).recv(buff, peer)
 
 
 def sync() -> None:
     """Runs every posted send/recv; all ranks must call it (jump hosts included)."""
+    global _profile_next_sync
     c = _default if _default is not None else _default_cpu
-    (c or init()).sync()
+    c = c or init()
+    if _profile_next_sync and torch.cuda.is_available():
+        from ..utils.profiler import profile_range
+        _profile_next_sync = False
+        with profile_range("mintccl_b200.sync"):
+            c.sync()
+            torch.cuda.synchronize()
+    else:
+        _profile_next_sync = False
+        c.sync()
 
 
 def broadcast(buff: torch.Tensor, root: int = 0, **kw) -> None:

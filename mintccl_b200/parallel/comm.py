@@ -338,7 +338,9 @@ class Communicator:
         return st
 
     def check(self) -> None:
-        """Synchronise and raise :class:`CollectiveError` if any device-side wait gave up."""
+        """Raise :class:`CollectiveError` if any device-side wait gave up.  Reading the status record waits for all
+        work queued on the device (``mt_comm_status`` synchronises it), so after ``check()`` returns every
+        collective launched so far has completed."""
         for lr in range(self.nlocal):
             st = self.status(lr)
             if st.code != 0 or st.abort != 0:
@@ -1014,17 +1016,22 @@ class Communicator:
         self._launch_ring(N.OP_SENDRECV, ins, outs, nbytes, N.DT_U8, self._pick_proto(nbytes, proto), chain=route,
                           nch=nch)
 
+    _P2P_MODES = {"sys": 0, "weak": 1, "bulk": 2}
+
     def p2p_copy(self, src_rank: int, dst_rank: int, src_ptr: int, dst_ptr: int, nbytes: int, pull: bool = True,
-                 nctas: Optional[int] = None) -> None:
+                 nctas: Optional[int] = None, mode: Optional[str] = None) -> None:
         """One direct copy over a peer-mapped pointer (both ranks call this with the same arguments; the
-        pointer of the remote side must be valid in the copier's address space)."""
+        pointer of the remote side must be valid in the copier's address space).  ``mode``: "sys" (16-byte
+        system-scope loads / stores from every thread), "weak" (volatile loads, weak stores) or "bulk" (the copy
+        engine, staged in shared memory); default ``MINTCCL_P2P_MODE`` or "sys"."""
         if self.emulated or self.rank in (src_rank, dst_rank):
-            nctas = self._direct_ctas(nbytes, nctas)
-            N.check(self.lib.mt_p2p(self._handle, self._stream(), src_rank, dst_rank, src_ptr, dst_ptr, nbytes,
-                                    1 if pull else 0, nctas), "mt_p2p")
+            m = self._P2P_MODES[(mode or os.environ.get("MINTCCL_P2P_MODE", "sys")).lower()]
+            nctas = self._direct_ctas(nbytes, nctas) if (m != 2 or nctas is not None) else self._bulk_ctas(nbytes)
+            N.check(self.lib.mt_p2p_mode(self._handle, self._stream(), src_rank, dst_rank, src_ptr, dst_ptr, nbytes,
+                                         1 if pull else 0, nctas, m), "mt_p2p")
 
     def sendrecv_direct(self, src_rank: int, dst_rank: int, buff: TensorOrList, pull: bool = True,
-                        nctas: Optional[int] = None) -> None:
+                        nctas: Optional[int] = None, mode: Optional[str] = None) -> None:
         """Direct send/recv of a symmetric tensor: ``buff`` of ``src_rank`` is copied into ``buff`` of
         ``dst_rank`` by a single kernel on the copying side (the receiver when ``pull``), which waits for the
         other side's ready signal and answers with a done signal (1_sendrecv_direct.py:60-79 has no such
@@ -1041,7 +1048,7 @@ class Communicator:
         else:
             sp = L.mt_comm_heap_ptr(self._handle, 0, src_rank) + off
             dp = L.mt_comm_heap_ptr(self._handle, 0, dst_rank) + off
-        self.p2p_copy(src_rank, dst_rank, sp, dp, nbytes, pull, nctas)
+        self.p2p_copy(src_rank, dst_rank, sp, dp, nbytes, pull, nctas, mode)
 
     def register(self, t: torch.Tensor) -> List[int]:
         """Make an ordinary CUDA tensor readable and writable by every peer: returns, for every rank, the

@@ -179,16 +179,15 @@ def ring_min_bandwidth(ring: Route, topo: Topology) -> float:
 
 
 def get_p2p_speed(src: int, dst: int, size: int = 32 << 20) -> float:
-    """Measured copy bandwidth ``src -> dst`` in GB/s (one warm-up copy, one timed copy of ``size`` bytes)."""
+    """Measured copy bandwidth ``src -> dst`` in GB/s (one warm-up copy, one timed copy of ``size`` bytes); 0.0
+    when the two devices have no peer access.  Only this pair is probed (topology.py:96-125 of the reference)."""
     L = _native()
     if L is None:
         raise RuntimeError("get_p2p_speed needs the native library and a GPU")
-    import torch
-    n = torch.cuda.device_count()
-    m = (C.c_double * (n * n))()
-    if L.mt_topo_probe(n, m, 1, size) < 0:
-        raise RuntimeError("topology probe failed")
-    return float(m[src * n + dst])
+    gbs = C.c_double(0.0)
+    if L.mt_topo_probe_pair(src, dst, size, C.byref(gbs)) < 0:
+        raise RuntimeError(f"no such device pair: {src} -> {dst}")
+    return float(gbs.value)
 
 
 def get_topology(topo: str = "topo.json", measure: Optional[bool] = None, ndev: Optional[int] = None) -> Topology:

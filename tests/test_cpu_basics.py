@@ -267,3 +267,21 @@ def test_ctypes_signatures_match_the_c_header():
     assert not wrong, wrong
     # functions without a ctypes signature would be called with default int conversions: none may be left
     assert not missing, missing
+
+
+def test_heap_smaller_than_its_control_region_is_refused():
+    """The FIFOs and control words are sized by the channel count; a heap that cannot hold them must be refused
+    when the communicator is created (the layout arithmetic needs no GPU), never found out by a kernel."""
+    import ctypes as C
+    from mintccl_b200 import _native as N
+    lib = N.lib()
+    lay_fn = lib.mt_layout_user_off
+    lay_fn.restype = C.c_uint64
+    lay_fn.argtypes = [C.c_int, C.POINTER(N.MtConfig)]
+    mc = N.MtConfig(nchannels=32, simple_slot_bytes=512 << 10, simple_slots=4, ll128_slot_bytes=128 << 10, ll128_slots=4,
+                    ll_bytes=256 << 10, scratch_bytes=1 << 20, heap_bytes=288 << 20, timeout_ms=1000, heap_kind=1)
+    need = lay_fn(4, C.byref(mc))
+    assert need > mc.heap_bytes                      # 32 channels x 4 peers x 2.5 MiB of FIFOs alone are 320 MiB
+    mc.nchannels = 16
+    mc.simple_slot_bytes = 256 << 10
+    assert lay_fn(4, C.byref(mc)) < (128 << 20)

@@ -18,3 +18,16 @@ def test_example_on_cpu(script):
                         os.path.join(ROOT, "examples", script)], cwd=ROOT, env=env, capture_output=True, text=True, timeout=200)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert "False" not in r.stdout
+
+
+@pytest.mark.parametrize("script", [f for f in EXAMPLES if f[0] in "1456789" and not f.startswith("10")])
+def test_example_self_test_mode_against_torch_distributed(script):
+    """MINTCCL_TEST_MODE=1: every script also runs the torch.distributed equivalent (gloo here, NCCL on GPUs) and
+    prints the comparison, like the reference's scripts do against NCCL."""
+    env = dict(os.environ, MINTCCL_TEST_COUNT="4096", CUDA_VISIBLE_DEVICES="", MINTCCL_TEST_MODE="1",
+               MINTCCL_TEST_VERBOSE="1")
+    r = subprocess.run([sys.executable, "-m", "mintccl_b200.launch", "-np", "2", "--timeout", "120",
+                        os.path.join(ROOT, "examples", script)], cwd=ROOT, env=env, capture_output=True, text=True, timeout=200)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "vs torch.distributed" in r.stdout and "False" not in r.stdout
+    assert "torch.dist   head" in r.stdout          # MINTCCL_TEST_VERBOSE

@@ -466,11 +466,13 @@ def test_direct_sendrecv_symmetric():
         b.fill_(float(r))
     bufs[1].copy_(torch.randn(1_000_000, device="cuda"))
     want = bufs[1].clone()
-    for pull in (True, False):
-        bufs[3].zero_()
-        w.sendrecv_direct(1, 3, bufs, pull=pull)
-        w.check()
-        assert torch.equal(bufs[3], want)
+    for mode in ("sys", "weak", "bulk"):
+        for pull in (True, False):
+            for view in (slice(None), slice(3, 999_990)):     # the second one is not 16-byte aligned
+                bufs[3].zero_()
+                w.sendrecv_direct(1, 3, [b[view] for b in bufs], pull=pull, mode=mode, nctas=7)
+                w.check()
+                assert torch.equal(bufs[3][view], want[view]), (mode, pull)
     w.symm_free(bufs)
 
 
