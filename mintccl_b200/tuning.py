@@ -53,8 +53,15 @@ class TuningTable:
 
     @classmethod
     def from_env(cls) -> Optional["TuningTable"]:
+        """``MINTCCL_TUNING_FILE``: a table to use; ``none`` (or ``0``): the built-in policy only.  Unset: the table
+        shipped with the package (``tuning_b200.json``, measured on HGX B200 boards), if there is one."""
         path = os.environ.get("MINTCCL_TUNING_FILE", "")
-        return cls.load(path) if path else None
+        if path.strip().lower() in ("none", "0", "off"):
+            return None
+        if path:
+            return cls.load(path)
+        shipped = os.path.join(os.path.dirname(os.path.abspath(__file__)), "tuning_b200.json")
+        return cls.load(shipped) if os.path.exists(shipped) else None
 
     def dump(self, path: str) -> None:
         rows = [r for k in sorted(self.rows) for r in self.rows[k]]
@@ -63,32 +70,43 @@ class TuningTable:
 
     # ---------------------------------------------------------------------------------------------- build
     @classmethod
-    def from_sweep(cls, rows: Iterable[dict], impl: str = "mintccl", symmetric: bool = True) -> "TuningTable":
-        """Best (algorithm, CTA count) per collective, rank count and size out of the rows ``benchmarks/sweep.py``
-        prints; neighbouring sizes with the same choice merge into one row, and a row reaches up to the geometric
-        mean of its last size and the next measured one."""
-        best: Dict[Tuple[str, int, int], dict] = {}
+    def from_sweep(cls, rows: Iterable[dict], impl: str = "mintccl", symmetric: Optional[bool] = None,
+                   margin: float = 0.05) -> "TuningTable":
+        """Best (algorithm, CTA count) per collective, rank count, kind of memory and size out of the rows
+        ``benchmarks/sweep.py`` prints.  The automatic choice (``algo == "auto"``) is the yardstick: a row is only
+        written where a named algorithm beat it by more than ``margin`` (timing noise must not flip choices), and
+        says ``auto`` where nothing did, so that the built-in policy keeps deciding there.  Neighbouring sizes with
+        the same choice merge into one row, and a row reaches up to the geometric mean of its last size and the next
+        measured one.  ``symmetric``: None = from each row's ``memory`` field (heap / ordinary)."""
+        cands: Dict[Tuple[str, int, bool, int], List[dict]] = {}
         for r in rows:
             if r.get("impl") != impl:
                 continue
-            k = (r["collective"], int(r["n"]), int(r["bytes"]))
-            if k not in best or r["us"] < best[k]["us"]:
-                best[k] = r
+            sym = symmetric if symmetric is not None else (str(r.get("memory", "heap")) == "heap")
+            cands.setdefault((r["collective"], int(r["n"]), sym, int(r["bytes"])), []).append(r)
+        groups: Dict[Tuple[str, int, bool], List[Tuple[int, Tuple[str, int]]]] = {}
+        for (coll, n, sym, nbytes), rs in cands.items():
+            auto = [r for r in rs if r["algo"] == "auto" and not r.get("ctas")]
+            best = min(rs, key=lambda r: r["us"])
+            choice = ("auto", 0)
+            if best["algo"] != "auto" or best.get("ctas"):
+                if not auto or best["us"] < (1.0 - margin) * min(r["us"] for r in auto):
+                    choice = (best["algo"], int(best.get("ctas") or 0))
+            groups.setdefault((coll, n, sym), []).append((nbytes, choice))
         out: List[dict] = []
-        groups: Dict[Tuple[str, int], List[Tuple[int, dict]]] = {}
-        for (coll, n, nbytes), r in best.items():
-            groups.setdefault((coll, n), []).append((nbytes, r))
-        for (coll, n), items in sorted(groups.items()):
+        for (coll, n, sym), items in sorted(groups.items()):
             items.sort()
-            for i, (nbytes, r) in enumerate(items):
-                choice = (r["algo"], int(r.get("ctas") or 0))
+            if all(c == ("auto", 0) for _, c in items):
+                continue
+            for i, (nbytes, choice) in enumerate(items):
                 nxt = items[i + 1][0] if i + 1 < len(items) else None
                 upto = int(math.sqrt(nbytes * nxt)) if nxt else nbytes
-                if out and out[-1]["collective"] == coll and out[-1]["nranks"] == n and \
-                        (out[-1]["algo"], out[-1]["nch"] or 0) == choice:
-                    out[-1]["max_bytes"] = upto
+                last = out[-1] if out else None
+                if last and (last["collective"], last["nranks"], last["symmetric"]) == (coll, n, sym) and \
+                        (last["algo"], last["nch"] or 0) == choice:
+                    last["max_bytes"] = upto
                 else:
-                    out.append({"collective": coll, "nranks": n, "max_bytes": upto, "symmetric": symmetric,
+                    out.append({"collective": coll, "nranks": n, "max_bytes": upto, "symmetric": sym,
                                 "algo": choice[0], "nch": choice[1] or None})
         return cls(out)
 
@@ -108,12 +126,16 @@ def main() -> None:
     ap = argparse.ArgumentParser(description="Build a tuning table from sweep results")
     ap.add_argument("sweeps", nargs="+", help="outputs of mintccl_b200/benchmarks/sweep.py (one per rank count)")
     ap.add_argument("-o", "--out", required=True)
-    ap.add_argument("--ordinary", action="store_true", help="the sweep ran on ordinary (not symmetric) tensors")
+    ap.add_argument("--ordinary", action="store_true",
+                    help="treat every row as measured on ordinary (not symmetric) tensors; default: the rows' own "
+                         "`memory` field")
+    ap.add_argument("--margin", type=float, default=0.05,
+                    help="a named algorithm must beat the automatic choice by this fraction to get a row")
     a = ap.parse_args()
     rows: List[dict] = []
     for p in a.sweeps:
         rows += _read_rows(p)
-    t = TuningTable.from_sweep(rows, symmetric=not a.ordinary)
+    t = TuningTable.from_sweep(rows, symmetric=False if a.ordinary else None, margin=a.margin)
     t.dump(a.out)
     print(f"{sum(len(v) for v in t.rows.values())} rows -> {a.out}")
 
