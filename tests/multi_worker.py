@@ -15,7 +15,7 @@ def gen(rank, numel, dtype, seed0=0):
     return torch.randn(numel, generator=g, device="cuda", dtype=torch.float32).to(dtype)
 
 
-def close(got, srcs, dtype, hops=1):
+def close(got, srcs, dtype, hops=1, what=""):
     """Element-wise bound from the arithmetic: one rounding of an fp32 sum for the one-hop paths, `hops` roundings
     of partial sums (each at most sum |x_r|) for a ring; see tests/test_gpu_emulated.py::assert_sum_close."""
     ref = sum(s.float() for s in srcs)
@@ -25,7 +25,8 @@ def close(got, srcs, dtype, hops=1):
     bound = (1.01 * half * ref.abs() if hops <= 1 or dtype == torch.float32 else 1.01 * half * hops * absum) + acc_err
     bound = bound + torch.finfo(dtype).smallest_normal * torch.finfo(dtype).eps
     err = (got.float() - ref).abs()
-    assert not bool((err > bound).any()), f"outside the bound by {float((err - bound).max()):.3e} ({dtype}, hops={hops})"
+    assert not bool((err > bound).any()), \
+        f"{what}: outside the bound by {float((err - bound).max()):.3e} ({dtype}, hops={hops}, {got.numel()} elements)"
 
 
 def ordinary_and_cast(c, rank, n):
@@ -147,9 +148,10 @@ def main():
                     got, hops = y, 1
                 else:
                     c.allreduce(x, algo=a)
-                    got, hops = x, 1
+                    # the switch adds in fp32 but its result can sit one rounding away from the nearest value
+                    got, hops = x, (2 if a == "nvls" else 1)
                 c.check()
-                close(got, srcs, dtype, hops)
+                close(got, srcs, dtype, hops, f"allreduce {a}")
                 c.symm_free(x)
                 c.symm_free(y)
             # all-gather / reduce-scatter / all-to-all / broadcast / reduce
@@ -173,7 +175,8 @@ def main():
                 c.control.barrier()
                 c.reducescatter(gb, out=out, mode=mode, algo=algo, proto=proto)
                 c.check()
-                close(out, [f[rank] for f in full], dtype, n if algo == "ring" else 1)
+                close(out, [f[rank] for f in full], dtype, n if algo == "ring" else (2 if algo == "nvls" else 1),
+                      f"reducescatter {algo}")
                 c.symm_free(gb)
             gi = c.symm_empty((n, numel), dtype)
             go = c.symm_empty((n, numel), dtype)
@@ -204,7 +207,7 @@ def main():
                 c.reduce(b, root=0, out=o, algo=algo)
                 c.check()
                 if rank == 0:
-                    close(o, srcs, dtype, n if algo == "ring" else 1)
+                    close(o, srcs, dtype, n if algo == "ring" else (2 if algo == "nvls" else 1), f"reduce {algo}")
                 if algo in ("direct", "nvls"):  # symmetric output: summing spread over all ranks
                     so = c.symm_zeros(numel, dtype)
                     torch.cuda.synchronize()
@@ -212,7 +215,7 @@ def main():
                     c.reduce(b, root=n - 1, out=so, algo=algo)
                     c.check()
                     if rank == n - 1:
-                        close(so, srcs, dtype, 1)
+                        close(so, srcs, dtype, 2 if algo == "nvls" else 1, f"reduce {algo} (symmetric output)")
                     c.control.barrier()
                     c.symm_free(so)
                 c.symm_free(b)
