@@ -83,7 +83,7 @@ class Config:
     max_channels: int = 64                # channels the FIFOs are sized for
     direct_ctas: int = 0                  # CTAs of direct kernels (0 = by message size, at most 128)
     nvls_ctas: int = 32                   # most CTAs of an NVLS kernel (the switch saturates with few)
-    bulk_ctas: int = 32                   # MINTCCL_BULK_CTAS: most CTAs of a copy-engine (cp.async.bulk) variant
+    bulk_ctas: int = 128                  # MINTCCL_BULK_CTAS: most CTAs of a copy-engine (cp.async.bulk) variant
     simple_slots: int = 4
     ll128_slot_bytes: int = 128 << 10
     ll128_slots: int = 4
@@ -138,7 +138,7 @@ class Config:
             max_channels=env_int("MINTCCL_MAX_CHANNELS", 64),
             direct_ctas=env_int("MINTCCL_DIRECT_CTAS", 0),
             nvls_ctas=env_int("MINTCCL_NVLS_CTAS", 32),
-            bulk_ctas=env_int("MINTCCL_BULK_CTAS", 32),
+            bulk_ctas=env_int("MINTCCL_BULK_CTAS", 128),
             simple_slots=env_int("MINTCCL_SIMPLE_SLOTS", 4),
             ll128_slot_bytes=env_int("MINTCCL_LL128_SLOT_BYTES", 128 << 10),
             ll128_slots=env_int("MINTCCL_LL128_SLOTS", 4),

@@ -105,29 +105,50 @@ struct SimplePrims {
     const bool aligned = (!(SRC || !RECV) || ((uintptr_t)src & 15) == 0) && (!DST || ((uintptr_t)dst & 15) == 0);
     if (aligned) {
       const uint64_t nvec = nbytes >> 4;
-      const uint64_t tile = (uint64_t)NTHREADS * kUnroll;
-      for (uint64_t base = 0; base < nvec; base += tile) {
+      constexpr uint64_t kTile = (uint64_t)NTHREADS * kUnroll;
+      const uint64_t full = nvec / kTile * kTile;
+      // Whole tiles: every thread moves kUnroll vectors that sit NTHREADS vectors apart, addressed from one
+      // pointer per stream plus compile-time offsets (keeps the loop inside the 128 registers a 512-thread CTA
+      // has; with one index computation and one bounds check per vector the loads of a tile spilled to local
+      // memory).  All loads of a tile are issued before the first use.
+      const uint64_t t16 = (uint64_t)tid << 4;
+      for (uint64_t base = 0; base < full; base += kTile) {
+        const uint64_t o = (base << 4) + t16;
         u128 v[kUnroll];
+        if (RECV) {
 #pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {
-          const uint64_t i = base + (uint64_t)u * NTHREADS + tid;
-          if (i < nvec) {
-            if (RECV) {
-              v[u] = load128(rslot + (i << 4));
-              if (SRC) v[u] = sum128<T>(v[u], load128_stream(src + (i << 4)));
-            } else {
-              v[u] = load128_stream(src + (i << 4));
-            }
-          }
-        }
+          for (int u = 0; u < kUnroll; ++u) v[u] = load128(rslot + o + (uint64_t)u * NTHREADS * 16);
+          if (SRC) {
+            u128 w[kUnroll];
 #pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {
-          const uint64_t i = base + (uint64_t)u * NTHREADS + tid;
-          if (i < nvec) {
-            if (SEND) store128_relaxed_sys(sslot + (i << 4), v[u]);
-            if (DST) *reinterpret_cast<u128*>(dst + (i << 4)) = v[u];
+            for (int u = 0; u < kUnroll; ++u) w[u] = load128_stream(src + o + (uint64_t)u * NTHREADS * 16);
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) v[u] = sum128<T>(v[u], w[u]);
           }
+        } else {
+#pragma unroll
+          for (int u = 0; u < kUnroll; ++u) v[u] = load128_stream(src + o + (uint64_t)u * NTHREADS * 16);
         }
+        if (SEND) {
+#pragma unroll
+          for (int u = 0; u < kUnroll; ++u) store128_relaxed_sys(sslot + o + (uint64_t)u * NTHREADS * 16, v[u]);
+        }
+        if (DST) {
+#pragma unroll
+          for (int u = 0; u < kUnroll; ++u) *reinterpret_cast<u128*>(dst + o + (uint64_t)u * NTHREADS * 16) = v[u];
+        }
+      }
+      // the vectors behind the last whole tile, one per thread and pass
+      for (uint64_t i = full + tid; i < nvec; i += NTHREADS) {
+        u128 v;
+        if (RECV) {
+          v = load128(rslot + (i << 4));
+          if (SRC) v = sum128<T>(v, load128_stream(src + (i << 4)));
+        } else {
+          v = load128_stream(src + (i << 4));
+        }
+        if (SEND) store128_relaxed_sys(sslot + (i << 4), v);
+        if (DST) *reinterpret_cast<u128*>(dst + (i << 4)) = v;
       }
       // tail of fewer than 16 bytes, element by element
       using E = typename T::elem;
@@ -157,10 +178,9 @@ struct SimplePrims {
     __syncthreads();
     if (SEND) {
       ++send_step;
-      if (tid == 0) {
-        fence_acq_rel_sys();
-        store64_release_sys(send_tail_rem, send_step);
-      }
+      // the release store is itself a system-scope fence followed by the store: the payload stores of all
+      // threads (ordered before it by the block barrier) are visible at the peer before the counter
+      if (tid == 0) store64_release_sys(send_tail_rem, send_step);
     }
     if (RECV) {
       ++recv_step;

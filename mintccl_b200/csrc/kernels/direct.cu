@@ -10,7 +10,7 @@ static cudaError_t go_direct(const MtDevComm* comms, const DirectArgs& a, int nc
   void* p[] = {(void*)&comms, (void*)&args};
   const void* fn = (const void*)direct_kernel<TI, TO, kDirectThreads>;
   size_t smem = 0;
-  if (a.variant == 4) {  // the copy-engine variants stage their pieces in dynamic shared memory
+  if (a.variant >= 4) {  // the copy-engine variants stage their pieces in dynamic shared memory
     static bool raised = false;   // per instantiation; the attribute belongs to the function, not to a device
     if (!raised) {
       cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBulkSmemBytes);

@@ -45,7 +45,7 @@ struct DirectArgs {
   uint64_t nbytes;               // AG/RS/A2A: bytes per shard; others: message bytes (input bytes)
   int32_t op;
   int32_t root;
-  int32_t variant;               // all-reduce: 0 two-shot, 1 one-shot; all-gather/all-to-all: 0 push, 1 pull, 4 bulk push;
+  int32_t variant;               // all-reduce: 0 two-shot, 1 one-shot; all-gather/all-to-all: 0 push, 1 pull, 4 bulk push, 5 bulk pull (all-gather);
                                  // broadcast: 4 bulk pull + replicate (the copy engine variants need dynamic shared memory);
                                  // broadcast: 0 root pushes, 1 peers pull, 2 pull + replicate (every rank reads 1/n from the root and stores it to all);
                                  // reduce: 0 root sums, 2 NVLS reduce-scatter + gather into the root, 3 the others sum and store into the root
@@ -501,7 +501,41 @@ __device__ void direct_body(const MtDevComm& c, const DirectArgs& a, int lr, int
               }
             }
           } else {
-            for (int d = 0; d < n; ++d) {
+            bool done = false;
+            if (a.variant == 5) {
+              // copy engine, pulling: one stream per peer from its contribution into my output
+              if (threadIdx.x == 0) {
+                int nj = 0;
+                for (int d = 1; d <= n; ++d) {   // the peers first, my own copy last
+                  const int p = (me + d) % n;
+                  const uint8_t* src = p == me ? in : P.in[p];
+                  uint8_t* dst = out + (uint64_t)p * B;
+                  if (p == me && in == dst) continue;
+                  BulkJob& J = ctl->jobs[nj++];
+                  J.src = src + r.lo;
+                  J.nbytes = (r.hi - r.lo) & ~15ull;
+                  J.ndst = 1;
+                  J.dst[0] = dst + r.lo;
+                }
+                ctl->njobs = nj;
+                ctl->abort = bulk_aligned(ctl) ? 0 : 2;
+                if (ctl->abort == 0 && nj > 0 && !bulk_run(ctl, ring, c.timeout_ns)) {
+                  ctl->abort = 1;
+                  report_error(c, MT_ERR_TIMEOUT_FLAG, cta, MT_WHERE_BULK, 0, 0, 0);
+                }
+              }
+              __syncthreads();
+              done = ctl->abort != 2;
+              if (done && ctl->abort == 0) {
+                for (uint64_t o = r.lo + ((r.hi - r.lo) & ~15ull) + threadIdx.x; o < r.hi; o += NTHREADS)
+                  for (int p = 0; p < n; ++p) {
+                    const uint8_t* src = p == me ? in : P.in[p];
+                    uint8_t* dst = out + (uint64_t)p * B;
+                    if (!(p == me && in == dst)) dst[o] = *(const volatile uint8_t*)(src + o);
+                  }
+              }
+            }
+            for (int d = 0; !done && d < n; ++d) {
               const int p = (me + d) % n;
               if (p == me) {
                 if (in != out + (uint64_t)me * B) copy_range<NTHREADS, false, false>(in + r.lo, out + (uint64_t)me * B + r.lo, r.hi - r.lo);

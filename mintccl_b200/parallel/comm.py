@@ -453,11 +453,12 @@ class Communicator:
         return max(1, min(cap, n))
 
     def _bulk_ctas(self, nbytes: int) -> int:
-        """CTAs of a copy-engine variant: each keeps 192 KiB in flight, so one per 256 KiB up to MINTCCL_BULK_CTAS."""
+        """CTAs of a copy-engine variant: one thread per CTA issues the copies, so the bytes in flight grow with
+        the CTA count; one CTA per 64 KiB up to MINTCCL_BULK_CTAS (128: measured best from 16 MiB on)."""
         cap = self.cfg.bulk_ctas
         if self.emulated:
             cap = min(cap, 148 // self.nlocal)
-        return max(1, min(cap, (nbytes + (256 << 10) - 1) // (256 << 10)))
+        return max(1, min(cap, (nbytes + (64 << 10) - 1) // (64 << 10)))
 
     def _pick_proto(self, nbytes: int, proto: Optional[str]) -> int:
         p = proto or self.cfg.proto
@@ -612,7 +613,7 @@ class Communicator:
 
     _ALGOS = {
         "allreduce": ("auto", "ring", "direct", "nvls", "ll", "oneshot"),
-        "allgather": ("auto", "ring", "direct", "nvls", "pull", "bulk"),
+        "allgather": ("auto", "ring", "direct", "nvls", "pull", "bulk", "bulkpull"),
         "reducescatter": ("auto", "ring", "direct", "nvls"),
         "broadcast": ("auto", "ring", "direct", "nvls", "pull", "push", "nvls1", "bulk"),
         "reduce": ("auto", "ring", "direct", "nvls", "direct1", "nvls1"),
@@ -786,15 +787,18 @@ class Communicator:
                 algo = "nvls"
             else:
                 algo = "direct" if self._peer_ok(outs) else "ring"
-        if algo in ("direct", "nvls", "pull", "bulk"):
+        if algo in ("direct", "nvls", "pull", "bulk", "bulkpull"):
             if algo == "nvls" and not (self.nvls and symm):
                 raise ValueError("algo=nvls needs the multicast mapping and a symmetric output buffer")
-            pull = algo == "pull"
+            pull = algo in ("pull", "bulkpull")
             # "bulk": the push through the copy engine (cp.async.bulk), each piece of the shard read once and
             # stored to every rank from shared memory; few CTAs (nch) are enough
-            if algo == "bulk" and nch is None:
+            # "bulkpull": the same engine pulling every peer's contribution (loads fill the link a little better
+            # than stores)
+            if algo in ("bulk", "bulkpull") and nch is None:
                 nch = self._bulk_ctas(B)
-            self._launch_direct(N.DOP_ALLGATHER, ins, outs, B, dt, variant=1 if pull else (4 if algo == "bulk" else 0), nvls=algo == "nvls",
+            variant = {"pull": 1, "bulk": 4, "bulkpull": 5}.get(algo, 0)
+            self._launch_direct(N.DOP_ALLGATHER, ins, outs, B, dt, variant=variant, nvls=algo == "nvls",
                                 nctas=nch, peers_read_in=pull, peers_write_out=not pull,
                                 in_from_out=pull and inp is None, in_extra=self.rank * B)
         else:

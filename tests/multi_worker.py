@@ -207,7 +207,7 @@ def main():
                 c.reduce(b, root=0, out=o, algo=algo)
                 c.check()
                 if rank == 0:
-                    close(o, srcs, dtype, n if algo == "ring" else (2 if algo == "nvls" else 1), f"reduce {algo}")
+                    close(o, srcs, dtype, n if algo == "ring" else (2 if algo.startswith("nvls") else 1), f"reduce {algo}")
                 if algo in ("direct", "nvls"):  # symmetric output: summing spread over all ranks
                     so = c.symm_zeros(numel, dtype)
                     torch.cuda.synchronize()
@@ -215,7 +215,7 @@ def main():
                     c.reduce(b, root=n - 1, out=so, algo=algo)
                     c.check()
                     if rank == n - 1:
-                        close(so, srcs, dtype, 2 if algo == "nvls" else 1, f"reduce {algo} (symmetric output)")
+                        close(so, srcs, dtype, 2 if algo.startswith("nvls") else 1, f"reduce {algo} (symmetric output)")
                     c.control.barrier()
                     c.symm_free(so)
                 c.symm_free(b)

@@ -441,6 +441,14 @@ def test_copy_engine_variants(n, numel):
         w.check()
         for b in bufs:
             assert torch.equal(b, want)
+        for use_inp in (False, True):
+            for r in range(n):
+                bufs[r].zero_()
+                bufs[r][r].copy_(src[r])
+            w.allgather(bufs, inp=src if use_inp else None, algo="bulkpull")
+            w.check()
+            for b in bufs:
+                assert torch.equal(b, want)
         full = rand(n, n * numel, dtype, seed0=63)
         ins = [f.view(n, numel) for f in full]
         outs = [torch.zeros(n * numel + off, device="cuda", dtype=dtype)[off:].view(n, numel) for _ in range(n)]
