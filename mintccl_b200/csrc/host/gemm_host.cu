@@ -248,7 +248,7 @@ static int ag_gemm_impl(MtComm* c, void* stream, const void* const* a_shard, con
   if (n > 1 && (comm_split < 1 || comm_split > ncomm)) return fail("comm_split must be in [1, ncomm]");
   a.comm_split = n > 1 ? comm_split : 1;
   a.shard_off = shard_off;
-  if (comm_mode < 0 || comm_mode > 2) return fail("comm_mode must be 0, 1 or 2");
+  if (comm_mode < 0 || comm_mode > 3) return fail("comm_mode must be 0, 1, 2 or 3");
   mt::GemmMaps maps;
   memset(&maps, 0, sizeof(maps));
   for (int lr = 0; lr < c->nlocal; ++lr) {

@@ -221,7 +221,11 @@ __device__ __forceinline__ void ag_comm_cta(const GemmArgs& a, int lr, int cc, i
     const int split = a.comm_split, ngroups = ncomm / split, grp = cc / split;
     const MtRange r = mt_split(chunk_bytes, split, cc % split, 128);
     const uint32_t ppc = (uint32_t)mt_div_up(r.hi - r.lo, COMM_PIECE);   // pieces per chunk for this CTA
-    const uint32_t npairs = (uint32_t)chunks * (uint32_t)(n - 1);       // (peer, chunk) pairs, in push order
+    // fan-out push (comm_mode 3): a piece is fetched from local memory once and stored to all n - 1 peers from
+    // shared memory, so a CTA reads 1/(n - 1) of what the pairwise push reads and has n - 1 stores in flight per
+    // load; the work units are the chunks themselves
+    const bool fan = a.comm_mode == 3;
+    const uint32_t npairs = fan ? (uint32_t)chunks : (uint32_t)chunks * (uint32_t)(n - 1);   // work units, in push order
     const uint32_t mine = grp < ngroups ? (npairs - grp + ngroups - 1) / ngroups : 0;  // pairs grp, grp+ngroups, ...
     const uint32_t total = ppc * mine;
     volatile int* ab = &cm->abort;
@@ -238,6 +242,13 @@ __device__ __forceinline__ void ag_comm_cta(const GemmArgs& a, int lr, int cc, i
       uint64_t off;
       uint32_t nb;
       locate(i, p, ci, off, nb);
+      if (fan) {
+        for (int d = 1; d < n; ++d) {
+          uint64_t* pc = (uint64_t*)(c.heap[(me + d) % n] + a.flags_off) + (uint64_t)me * chunks + ci;
+          asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(pc), "l"(1ull) : "memory");
+        }
+        return;
+      }
       // push: count on the peer, in my row of its counters; pull: count locally, in the peer's row
       uint64_t* cnt = pull ? (uint64_t*)(c.heap[me] + a.flags_off) + (uint64_t)p * chunks + ci
                            : (uint64_t*)(c.heap[p] + a.flags_off) + (uint64_t)me * chunks + ci;
@@ -272,11 +283,20 @@ __device__ __forceinline__ void ag_comm_cta(const GemmArgs& a, int lr, int cc, i
           ok = false;
           break;
         }
-        uint8_t* dst = pull ? c.heap[me] + a.gather_off + (uint64_t)p * shard_rows * row_bytes + off
-                            : c.heap[p] + a.gather_off + (uint64_t)me * shard_rows * row_bytes + off;
-        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst),
-                     "r"(smem_u32(smem + (uint64_t)s_ * COMM_PIECE)), "r"(nb)
-                     : "memory");
+        if (fan) {
+          for (int d = 1; d < n; ++d) {
+            uint8_t* pd = c.heap[(me + d) % n] + a.gather_off + (uint64_t)me * shard_rows * row_bytes + off;
+            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(pd),
+                         "r"(smem_u32(smem + (uint64_t)s_ * COMM_PIECE)), "r"(nb)
+                         : "memory");
+          }
+        } else {
+          uint8_t* dst = pull ? c.heap[me] + a.gather_off + (uint64_t)p * shard_rows * row_bytes + off
+                              : c.heap[p] + a.gather_off + (uint64_t)me * shard_rows * row_bytes + off;
+          asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst),
+                       "r"(smem_u32(smem + (uint64_t)s_ * COMM_PIECE)), "r"(nb)
+                       : "memory");
+        }
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         // A chunk is announced once its last store has COMPLETED (not merely left shared memory).  That
         // takes a round trip to the peer, so announcements trail the stores by COMM_SIGLAG pieces: up to

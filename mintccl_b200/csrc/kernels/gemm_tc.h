@@ -28,7 +28,8 @@ struct GemmArgs {
   int32_t M, N, K, ldc;
   int32_t nranks;
   int32_t ncomm;                       // AG_GEMM: CTAs that move data instead of computing; GEMM_RS: reducers
-  int32_t comm_mode;                   // AG_GEMM: 0 copy-engine push, 1 copy-engine pull, 2 push with plain stores
+  int32_t comm_mode;                   // AG_GEMM: 0 copy-engine push (one peer per piece), 1 copy-engine pull, 2 push with plain stores,
+                                       // 3 copy-engine fan-out push (every piece to all peers)
   int32_t comm_split;                  // AG_GEMM: comm CTAs that share one 128-row chunk
   int32_t raster;                      // plain GEMM: row blocks per group of the tile order (<= 1: row-major)
   uint64_t shard_off;                  // AG_GEMM pull: heap offset of every rank's own rows

@@ -65,7 +65,8 @@ class AllGatherGemm(_Fused):
     """Plan for ``allgather(a_shard)[M, K] @ w[N, K].T``: owns the gathered-input buffer and the arrival
     counters in the symmetric heap.  Create it collectively (same order on every rank), call it every step."""
 
-    MODES = {"push": 0, "pull": 1, "push_st": 2}
+    # "fan": every 32 KiB piece of this rank's rows is read once and stored to all peers from shared memory
+    MODES = {"push": 0, "pull": 1, "push_st": 2, "fan": 3}
 
     def __init__(self, comm, M: int, N_: int, K: int, ncomm: Optional[int] = None, mode: str = "push", split: int = 1,
                  fp8: bool = False):
@@ -78,6 +79,14 @@ class AllGatherGemm(_Fused):
                                     bytes_in=(nw - 1) / max(nw, 1) * M * K * (1 if fp8 else 2), fp8=fp8)
         self.split = max(1, min(split, ncomm))
         n = comm.world_size
+        if mode == "fan" and split == 1 and n > 1:
+            # the work units of the fan-out push are this rank's 128-row chunks: more comm CTAs than chunks share them
+            chunks = max(1, M // n // BM)
+            ncomm = (ncomm + 1) & ~1
+            sp = max(1, ncomm // min(ncomm, chunks))
+            while ncomm % sp:
+                sp -= 1
+            self.split = sp
         if M % (BM * n) or N_ % BN or K % BK:
             raise ValueError("M must be a multiple of 128 x world, N of 256, K of 64")
         self.M, self.N, self.K, self.ncomm = M, N_, K, ncomm

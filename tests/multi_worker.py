@@ -298,6 +298,16 @@ def main():
     if rank == route[-1]:
         assert float(got[0]) == float(route[0])
     c.control.barrier()
+    if os.environ.get("MINTCCL_TEST_PROBE") and rank == 0:
+        # link discovery on real devices: the peer-access map, and one measured pair (1 MiB copies)
+        from mintccl_b200.topology import get_p2p_speed, get_topology
+        topo = get_topology("", measure=False, ndev=n)
+        assert sorted(topo) == list(range(n)) and all(sorted(d for d, _ in topo[s]) == [d for d in range(n) if d != s]
+                                                      for s in range(n)), topo
+        bw = get_p2p_speed(0, 1, 1 << 20)
+        assert bw > 1.0, bw
+        print(f"[r0] probe 0 -> 1: {bw:.1f} GB/s at 1 MiB; discovered ring {c.ring}", flush=True)
+    c.control.barrier()
     c.close()
     print(f"[r{rank}] MULTI OK", flush=True)
 

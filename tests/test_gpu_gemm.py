@@ -54,12 +54,13 @@ def world(n):
     return _worlds[n]
 
 
+@pytest.mark.parametrize("mode", ["push", "fan"])
 @pytest.mark.parametrize("n", [1, 2, 4])
-def test_ag_gemm_emulated(n):
+def test_ag_gemm_emulated(n, mode):
     from mintccl_b200.ops.gemm import AllGatherGemm
     w_ = world(n)
     M, N, K = 128 * n * 2, 512, 256
-    plan = AllGatherGemm(w_, M, N, K, ncomm=4)
+    plan = AllGatherGemm(w_, M, N, K, ncomm=4, mode=mode)
     for it in range(3):  # counters keep growing across calls
         g = torch.Generator(device="cuda").manual_seed(it)
         shards = [torch.randn(M // n, K, generator=g, device="cuda").to(torch.bfloat16) for _ in range(n)]

@@ -32,4 +32,6 @@ def test_all_gpus():
 
 
 def test_two_gpus_ipc_heap():
-    _run(2, {"MINTCCL_HEAP": "ipc"})
+    """The cudaMalloc + cudaIpc heap, with the ring taken from a discovered and measured link map
+    (MINTCCL_TOPO_DISCOVER / MINTCCL_TOPO_MEASURE) and the pair probe of get_p2p_speed run by rank 0."""
+    _run(2, {"MINTCCL_HEAP": "ipc", "MINTCCL_TOPO_DISCOVER": "1", "MINTCCL_TOPO_MEASURE": "1", "MINTCCL_TEST_PROBE": "1"})
