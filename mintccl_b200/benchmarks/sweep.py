@@ -196,6 +196,12 @@ def main() -> None:
                         if impl == "mintccl":
                             comm.check()
                     except (ValueError, RuntimeError) as e:
+                        from mintccl_b200.parallel.comm import CollectiveError
+                        if isinstance(e, CollectiveError):
+                            # a device-side wait gave up: the communicator is unusable from here on, and every
+                            # further point would only wait out its time limit
+                            print(f"# rank {rank}: {coll} {size} {impl}:{algo} failed on the device: {e}", file=sys.stderr, flush=True)
+                            raise SystemExit(3)
                         if rank == 0:
                             print(f"# skip {coll} {size} {impl}:{algo}: {e}", file=sys.stderr)
                         continue

@@ -94,15 +94,35 @@ static bool use_pair(int M) {
   return g_pair_mode != 0 && M % 256 == 0;
 }
 
+// Tile width of a bf16 pair GEMM over `row_tiles` 256-row blocks on `nclusters` clusters: 224 columns when N
+// allows it and the waves of narrower tiles add up to less work than the waves of 256-column tiles
+// (MINTCCL_GEMM_BN=256 / 224 forces one).
+static int pick_bn(int row_tiles, int N, int nclusters, bool fp8) {
+  if (fp8 || N % 224 || nclusters < 1) return 256;
+  if (const char* e = getenv("MINTCCL_GEMM_BN")) {
+    const int v = atoi(e);
+    if (v == 224 || v == 256) return v;
+  }
+  const long w256 = (long)((row_tiles * (N / 256) + nclusters - 1) / nclusters) * 256;
+  const long w224 = (long)((row_tiles * (N / 224) + nclusters - 1) / nclusters) * 224;
+  return w224 < w256 ? 224 : 256;
+}
+
 static int gemm_pair(void* stream, const void* A, const void* sfa, const void* B, const void* sfb, void* C, int M, int N,
                      int K, int ldc, int nctas, bool fp8) {
   int dev = 0;
   cudaGetDevice(&dev);
+  int ncl = (nctas > 0 ? nctas : sm_count(dev)) / 2;
+  {
+    const int fit = mt::gemm_pair_max_clusters(mt::MODE_PLAIN, fp8);
+    if (fit > 0 && ncl > fit) ncl = fit;
+  }
+  const int bn = pick_bn(M / 256, N, ncl, fp8);
   mt::GemmMaps maps;
   mt::PairSfMaps sf;
   memset(&maps, 0, sizeof(maps));
   memset(&sf, 0, sizeof(sf));
-  if (make_map(&maps.a[0], A, M, K, 128, fp8) || make_map(&maps.b[0], B, N, K, 128, fp8)) return -1;
+  if (make_map(&maps.a[0], A, M, K, 128, fp8) || make_map(&maps.b[0], B, N, K, bn / 2, fp8)) return -1;
   maps.a2[0] = maps.a[0];
   if (fp8) {
     if (make_sf_map(&sf.sfa[0], sfa, (uint64_t)(M / 128) * (K / 128)) ||
@@ -119,11 +139,11 @@ static int gemm_pair(void* stream, const void* A, const void* sfa, const void* B
   a.nranks = 1;
   a.raster = raster_for(M, N, K, fp8 ? 1 : 2) / 2;
   a.timeout_ns = 4000000000ull;
-  const int tiles = (M / 256) * (N / kBN);
+  const int tiles = (M / 256) * (N / bn);
   int nclusters = (nctas > 0 ? nctas : sm_count(dev)) / 2;
   if (nclusters > tiles) nclusters = tiles;
   if (nclusters < 1) nclusters = 1;
-  cudaError_t e = mt::launch_gemm_pair(mt::MODE_PLAIN, maps, sf, a, nclusters, 1, (cudaStream_t)stream, fp8);
+  cudaError_t e = mt::launch_gemm_pair(mt::MODE_PLAIN, maps, sf, a, nclusters, 1, (cudaStream_t)stream, fp8, bn);
   if (e != cudaSuccess) return fail(std::string("pair gemm launch: ") + cudaGetErrorString(e));
   mthost::stat_add(fp8 ? mthost::ST_GEMM_MXFP8 : mthost::ST_GEMM, (uint64_t)(2.0 * M * N * K));
   return 0;
@@ -269,17 +289,18 @@ static int ag_gemm_impl(MtComm* c, void* stream, const void* const* a_shard, con
     // CTA pairs: 256-row tiles inside one owner's rows, B split between the two CTAs, comm CTAs in whole clusters
     mt::PairSfMaps sf;
     memset(&sf, 0, sizeof(sf));
-    for (int lr = 0; lr < c->nlocal; ++lr) {
-      if (make_map(&maps.b[lr], B[lr], N, K, 128, fp8)) return -1;
-      if (fp8 && (make_sf_map(&sf.sfa[lr], sfa[lr], (uint64_t)(M / 128) * (K / 128)) ||
-                  make_sf_map(&sf.sfb[lr], sfb[lr], (uint64_t)(N / 128) * (K / 128))))
-        return -1;
-    }
     a.ncomm = (ncomm + 1) & ~1;
     if (a.comm_split > 1 && a.ncomm % a.comm_split) return fail("comm_split must divide the (even) number of comm CTAs");
     const int nclusters = (grid - a.ncomm) / 2;
     if (nclusters < 1) return fail("not enough CTAs for the requested comm CTAs");
-    cudaError_t e2 = mt::launch_gemm_pair(mt::MODE_AG_GEMM, maps, sf, a, nclusters, c->nlocal, (cudaStream_t)stream, fp8);
+    const int bn = pick_bn(M / 256, N, nclusters, fp8);
+    for (int lr = 0; lr < c->nlocal; ++lr) {
+      if (make_map(&maps.b[lr], B[lr], N, K, bn / 2, fp8)) return -1;
+      if (fp8 && (make_sf_map(&sf.sfa[lr], sfa[lr], (uint64_t)(M / 128) * (K / 128)) ||
+                  make_sf_map(&sf.sfb[lr], sfb[lr], (uint64_t)(N / 128) * (K / 128))))
+        return -1;
+    }
+    cudaError_t e2 = mt::launch_gemm_pair(mt::MODE_AG_GEMM, maps, sf, a, nclusters, c->nlocal, (cudaStream_t)stream, fp8, bn);
     if (e2 != cudaSuccess) return fail(std::string("pair ag_gemm launch: ") + cudaGetErrorString(e2));
     mthost::stat_add(mthost::ST_AG_GEMM, (uint64_t)(2.0 * M * N * K));
     return 0;

@@ -49,9 +49,11 @@ struct PairSfMaps {
   CUtensorMap sfa[MT_MAX_RANKS];  // MXFP8: tiled scales of (the gathered) A as [atoms, 128] u32, box = one 512-byte atom
   CUtensorMap sfb[MT_MAX_RANKS];  // same for B
 };
+// bn: columns of a tile, 256, or 224 (bf16, plain GEMM and all-gather -> GEMM only; the map of B then has boxes of
+// 112 rows)
 cudaError_t launch_gemm_pair(int mode, const GemmMaps& maps, const PairSfMaps& sf, const GemmArgs& a, int nclusters,
-                             int nlocal, cudaStream_t s, bool fp8);
-int gemm_pair_max_clusters(int mode, bool fp8);
+                             int nlocal, cudaStream_t s, bool fp8, int bn = 256);
+int gemm_pair_max_clusters(int mode, bool fp8, int bn = 256);
 int gemm_pair_error();   // 1 after a wait of the pair kernel expired (synchronises), -1 on a CUDA error
 
 }  // namespace mt

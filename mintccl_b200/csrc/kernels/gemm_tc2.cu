@@ -90,15 +90,22 @@ __device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, volatil
 
 // Tile order: fused_schedule.h with 256-row tiles (mb, jb count 256-row blocks).
 using Tile = MtTile;
-template <int MODE>
+template <int MODE, int TILE_N>
 __device__ __forceinline__ Tile tile_of(const GemmArgs& a, int lr, int t) {
   static_assert(MODE_PLAIN == MT_TILE_PLAIN && MODE_AG_GEMM == MT_TILE_AG_GEMM && MODE_GEMM_RS == MT_TILE_GEMM_RS, "mode codes");
-  return mt_fused_tile(MODE, t, a.M, a.N, a.nranks, a.rank[lr], a.raster, BM2, BN);
+  return mt_fused_tile(MODE, t, a.M, a.N, a.nranks, a.rank[lr], a.raster, BM2, TILE_N);
 }
 
-template <int MODE, bool FP8>
+// TILE_N: columns of a tile, 256 or 224.  224 exists for the wave count: 8192 x 1792 (the Llama-3-8B up projection on
+// 8 ranks) is 224 tiles of 256 x 256, 3.03 waves on 74 clusters, i.e. a fourth wave for two tiles; as 256 tiles of
+// 256 x 224 it is four waves of tiles that are an eighth smaller.  bf16 only (the MXFP8 scale atoms cover 128
+// rows of B) and not for GEMM -> reduce-scatter (its staging layout is in 256-column tiles).
+template <int MODE, bool FP8, int TILE_N>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     gemm_pair_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ PairSfMaps sfmaps, GemmArgs a) {
+  static_assert(TILE_N == 256 || (TILE_N == 224 && !FP8 && MODE != MODE_GEMM_RS), "tile widths");
+  constexpr int BN = TILE_N, BNC = TILE_N / 2;             // shadow the 256-column constants of the namespace
+  constexpr uint32_t B_BYTES = BNC * 128;                   // a multiple of 1024: whole 128-byte swizzle atoms
   extern __shared__ uint8_t smem_raw[];
   const int lr = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -161,7 +168,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     if (lane == 0) {
       uint32_t it = 0;
       for (int t = cluster_id; t < tiles && !*abort_flag; t += nclusters) {
-        const Tile tc_ = tile_of<MODE>(a, lr, t);
+        const Tile tc_ = tile_of<MODE, BN>(a, lr, t);
         int arow = tc_.mb * BM2 + (int)cr * BMC;
         const int brow = tc_.nb * BN + (int)cr * BNC;
         const int sfa_row = tc_.mb * 2 + (int)cr;  // 128-row block of A in the (gathered) scale tensor
@@ -198,7 +205,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
           // the MMA thread's commit lands on the leader's barrier only: pass it on to the peer's producer
           if (leader && it >= (uint32_t)STAGES) mbar_arrive_cluster(map_to_cta(smem_u32(&ctl->empty[s]), 1));
           const uint32_t full0 = map_to_cta(smem_u32(&ctl->full[s]), 0);
-          if (leader) mbar_expect_tx(&ctl->full[s], 2 * (STAGE_BYTES + (FP8 ? SF_STAGE_BYTES : 0)));
+          if (leader) mbar_expect_tx(&ctl->full[s], 2 * (A_BYTES + B_BYTES + (FP8 ? SF_STAGE_BYTES : 0)));
           tma_load_2d_pair(sA + s * A_BYTES, amap, kb * BKE, arow, full0);
           tma_load_2d_pair(sB + s * B_BYTES, &maps.b[lr], kb * BKE, brow, full0);
           if (FP8) {
@@ -272,7 +279,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
       // the commit lands on the leader's barrier only: its first epilogue warp passes it on to the peer
       if (leader && warp == 2 && lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&ctl->acc_full[as]), 1));
       tc_fence_after();
-      const Tile tc_ = tile_of<MODE>(a, lr, t);
+      const Tile tc_ = tile_of<MODE, BN>(a, lr, t);
       // destination of this CTA's 128 rows of the tile
       uint8_t* dst;
       uint64_t ld_bytes;
@@ -294,10 +301,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + as * BN;
       const uint32_t acc_empty0 = map_to_cta(smem_u32(&ctl->acc_empty[as]), 0);
       // 4 rows per pass of 8 lanes x 16 bytes: full 128-byte lines
-      auto store_block = [&](int cb) {
+      // `nchunk` 16-byte pieces per row: 8 for a full block of 64 columns, 4 for the last half block of a 224 tile
+      auto store_block = [&](int cb, int nchunk = 8) {
 #pragma unroll
         for (int p = 0; p < 8; ++p) {
           const int rr = p * 4 + (lane >> 3), c16 = lane & 7;
+          if (c16 >= nchunk) continue;
           const uint4 v = *(const uint4*)(stg + rr * EPI_PITCH + c16 * 16);
           uint8_t* g = dst + (uint64_t)rr * ld_bytes + cb * 128 + c16 * 16;
           if (MODE == MODE_GEMM_RS) {
@@ -342,10 +351,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         }
       } else {
 #pragma unroll 1
-        for (int cb = 0; cb < BN / 64; ++cb) {
+        for (int cb = 0; cb < (BN + 63) / 64; ++cb) {
           uint32_t r0[32], r1[32];
+          const bool half = cb * 64 + 32 >= BN;   // only 32 columns left (224 = 3 x 64 + 32)
           tmem_ld_32x32(taddr + cb * 64, r0);
-          tmem_ld_32x32(taddr + cb * 64 + 32, r1);
+          if (!half) tmem_ld_32x32(taddr + cb * 64 + 32, r1);
           tmem_ld_wait();
           uint4* row = (uint4*)(stg + lane * EPI_PITCH);
 #pragma unroll
@@ -365,7 +375,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
             row[4 + j] = make_uint4(*(uint32_t*)&p0, *(uint32_t*)&p1, *(uint32_t*)&p2, *(uint32_t*)&p3);
           }
           __syncwarp();
-          store_block(cb);
+          store_block(cb, half ? 4 : 8);
           __syncwarp();
         }
         // accumulator drained: hand it back to the leader's MMA thread
@@ -404,25 +414,31 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 
 }  // namespace pair
 
-static const void* pair_fn(int mode, bool fp8) {
+static const void* pair_fn(int mode, bool fp8, int bn = 256) {
+  if (bn == 224) {
+    if (fp8) return nullptr;
+    if (mode == MODE_PLAIN) return (const void*)pair::gemm_pair_kernel<MODE_PLAIN, false, 224>;
+    if (mode == MODE_AG_GEMM) return (const void*)pair::gemm_pair_kernel<MODE_AG_GEMM, false, 224>;
+    return nullptr;
+  }
   switch (mode * 2 + (fp8 ? 1 : 0)) {
-    case MODE_PLAIN * 2: return (const void*)pair::gemm_pair_kernel<MODE_PLAIN, false>;
-    case MODE_PLAIN * 2 + 1: return (const void*)pair::gemm_pair_kernel<MODE_PLAIN, true>;
-    case MODE_AG_GEMM * 2: return (const void*)pair::gemm_pair_kernel<MODE_AG_GEMM, false>;
-    case MODE_AG_GEMM * 2 + 1: return (const void*)pair::gemm_pair_kernel<MODE_AG_GEMM, true>;
-    case MODE_GEMM_RS * 2: return (const void*)pair::gemm_pair_kernel<MODE_GEMM_RS, false>;
-    case MODE_GEMM_RS * 2 + 1: return (const void*)pair::gemm_pair_kernel<MODE_GEMM_RS, true>;
+    case MODE_PLAIN * 2: return (const void*)pair::gemm_pair_kernel<MODE_PLAIN, false, 256>;
+    case MODE_PLAIN * 2 + 1: return (const void*)pair::gemm_pair_kernel<MODE_PLAIN, true, 256>;
+    case MODE_AG_GEMM * 2: return (const void*)pair::gemm_pair_kernel<MODE_AG_GEMM, false, 256>;
+    case MODE_AG_GEMM * 2 + 1: return (const void*)pair::gemm_pair_kernel<MODE_AG_GEMM, true, 256>;
+    case MODE_GEMM_RS * 2: return (const void*)pair::gemm_pair_kernel<MODE_GEMM_RS, false, 256>;
+    case MODE_GEMM_RS * 2 + 1: return (const void*)pair::gemm_pair_kernel<MODE_GEMM_RS, true, 256>;
     default: return nullptr;
   }
 }
 
 // Clusters of this kernel that the device can hold at once.  The kernel is persistent (cluster i takes tiles
 // i, i + n, ...), so a grid with more clusters than fit would run its tail after the rest has finished.
-int gemm_pair_max_clusters(int mode, bool fp8) {
-  static int cached[6] = {0, 0, 0, 0, 0, 0};
-  const void* fn = pair_fn(mode, fp8);
+int gemm_pair_max_clusters(int mode, bool fp8, int bn) {
+  static int cached[12] = {};
+  const void* fn = pair_fn(mode, fp8, bn);
   if (!fn) return 0;
-  int& slot = cached[mode * 2 + (fp8 ? 1 : 0)];
+  int& slot = cached[(mode * 2 + (fp8 ? 1 : 0)) * 2 + (bn == 224 ? 1 : 0)];
   if (slot > 0) return slot;
   if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, pair::SMEM_BYTES) != cudaSuccess) return 0;
   int dev = 0, sms = 148;
@@ -455,10 +471,10 @@ int gemm_pair_max_clusters(int mode, bool fp8) {
 
 // Grid: 2 * nclusters GEMM CTAs followed by a.ncomm comm / reducer CTAs (even), times nlocal emulated ranks.
 cudaError_t launch_gemm_pair(int mode, const GemmMaps& maps, const PairSfMaps& sf, const GemmArgs& a, int nclusters,
-                             int nlocal, cudaStream_t s, bool fp8) {
-  const void* fn = pair_fn(mode, fp8);
+                             int nlocal, cudaStream_t s, bool fp8, int bn) {
+  const void* fn = pair_fn(mode, fp8, bn);
   if (!fn) return cudaErrorInvalidValue;
-  const int fit = gemm_pair_max_clusters(mode, fp8);  // also sets the shared-memory attribute once
+  const int fit = gemm_pair_max_clusters(mode, fp8, bn);  // also sets the shared-memory attribute once
   if (fit <= 0) return cudaErrorInvalidValue;
   const int extra = mode == MODE_PLAIN ? 0 : a.ncomm;
   if (extra & 1) return cudaErrorInvalidValue;

@@ -644,6 +644,8 @@ class Communicator:
         if hit[0].startswith("nvls") and (not self.nvls or (unit if unit is not None else nbytes) % 16
                                           or any(t.data_ptr() % 16 for t in tensors)):
             return algo, nch
+        if hit[0] not in ("auto", "ring", "ll") and not symmetric and not all(self._peer_ok([t]) for t in tensors):
+            return algo, nch     # a one-hop row, but the peers cannot address this memory
         return hit
 
     def _want_nvls(self, nbytes: int, tensors) -> bool:
@@ -783,7 +785,9 @@ class Communicator:
         if n == 1:
             algo = "ring"
         if algo == "auto":
-            if symm and self._want_nvls(B, ins + outs):
+            if B * n >= (32 << 20) and self._peer_ok(outs):
+                algo = "bulk"      # copy engine: every piece read once, stored to all ranks (676 against 615 GB/s at 1 GiB on 8 GPUs)
+            elif symm and self._want_nvls(B, ins + outs):
                 algo = "nvls"
             else:
                 algo = "direct" if self._peer_ok(outs) else "ring"
@@ -874,16 +878,14 @@ class Communicator:
         algo, nch = self._tuned("broadcast", nbytes, algo, nch, symm, ts)
         algo = self._algo(algo, "broadcast")
         if algo == "auto":
-            # A wide pipelined ring (algo="ring", 48+ channels) moves more bytes per second when broadcasts
-            # follow each other back to back (631 against 528 GB/s at 1 GiB on 4 GPUs), but a single broadcast
-            # then pays the fill time of the chain before the last rank has its data.  The multicast variant
-            # finishes on every rank at the same time, so it is the default.
-            if symm and self._want_nvls(nbytes, ts):
-                algo = "nvls"
-            elif nbytes > (64 << 10) and self._peer_ok(ts):
-                algo = "direct"   # one hop: the root pushes (two ranks) or everybody pulls a part and replicates it
+            # The pipelined chain over the FIFOs (LL128 for small messages, Simple with sub-slot steps for large
+            # ones) has no entry and exit barrier and keeps every link busy once it is full: measured fastest at
+            # every size on 4 and 8 GPUs (8 GPUs, 64 MiB: 511 GB/s against 423 for the multicast variant) and up to
+            # 64 MiB on two.  Two ranks have nothing to pipeline for large messages: the receiver pulls.
+            if self.world_size == 2 and nbytes >= (128 << 20) and self._peer_ok(ts):
+                algo = "pull"
             else:
-                algo = "ring"     # LL128 chain for small messages
+                algo = "ring"
         if algo in ("direct", "nvls", "pull", "push", "nvls1", "bulk"):
             if algo in ("nvls", "nvls1") and not (self.nvls and symm):
                 raise ValueError(f"algo={algo} needs the multicast mapping and a symmetric buffer")
@@ -931,10 +933,10 @@ class Communicator:
         if self.world_size == 1:
             algo = "ring" if not cast else "direct1"
         if algo == "auto":
-            if symm and separate and not cast and self._want_nvls(nbytes, ins + outs):
-                algo = "nvls"
-            elif separate and (cast or nbytes > (64 << 10)) and self._peer_ok(ins):
-                algo = "direct"
+            # the pipelined chain wins on 4 and 8 GPUs at every size and up to 64 MiB on two (see broadcast); a
+            # result in another element type needs the one-hop kernel
+            if cast or (self.world_size == 2 and nbytes >= (128 << 20)):
+                algo = "direct" if separate and self._peer_ok(ins) else "ring"
             else:
                 algo = "ring"
         if cast and algo not in ("direct", "direct1"):

@@ -86,12 +86,24 @@ class TuningTable:
             cands.setdefault((r["collective"], int(r["n"]), sym, int(r["bytes"])), []).append(r)
         groups: Dict[Tuple[str, int, bool], List[Tuple[int, Tuple[str, int]]]] = {}
         for (coll, n, sym, nbytes), rs in cands.items():
-            auto = [r for r in rs if r["algo"] == "auto" and not r.get("ctas")]
-            best = min(rs, key=lambda r: r["us"])
+            # per algorithm: its own default CTA count unless an explicit count beat that by more than 3 %
+            per_algo: Dict[str, Tuple[float, int]] = {}
+            for algo_name in {r["algo"] for r in rs}:
+                mine = [r for r in rs if r["algo"] == algo_name]
+                dflt = [r for r in mine if not r.get("ctas")]
+                best = min(mine, key=lambda r: r["us"])
+                if dflt and best["us"] >= 0.97 * min(r["us"] for r in dflt):
+                    per_algo[algo_name] = (min(r["us"] for r in dflt), 0)
+                else:
+                    per_algo[algo_name] = (best["us"], int(best.get("ctas") or 0))
+            if "ring" in per_algo and per_algo["ring"][1] > 64:
+                per_algo["ring"] = (per_algo["ring"][0], 64)   # the FIFOs are laid out for 64 channels: more is the same
             choice = ("auto", 0)
-            if best["algo"] != "auto" or best.get("ctas"):
-                if not auto or best["us"] < (1.0 - margin) * min(r["us"] for r in auto):
-                    choice = (best["algo"], int(best.get("ctas") or 0))
+            name = min(per_algo, key=lambda k: per_algo[k][0])
+            if name != "auto" and ("auto" not in per_algo or per_algo[name][0] < (1.0 - margin) * per_algo["auto"][0]):
+                choice = (name, per_algo[name][1])
+            elif "auto" in per_algo and per_algo["auto"][1]:
+                choice = ("auto", per_algo["auto"][1])
             groups.setdefault((coll, n, sym), []).append((nbytes, choice))
         out: List[dict] = []
         for (coll, n, sym), items in sorted(groups.items()):

@@ -11,6 +11,7 @@ from mintccl_b200.parallel.comm import Communicator
 
 class Recorder(Communicator):
     def __init__(self, world=8, nvls=True, rank=0, **cfg):   # no device, no native communicator
+        heap_mib = int(cfg.pop("_heap_mib", 64))
         cfg.setdefault("auto_register", False)      # ordinary tensors: FIFO ring unless a test shares them
         self.cfg = Config.from_env(**cfg)
         self.lib = N.lib()
@@ -18,7 +19,7 @@ class Recorder(Communicator):
         self.world_size, self.rank, self.nlocal, self.emulated, self.nvls = world, rank, 1, False, nvls
         self.device = 0
         self._plans, self._rec_key, self._pending = {}, None, []
-        self.heap = torch.zeros(64 << 20, dtype=torch.uint8)
+        self.heap = torch.empty(heap_mib << 20, dtype=torch.uint8)
         self.heap_base, self.user_off, self.heap_bytes = [self.heap.data_ptr()], 0, self.heap.numel()
         self.ll_capacity = 200 << 10
         self.ring = list(range(world))
@@ -116,24 +117,34 @@ def test_allgather_reducescatter_dispatch():
 def test_broadcast_and_reduce_dispatch():
     c = Recorder(world=8)
     x, out = c.sym(1 << 20), c.sym(1 << 20)
-    c.broadcast(x, root=3)
+    c.broadcast(x, root=3)                                                       # automatic: the pipelined chain
+    l = c.last()
+    assert l["fn"] == "mt_ring" and l["op"] == N.OP_BROADCAST and l["proto"] == N.PROTO_SIMPLE and l["root"] == 3
+    c.broadcast(x, root=3, algo="nvls")
     l = c.last()
     assert l["fn"] == "mt_direct" and l["op"] == N.DOP_BROADCAST and l["nvls"] == 1 and l["variant"] == 2 and l["root"] == 3
     c.broadcast(torch.zeros(100, dtype=torch.float16), root=1)
     assert c.last()["fn"] == "mt_ring" and c.last()["proto"] == N.PROTO_LL128    # small, ordinary memory: LL128 chain
     c.reduce(x, root=2, out=out)
+    assert c.last()["fn"] == "mt_ring" and c.last()["op"] == N.OP_REDUCE
+    c.reduce(x, root=2, out=out, algo="nvls")
     l = c.last()
     assert l["fn"] == "mt_direct" and l["op"] == N.DOP_REDUCE and l["nvls"] == 1 and l["variant"] == 2
     c.reduce(x, root=2)                                                          # in place: the ring reduces in place
     assert c.last()["fn"] == "mt_ring" and c.last()["op"] == N.OP_REDUCE
     with pytest.raises(ValueError):
         c.reduce(x, root=2, algo="direct")                                       # direct reduce needs a separate output
-    c2 = Recorder(world=2)
+    c2 = Recorder(world=2, _heap_mib=320)
     y, o2 = c2.sym(1 << 20), c2.sym(1 << 20)
     c2.broadcast(y)
-    assert c2.last()["fn"] == "mt_direct" and c2.last()["nvls"] == 0 and c2.last()["variant"] == 0   # root pushes once
-    c2.reduce(y, out=o2)
+    assert c2.last()["fn"] == "mt_ring"                                          # 2 MiB: still the chain
+    big, bigo = c2.sym(32 << 20, torch.float32), c2.sym(32 << 20, torch.float32)  # 128 MiB on two ranks: one hop
+    c2.broadcast(big)
+    assert c2.last()["fn"] == "mt_direct" and c2.last()["nvls"] == 0 and c2.last()["variant"] == 1   # the receiver pulls
+    c2.reduce(big, out=bigo)
     assert c2.last()["fn"] == "mt_direct" and c2.last()["variant"] == 0
+    c2.broadcast(y, algo="direct")
+    assert c2.last()["fn"] == "mt_direct" and c2.last()["variant"] == 0          # two ranks: the root pushes once
 
 
 def test_one_rank_world_always_takes_the_copy_path():
@@ -305,10 +316,12 @@ def test_ordinary_tensors_take_the_one_hop_kernels_once_shared():
     c.reducescatter(buf, out=torch.zeros(4096, dtype=torch.float32))
     assert c.last()["fn"] == "mt_direct" and c.last()["pub_out"] == [0] * 8    # the shard stays local: not shared
     big = torch.zeros(1 << 20, dtype=torch.float16)
-    c.broadcast(big, root=2)
+    c.broadcast(big, root=2, algo="direct")
     assert c.last()["fn"] == "mt_direct" and c.last()["variant"] == 2 and c.last()["nvls"] == 0
-    c.reduce(big, root=2, out=torch.zeros(1 << 20, dtype=torch.float16))
+    c.reduce(big, root=2, out=torch.zeros(1 << 20, dtype=torch.float16), algo="direct")
     assert c.last()["fn"] == "mt_direct" and c.last()["variant"] == 3           # the other ranks sum, the root receives
+    c.broadcast(big, root=2)                                       # automatic: the pipelined chain, any memory
+    assert c.last()["fn"] == "mt_ring"
     with pytest.raises(ValueError):
         c.allreduce(x, algo="nvls")                                # the multicast alias covers the heap only
 
@@ -318,9 +331,9 @@ def test_unaligned_views_never_reach_vector_only_paths():
     in the kernel) and never the multicast variant."""
     c = Recorder(world=4)
     x = c.sym(1 << 20)
-    c.broadcast(x[4:], root=0)                                     # 8 bytes into a 256-byte aligned allocation
+    c.broadcast(x[4:], root=0, algo="direct")                      # 8 bytes into a 256-byte aligned allocation
     l = c.last()
-    assert l["fn"] == "mt_direct" and l["nvls"] == 0
+    assert l["fn"] == "mt_direct" and l["nvls"] == 0 and l["variant"] == 2
     with pytest.raises(ValueError):
         c.broadcast(x[4:], root=0, algo="nvls")
 

@@ -42,6 +42,31 @@ def test_gemm_matches_fp32_reference(shape, gemm_kernel):
     assert torch.equal(out, out2)
 
 
+@pytest.mark.parametrize("bn", ["224", "256"])
+@pytest.mark.parametrize("shape", [(256, 1792, 128), (2048, 1792, 512), (8192, 1792, 1024)])
+def test_gemm_tile_width(shape, bn, monkeypatch):
+    """The CTA-pair GEMM with 224-column tiles (chosen by itself when that saves a wave, forced here) against
+    the fp32 reference and, bit for bit, against the 256-column tiles."""
+    from mintccl_b200 import _native as N
+    from mintccl_b200.ops.gemm import gemm
+    M, Nn, K = shape
+    g = torch.Generator(device="cuda").manual_seed(7 * M + K)
+    a = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(Nn, K, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    N.lib().mt_gemm_set_pair(1)
+    try:
+        monkeypatch.setenv("MINTCCL_GEMM_BN", bn)
+        out = gemm(a, w)
+        monkeypatch.setenv("MINTCCL_GEMM_BN", "256")
+        ref256 = gemm(a, w)
+        torch.cuda.synchronize()
+        assert N.lib().mt_gemm_pair_error() == 0
+    finally:
+        N.lib().mt_gemm_set_pair(-1)
+    close(out, ref_mm(a, w), K)
+    assert torch.equal(out, ref256)
+
+
 _worlds = {}
 
 
@@ -56,10 +81,11 @@ def world(n):
 
 @pytest.mark.parametrize("mode", ["push", "fan"])
 @pytest.mark.parametrize("n", [1, 2, 4])
-def test_ag_gemm_emulated(n, mode):
+@pytest.mark.parametrize("N", [512, 1792])       # 1792: the fused kernel picks 224-column tiles
+def test_ag_gemm_emulated(n, mode, N):
     from mintccl_b200.ops.gemm import AllGatherGemm
     w_ = world(n)
-    M, N, K = 128 * n * 2, 512, 256
+    M, K = 128 * n * 2, 256
     plan = AllGatherGemm(w_, M, N, K, ncomm=4, mode=mode)
     for it in range(3):  # counters keep growing across calls
         g = torch.Generator(device="cuda").manual_seed(it)
