@@ -198,8 +198,12 @@ def test_tuning_table_overrides_the_policy_only_where_it_applies(tmp_path, monke
     monkeypatch.setenv("MINTCCL_TUNING_FILE", path)
     again = TuningTable.from_env()
     assert again.lookup("allreduce", 8, 1 << 19) == ("direct", 48) and again.lookup("allreduce", 8, 1 << 27) is None
+    monkeypatch.setenv("MINTCCL_TUNING_FILE", "none")
+    assert TuningTable.from_env() is None                 # switched off: the built-in policy alone
     monkeypatch.delenv("MINTCCL_TUNING_FILE")
-    assert TuningTable.from_env() is None
+    shipped = TuningTable.from_env()                      # unset: the table measured on HGX B200 that ships with the package
+    assert shipped is not None and shipped.lookup("broadcast", 8, 64 << 20, True) == ("ring", None)
+    assert shipped.lookup("allreduce", 3, 1 << 20, True) is None    # no rows for rank counts that were not measured
 
 
 def test_tuning_table_from_sweep_rows():
