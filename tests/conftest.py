@@ -4,6 +4,9 @@ import sys
 import pytest
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+# The tests pin down which algorithm the built-in policy picks, so the shipped tuning table (measured choices that
+# override the policy per size) stays out of them unless a test loads one itself; child processes inherit this.
+os.environ.setdefault("MINTCCL_TUNING_FILE", "none")
 
 
 def pytest_configure(config):
