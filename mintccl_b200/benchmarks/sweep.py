@@ -52,6 +52,7 @@ def main() -> None:
                     help="comma list of MINTCCL_CHAIN_STEP_BYTES values (0 = whole slots) to try for this library's "
                          "broadcast and reduce (they only matter for algo=ring over the Simple protocol)")
     ap.add_argument("--repeats", type=int, default=5, help="timed blocks per point; the median is reported")
+    ap.add_argument("--size-mult", type=int, default=2, help="factor between consecutive sizes (2: every power of two)")
     ap.add_argument("--memory", default="heap", choices=["heap", "ordinary"],
                     help="where this library's buffers live: its symmetric heap, or ordinary torch tensors")
     ap.add_argument("--out", default="")
@@ -78,7 +79,7 @@ def main() -> None:
     s = lo
     while s <= hi:
         sizes.append(s)
-        s *= 2
+        s *= max(2, a.size_mult)
 
     def maxr(x: float) -> float:
         t = torch.tensor([x], dtype=torch.float64)

@@ -382,3 +382,24 @@ def test_reductions_into_another_element_type():
     small = c.sym(64, torch.float16)
     c.allreduce(small, out=c.sym(64, torch.float32))               # small and converting: the one-hop kernel, not LL
     assert c.last()["fn"] == "mt_direct"
+
+
+def test_tuning_table_ignores_noise_and_keeps_memory_kinds_apart():
+    """A named algorithm needs a margin over the automatic choice, an explicit CTA count needs 3 % over the algorithm's own
+    default, ring channel counts above the FIFO layout are the same thing, and rows measured on ordinary tensors do not
+    apply to heap tensors."""
+    from mintccl_b200.tuning import TuningTable
+
+    def row(algo, ctas, us, nbytes=1 << 24, memory="heap", coll="allgather"):
+        return {"collective": coll, "bytes": nbytes, "impl": "mintccl", "algo": algo, "ctas": ctas, "us": us, "n": 8, "memory": memory}
+
+    rows = [row("auto", 0, 100.0), row("bulk", 0, 97.0), row("bulk", 64, 96.0),            # 3-4 % better: noise, no row
+            row("auto", 0, 100.0, 1 << 26), row("bulk", 0, 80.0, 1 << 26), row("bulk", 128, 79.0, 1 << 26),   # bulk, default CTAs
+            row("auto", 0, 100.0, 1 << 28), row("ring", 64, 70.0, 1 << 28), row("ring", 128, 69.9, 1 << 28),
+            row("auto", 0, 50.0, 1 << 26, "ordinary"), row("direct", 64, 40.0, 1 << 26, "ordinary")]
+    t = TuningTable.from_sweep(rows)
+    assert t.lookup("allgather", 8, 1 << 24, True) == ("auto", None)
+    assert t.lookup("allgather", 8, 1 << 26, True) == ("bulk", None)
+    assert t.lookup("allgather", 8, 1 << 28, True) == ("ring", 64)
+    assert t.lookup("allgather", 8, 1 << 26, False) == ("direct", 64)
+    assert t.lookup("allgather", 8, 1 << 28, False) is None
