@@ -51,25 +51,20 @@ struct RingArgs {
 };
 
 // Step size of chain operations (send/recv over a route, broadcast, reduce).  The last of L ranks sees its first
-// byte after L - 2 extra steps, so a message of few slot-sized steps per channel spends most of its time filling
-// the chain; smaller steps shorten the fill at the price of more flag traffic per byte.  MINTCCL_CHAIN_STEP_BYTES
-// sets it (rounded down to a multiple of 128, at least 4 KiB; 0 keeps whole slots).  Unset, a channel's share of
-// the message is cut into about eight steps of at least 64 KiB and at most one slot.
-static inline uint32_t mt_chain_step_bytes(uint64_t bytes_per_channel, uint64_t slot_bytes) {
+// byte after L - 2 extra steps, so smaller steps shorten the fill of the chain; but every step costs a flag round
+// (block barrier, release store, the peer's poll), and that cost won on 8 B200: cutting a channel's share into eight
+// steps took the 64 MiB broadcast from 511 to 373 GB/s (8 - 128 MiB all slower, 256 - 512 MiB 4 % faster).  So the
+// default is whole slots; MINTCCL_CHAIN_STEP_BYTES sets a smaller step (rounded down to a multiple of 128, at least
+// 4 KiB; 0 or unset: whole slots).
+static inline uint32_t mt_chain_step_from_env() {
   const char* e = getenv("MINTCCL_CHAIN_STEP_BYTES");
-  if (e) {
-    long long v = atoll(e);
-    if (v <= 0) return 0;
-    if (v < 4096) v = 4096;
-    if (v > (1ll << 30)) v = 1ll << 30;
-    return (uint32_t)(v & ~127ll);
-  }
-  uint64_t step = bytes_per_channel / 8;
-  if (step < (64u << 10)) step = 64u << 10;
-  if (step >= slot_bytes) return 0;
-  return (uint32_t)(step & ~127ull);
+  if (!e) return 0;
+  long long v = atoll(e);
+  if (v <= 0) return 0;
+  if (v < 4096) v = 4096;
+  if (v > (1ll << 30)) v = 1ll << 30;
+  return (uint32_t)(v & ~127ll);
 }
-static inline uint32_t mt_chain_step_from_env() { return mt_chain_step_bytes(~0ull, 0); }
 
 enum Role : int {
   R_NONE = 0,
