@@ -293,12 +293,12 @@ __device__ __forceinline__ void nvls_bcast_range(const uint8_t* src, uint8_t* mc
   }
 }
 
-// Bytes [lo, lo + nbytes) of every peer's output (and of the local one unless skip_local) = src, reading
-// each vector once.  Any alignment: 16-byte vectors when src and every destination allow it, bytes otherwise
+// Bytes [lo, lo + nbytes) of every peer's output (but skip_rank's; and of the local one unless skip_local) = src,
+// reading each vector once.  Any alignment: 16-byte vectors when src and every destination allow it, bytes otherwise
 // and for the tail.
 template <int NTHREADS>
 __device__ __forceinline__ void bcast_fanout(const MtDevComm& c, const uint8_t* src, const PeerBufs& P, uint64_t lo,
-                                             uint64_t nbytes, bool skip_local) {
+                                             uint64_t nbytes, bool skip_local, int skip_rank = -1) {
   const int n = c.nranks;
   uint64_t mis = (uint64_t)(uintptr_t)src & 15;
   for (int p = 0; p < n; ++p) mis |= (uint64_t)(uintptr_t)(P.out[p] + lo) & 15;
@@ -315,14 +315,20 @@ __device__ __forceinline__ void bcast_fanout(const MtDevComm& c, const uint8_t* 
     for (int u = 0; u < kDirectUnroll; ++u) {
       const uint64_t i = base + (uint64_t)u * NTHREADS + threadIdx.x;
       if (i < nvec) {
-        for (int d = 1; d < n; ++d) store128_relaxed_sys(P.out[(c.rank + d) % n] + lo + (i << 4), v[u]);
+        for (int d = 1; d < n; ++d) {
+          const int p = (c.rank + d) % n;
+          if (p != skip_rank) store128_relaxed_sys(P.out[p] + lo + (i << 4), v[u]);
+        }
         if (!skip_local) *reinterpret_cast<u128*>(local_dst + (i << 4)) = v[u];
       }
     }
   }
   for (uint64_t o = (nvec << 4) + threadIdx.x; o < nbytes; o += NTHREADS) {
     const uint8_t b = *reinterpret_cast<const volatile uint8_t*>(src + o);
-    for (int d = 1; d < n; ++d) *reinterpret_cast<volatile uint8_t*>(P.out[(c.rank + d) % n] + lo + o) = b;
+    for (int d = 1; d < n; ++d) {
+      const int p = (c.rank + d) % n;
+      if (p != skip_rank) *reinterpret_cast<volatile uint8_t*>(P.out[p] + lo + o) = b;
+    }
     if (!skip_local) local_dst[o] = b;
   }
 }
@@ -639,12 +645,23 @@ __device__ void direct_body(const MtDevComm& c, const DirectArgs& a, int lr, int
       if constexpr (kSame) {
         const MtRange r = mt_split(B, ncta, cta, kSplitAlignDirect);
         if (a.variant == 2 || a.variant == 4) {
-          // pull + replicate: rank j fetches sub-slice j straight from the root's buffer and replicates it
-          // to everybody (one multimem.st per vector, or plain stores to every peer).  The root's link only
-          // carries each byte once, the replication is spread over all ranks (a single source of multicast
-          // stores tops out near 400 GB/s), and there is no phase in which only the root's link is busy.
+          // pull + replicate: a rank fetches one sub-slice straight from the root's buffer and replicates it
+          // (one multimem.st per vector, or plain / bulk stores to every peer).  The root's link carries each
+          // byte once, the replication is spread over the ranks (a single source of multicast stores tops out
+          // near 400 GB/s), and there is no phase in which only the root's link is busy.  With multicast
+          // stores all n ranks take a sub-slice (the root's copy leaves its link once).  With plain stores
+          // only the n - 1 other ranks do: a root that also replicated a sub-slice to n - 1 peers would put
+          // 2 (n - 1) / n message sizes on its outgoing link, where every other link carries one.
           const uint64_t len = r.hi - r.lo;
-          const MtRange sm = mt_split(len, n, me, 16);
+          const bool others_only = !a.nvls && n > 2;
+          const int nsl = others_only ? n - 1 : n;
+          const int idx = others_only ? mt_mod(me - a.root - 1, n) : me;   // the root: n - 1, no sub-slice
+          const int skip_rank = others_only ? a.root : -1;
+          if (others_only && me == a.root) {
+            if (in != out && len) copy_range<NTHREADS, false, false>(in + r.lo, out + r.lo, len);
+            break;
+          }
+          const MtRange sm = mt_split(len, nsl, idx, 16);
           if (sm.hi > sm.lo) {
             const uint8_t* src = (me == a.root ? in : P.in[a.root]) + r.lo + sm.lo;
             const uint64_t nb = sm.hi - sm.lo;
@@ -653,10 +670,10 @@ __device__ void direct_body(const MtDevComm& c, const DirectArgs& a, int lr, int
               else nvls_bcast_range<NTHREADS, true>(src, c.mc + a.mc_out_off + r.lo + sm.lo, nb >> 4);
             } else {
               bool done = false;
+              const bool skip_self = me == a.root && in == out;
               if (a.variant == 4) {
                 // copy engine: the sub-slice crosses the root's link once (a bulk load from the root's memory)
                 // and is stored to every rank from shared memory
-                const bool skip_self = me == a.root && in == out;
                 if (threadIdx.x == 0) {
                   BulkJob& J = ctl->jobs[0];
                   J.src = src;
@@ -664,7 +681,7 @@ __device__ void direct_body(const MtDevComm& c, const DirectArgs& a, int lr, int
                   J.ndst = 0;
                   for (int d = 1; d <= n; ++d) {
                     const int p = (me + d) % n;
-                    if (p == me && skip_self) continue;
+                    if ((p == me && skip_self) || p == skip_rank) continue;
                     J.dst[J.ndst++] = P.out[p] + r.lo + sm.lo;
                   }
                   ctl->njobs = 1;
@@ -677,9 +694,9 @@ __device__ void direct_body(const MtDevComm& c, const DirectArgs& a, int lr, int
                 __syncthreads();
                 done = ctl->abort != 2;
                 if (done && ctl->abort == 0 && (nb & 15))
-                  bcast_fanout<NTHREADS>(c, src + (nb & ~15ull), P, r.lo + sm.lo + (nb & ~15ull), nb & 15, skip_self);
+                  bcast_fanout<NTHREADS>(c, src + (nb & ~15ull), P, r.lo + sm.lo + (nb & ~15ull), nb & 15, skip_self, skip_rank);
               }
-              if (!done) bcast_fanout<NTHREADS>(c, src, P, r.lo + sm.lo, nb, me == a.root && in == out);
+              if (!done) bcast_fanout<NTHREADS>(c, src, P, r.lo + sm.lo, nb, skip_self, skip_rank);
             }
           }
           break;

@@ -855,6 +855,31 @@ class Communicator:
             self._launch_ring(N.OP_REDUCESCATTER, ins, outs, B, dt, self._pick_proto(B * (n - 1), proto),
                               spatial=mode == "spatial", nch=nch)
 
+    def _auto_rooted(self, coll: str, nbytes: int, symm: bool, peer_ok: bool, separate: bool) -> str:
+        """Automatic algorithm of broadcast and reduce.
+
+        The chain over the FIFOs has no entry or exit barrier, so consecutive calls overlap: called back to back it
+        measures fastest at most sizes (8 GPUs, 64 MiB broadcast: 511 GB/s against 424 for the multicast variant).
+        A single call between other work pays the fill of the chain instead: the message crosses ``n - 1`` links
+        one after the other, a FIFO step at a time.  On 8 GPUs a step of five collectives at 64 MiB took 1.42 ms
+        with chain broadcast and reduce against 0.70 ms with the one-hop kernels, although each chain measured
+        faster alone.  So the chain serves what it is good at: small messages (LL128: a few microseconds per
+        link, no barriers), two ranks (one link, nothing to fill) and buffers the peers cannot address.  Larger
+        messages take a kernel in which every byte crosses the switch at most twice."""
+        n = self.world_size
+        if n == 2:
+            # two ranks: the chain is a single link; above 64 MiB the plain one-hop copy / sum measured faster
+            if nbytes >= (128 << 20) and peer_ok and separate:
+                return "pull" if coll == "broadcast" else "direct"
+            return "ring"
+        if nbytes <= self.cfg.ll128_max_bytes or not separate:
+            return "ring"
+        if self.nvls and symm:
+            return "nvls"
+        if peer_ok:
+            return "bulk" if coll == "broadcast" and nbytes >= (8 << 20) else "direct"
+        return "ring"
+
     def broadcast(self, buff: TensorOrList, root: int = 0, algo: Optional[str] = None, proto: Optional[str] = None,
                   nch: Optional[int] = None) -> None:
         """Copy ``buff`` of ``root`` into ``buff`` of every rank (4_broadcast.py:79-101)."""
@@ -878,14 +903,7 @@ class Communicator:
         algo, nch = self._tuned("broadcast", nbytes, algo, nch, symm, ts)
         algo = self._algo(algo, "broadcast")
         if algo == "auto":
-            # The pipelined chain over the FIFOs (LL128 for small messages, Simple with sub-slot steps for large
-            # ones) has no entry and exit barrier and keeps every link busy once it is full: measured fastest at
-            # every size on 4 and 8 GPUs (8 GPUs, 64 MiB: 511 GB/s against 423 for the multicast variant) and up to
-            # 64 MiB on two.  Two ranks have nothing to pipeline for large messages: the receiver pulls.
-            if self.world_size == 2 and nbytes >= (128 << 20) and self._peer_ok(ts):
-                algo = "pull"
-            else:
-                algo = "ring"
+            algo = self._auto_rooted("broadcast", nbytes, symm, self._peer_ok(ts), True)
         if algo in ("direct", "nvls", "pull", "push", "nvls1", "bulk"):
             if algo in ("nvls", "nvls1") and not (self.nvls and symm):
                 raise ValueError(f"algo={algo} needs the multicast mapping and a symmetric buffer")
@@ -933,12 +951,10 @@ class Communicator:
         if self.world_size == 1:
             algo = "ring" if not cast else "direct1"
         if algo == "auto":
-            # the pipelined chain wins on 4 and 8 GPUs at every size and up to 64 MiB on two (see broadcast); a
-            # result in another element type needs the one-hop kernel
-            if cast or (self.world_size == 2 and nbytes >= (128 << 20)):
+            if cast:   # a result in another element type needs the one-hop kernel
                 algo = "direct" if separate and self._peer_ok(ins) else "ring"
             else:
-                algo = "ring"
+                algo = self._auto_rooted("reduce", nbytes, symm, self._peer_ok(ins), separate)
         if cast and algo not in ("direct", "direct1"):
             raise ValueError(f"reduce into another element type runs on the one-hop paths (direct, direct1), not {algo}")
         if algo in ("direct", "nvls", "direct1", "nvls1"):

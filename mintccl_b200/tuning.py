@@ -82,6 +82,11 @@ class TuningTable:
         for r in rows:
             if r.get("impl") != impl:
                 continue
+            # Broadcast and reduce on more than two ranks are tuned from fenced measurements only (sweep.py --sync):
+            # consecutive calls of the barrier-free chain overlap one another, so a back-to-back block rates the
+            # chain by its steady state and hides the fill that a single call between other work pays in full.
+            if r["collective"] in ("broadcast", "reduce") and int(r["n"]) > 2 and not r.get("sync"):
+                continue
             sym = symmetric if symmetric is not None else (str(r.get("memory", "heap")) == "heap")
             cands.setdefault((r["collective"], int(r["n"]), sym, int(r["bytes"])), []).append(r)
         groups: Dict[Tuple[str, int, bool], List[Tuple[int, Tuple[str, int]]]] = {}

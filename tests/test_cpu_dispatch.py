@@ -117,7 +117,14 @@ def test_allgather_reducescatter_dispatch():
 def test_broadcast_and_reduce_dispatch():
     c = Recorder(world=8)
     x, out = c.sym(1 << 20), c.sym(1 << 20)
-    c.broadcast(x, root=3)                                                       # automatic: the pipelined chain
+    c.broadcast(x, root=3)                                  # automatic, 2 MiB on 8 ranks: one hop through the switch
+    l = c.last()
+    assert l["fn"] == "mt_direct" and l["op"] == N.DOP_BROADCAST and l["nvls"] == 1 and l["variant"] == 2 and l["root"] == 3
+    small = c.sym(1 << 17)
+    c.broadcast(small, root=3)                              # 256 KiB: the LL128 chain (no barriers, short fill)
+    l = c.last()
+    assert l["fn"] == "mt_ring" and l["op"] == N.OP_BROADCAST and l["proto"] == N.PROTO_LL128 and l["root"] == 3
+    c.broadcast(x, root=3, algo="ring")
     l = c.last()
     assert l["fn"] == "mt_ring" and l["op"] == N.OP_BROADCAST and l["proto"] == N.PROTO_SIMPLE and l["root"] == 3
     c.broadcast(x, root=3, algo="nvls")
@@ -125,7 +132,15 @@ def test_broadcast_and_reduce_dispatch():
     assert l["fn"] == "mt_direct" and l["op"] == N.DOP_BROADCAST and l["nvls"] == 1 and l["variant"] == 2 and l["root"] == 3
     c.broadcast(torch.zeros(100, dtype=torch.float16), root=1)
     assert c.last()["fn"] == "mt_ring" and c.last()["proto"] == N.PROTO_LL128    # small, ordinary memory: LL128 chain
+    ordinary = torch.zeros(8 << 20, dtype=torch.float16)    # 16 MiB the peers cannot address (not shared): the chain
+    c.broadcast(ordinary, root=1)
+    assert c.last()["fn"] == "mt_ring" and c.last()["proto"] == N.PROTO_SIMPLE
     c.reduce(x, root=2, out=out)
+    l = c.last()
+    assert l["fn"] == "mt_direct" and l["op"] == N.DOP_REDUCE and l["nvls"] == 1 and l["variant"] == 2
+    c.reduce(small, root=2, out=c.sym(1 << 17))
+    assert c.last()["fn"] == "mt_ring" and c.last()["op"] == N.OP_REDUCE
+    c.reduce(ordinary, root=2, out=torch.zeros(8 << 20, dtype=torch.float16))
     assert c.last()["fn"] == "mt_ring" and c.last()["op"] == N.OP_REDUCE
     c.reduce(x, root=2, out=out, algo="nvls")
     l = c.last()
@@ -202,7 +217,8 @@ def test_tuning_table_overrides_the_policy_only_where_it_applies(tmp_path, monke
     assert TuningTable.from_env() is None                 # switched off: the built-in policy alone
     monkeypatch.delenv("MINTCCL_TUNING_FILE")
     shipped = TuningTable.from_env()                      # unset: the table measured on HGX B200 that ships with the package
-    assert shipped is not None and shipped.lookup("broadcast", 8, 64 << 20, True) == ("ring", None)
+    assert shipped is not None and shipped.lookup("allgather", 8, 64 << 20, True)[0] == "bulk"
+    assert shipped.lookup("broadcast", 8, 64 << 20, True) is None   # rooted collectives: tuned from fenced rows only
     assert shipped.lookup("allreduce", 3, 1 << 20, True) is None    # no rows for rank counts that were not measured
 
 
@@ -223,6 +239,15 @@ def test_tuning_table_from_sweep_rows():
     assert t.lookup("allreduce", 8, 1 << 29) is None and t.lookup("allreduce", 4, 1 << 20) is None
     # boundaries sit between the measured sizes (geometric mean)
     assert got[0]["max_bytes"] == int((float(1 << 14) * (1 << 20)) ** 0.5)
+    # broadcast / reduce on more than two ranks: back-to-back rows rate the barrier-free chain by its steady state, so
+    # only fenced rows count
+    chain = [{"collective": "broadcast", "bytes": 1 << 26, "impl": "mintccl", "algo": a_, "ctas": 0, "us": us, "n": 8,
+              "sync": sync} for a_, us, sync in (("ring", 10.0, False), ("nvls", 20.0, False), ("auto", 20.0, False))]
+    assert ("broadcast", 8, True) not in TuningTable.from_sweep(chain).rows
+    fenced = [dict(r, sync=True, us={"ring": 60.0, "nvls": 20.0, "auto": 60.0}[r["algo"]]) for r in chain]
+    assert TuningTable.from_sweep(chain + fenced).lookup("broadcast", 8, 1 << 26) == ("nvls", None)
+    two = [dict(r, n=2) for r in chain]
+    assert TuningTable.from_sweep(two).lookup("broadcast", 2, 1 << 26) == ("ring", None)   # one link: nothing to fill
 
 
 def test_emulated_world_takes_one_tensor_per_rank():
@@ -319,12 +344,23 @@ def test_ordinary_tensors_take_the_one_hop_kernels_once_shared():
     assert l["variant"] == 1 and l["pub_in"][3] == buf.data_ptr() + 3 * 4096 * 4 and l["pub_out"] == [0] * 8
     c.reducescatter(buf, out=torch.zeros(4096, dtype=torch.float32))
     assert c.last()["fn"] == "mt_direct" and c.last()["pub_out"] == [0] * 8    # the shard stays local: not shared
+    large = torch.zeros(8 << 20, dtype=torch.float16)              # automatic, 16 MiB: the copy engine, no multicast
+    c.broadcast(large, root=1)
+    l = c.last()
+    assert l["fn"] == "mt_direct" and l["op"] == N.DOP_BROADCAST and l["nvls"] == 0 and l["variant"] == 4
+    c.broadcast(torch.zeros(1 << 20, dtype=torch.float16), root=1)  # 2 MiB: register-staged pull + replicate
+    assert c.last()["fn"] == "mt_direct" and c.last()["nvls"] == 0 and c.last()["variant"] == 2
+    c.reduce(large, root=2, out=torch.zeros(8 << 20, dtype=torch.float16))     # the others sum a slice each
+    l = c.last()
+    assert l["fn"] == "mt_direct" and l["op"] == N.DOP_REDUCE and l["nvls"] == 0 and l["variant"] == 3
+    c.reduce(large, root=2)                                        # in place: the chain
+    assert c.last()["fn"] == "mt_ring"
     big = torch.zeros(1 << 20, dtype=torch.float16)
     c.broadcast(big, root=2, algo="direct")
     assert c.last()["fn"] == "mt_direct" and c.last()["variant"] == 2 and c.last()["nvls"] == 0
     c.reduce(big, root=2, out=torch.zeros(1 << 20, dtype=torch.float16), algo="direct")
     assert c.last()["fn"] == "mt_direct" and c.last()["variant"] == 3           # the other ranks sum, the root receives
-    c.broadcast(big, root=2)                                       # automatic: the pipelined chain, any memory
+    c.broadcast(big[: 1 << 17], root=2)                            # 256 KiB: the LL128 chain, any memory
     assert c.last()["fn"] == "mt_ring"
     with pytest.raises(ValueError):
         c.allreduce(x, algo="nvls")                                # the multicast alias covers the heap only

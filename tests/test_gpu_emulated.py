@@ -259,13 +259,13 @@ def test_direct_collectives(n, numel):
         # broadcast and reduce
         for r in range(n):
             gb[r].view(-1).copy_(full[r])
-        for algo in ("direct", "push", "pull"):
+        for algo, root in (("direct", n - 1), ("direct", 1 % n), ("push", n - 1), ("pull", n - 1), (None, 0)):
             for r in range(n):
                 gb[r].view(-1).copy_(full[r])
-            w.broadcast(gb, root=n - 1, algo=algo)
+            w.broadcast(gb, root=root, algo=algo)
             w.check()
             for r in range(n):
-                assert torch.equal(gb[r].view(-1), full[n - 1]), algo
+                assert torch.equal(gb[r].view(-1), full[root]), (algo, root)
         for r in range(n):
             gb[r].view(-1).copy_(full[r])
         routs = [torch.zeros(n, numel, device="cuda", dtype=dtype) for _ in range(n)]
@@ -457,7 +457,7 @@ def test_copy_engine_variants(n, numel):
         for r in range(n):
             for p in range(n):
                 assert torch.equal(outs[r][p], ins[p][r])
-        for root in (0, n - 1):
+        for root in sorted({0, 1, n - 1}):
             bs = [torch.zeros(numel + off, device="cuda", dtype=dtype)[off:] for _ in range(n)]
             for b, s_ in zip(bs, src):
                 b.copy_(s_)
