@@ -661,7 +661,9 @@ __device__ void direct_body(const MtDevComm& c, const DirectArgs& a, int lr, int
             if (in != out && len) copy_range<NTHREADS, false, false>(in + r.lo, out + r.lo, len);
             break;
           }
-          const MtRange sm = mt_split(len, nsl, idx, 16);
+          // n - 1 sub-slices do not fall on 128-byte lines by themselves (n sub-slices of a 128-aligned range do
+          // for a power-of-two n): ask for it, so that warps and bulk copies move whole lines
+          const MtRange sm = mt_split(len, nsl, idx, others_only ? 128 : 16);
           if (sm.hi > sm.lo) {
             const uint8_t* src = (me == a.root ? in : P.in[a.root]) + r.lo + sm.lo;
             const uint64_t nb = sm.hi - sm.lo;
@@ -750,7 +752,7 @@ __device__ void direct_body(const MtDevComm& c, const DirectArgs& a, int lr, int
         // one message size, where "root sums everything" puts (n - 1) messages on the root's link.
         if (me != a.root) {
           const int idx = mt_mod(me - a.root - 1, n);
-          const MtRange sm = mt_split(r.hi - r.lo, n - 1, idx, 16);
+          const MtRange sm = mt_split(r.hi - r.lo, n - 1, idx, 128);   // whole 128-byte lines per warp
           if (sm.hi > sm.lo)
             pull_reduce_range<TI, TO, NTHREADS, false, false>(c, P, P.out[a.root], r.lo + sm.lo, r.lo + sm.hi, 0);
         }
