@@ -52,10 +52,12 @@ struct RingArgs {
 
 // Step size of chain operations (send/recv over a route, broadcast, reduce).  The last of L ranks sees its first
 // byte after L - 2 extra steps, so smaller steps shorten the fill of the chain; but every step costs a flag round
-// (block barrier, release store, the peer's poll), and that cost won on 8 B200: cutting a channel's share into eight
-// steps took the 64 MiB broadcast from 511 to 373 GB/s (8 - 128 MiB all slower, 256 - 512 MiB 4 % faster).  So the
-// default is whole slots; MINTCCL_CHAIN_STEP_BYTES sets a smaller step (rounded down to a multiple of 128, at least
-// 4 KiB; 0 or unset: whole slots).
+// (block barrier, release store, the peer's poll).  On 8 B200, in blocks of back-to-back calls (which overlap one
+// another, so the fill hardly counts), cutting a channel's share into eight steps took the 64 MiB broadcast from
+// 511 to 373 GB/s; in a step that mixes five collectives (each chain call pays its fill) the same cut took the
+// step from 1.42 to 0.95 ms.  The default is whole slots, and the automatic choice keeps large broadcasts and
+// reductions off the chain; MINTCCL_CHAIN_STEP_BYTES sets a smaller step (rounded down to a multiple of 128, at
+// least 4 KiB; 0 or unset: whole slots).
 static inline uint32_t mt_chain_step_from_env() {
   const char* e = getenv("MINTCCL_CHAIN_STEP_BYTES");
   if (!e) return 0;
