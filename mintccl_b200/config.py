@@ -16,7 +16,7 @@ the routes (default: uniform, which is exact on an NVSwitch node); ``MINTCCL_RIN
 Read by the native library itself, at every call (tuning switches, not part of :class:`Config`):
 ``MINTCCL_GEMM_PAIR`` (0: single-CTA GEMM kernels instead of CTA pairs), ``MINTCCL_GEMM_RASTER`` (row blocks per
 group of the plain GEMM's tile order), ``MINTCCL_CHAIN_STEP_BYTES`` (bytes per FIFO step of chain operations over
-the Simple protocol; default and 0: whole slots, measured fastest on 8 GPUs), ``MINTCCL_NO_LOCAL_COPY`` (one-rank communicators use the ring kernel).
+the Simple protocol; default: half a channel's share, 64 - 256 KiB, which serves a single call; 0: whole slots, the best for streams of identical calls), ``MINTCCL_NO_LOCAL_COPY`` (one-rank communicators use the ring kernel).
 """
 from __future__ import annotations
 

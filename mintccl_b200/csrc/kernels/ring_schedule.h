@@ -50,22 +50,30 @@ struct RingArgs {
                                   // (0: whole slots); a multiple of 128
 };
 
-// Step size of chain operations (send/recv over a route, broadcast, reduce).  The last of L ranks sees its first
-// byte after L - 2 extra steps, so smaller steps shorten the fill of the chain; but every step costs a flag round
-// (block barrier, release store, the peer's poll).  On 8 B200, in blocks of back-to-back calls (which overlap one
-// another, so the fill hardly counts), cutting a channel's share into eight steps took the 64 MiB broadcast from
-// 511 to 373 GB/s; in a step that mixes five collectives (each chain call pays its fill) the same cut took the
-// step from 1.42 to 0.95 ms.  The default is whole slots, and the automatic choice keeps large broadcasts and
-// reductions off the chain; MINTCCL_CHAIN_STEP_BYTES sets a smaller step (rounded down to a multiple of 128, at
-// least 4 KiB; 0 or unset: whole slots).
-static inline uint32_t mt_chain_step_from_env() {
+// Step size of chain operations (send/recv over a route, broadcast, reduce) over the Simple protocol.  The last of L
+// ranks sees its first byte after L - 2 extra steps, so smaller steps shorten the fill of the chain; but every step
+// costs a flag round (block barrier, release store, the peer's poll).  Which side wins depends on how the calls
+// follow one another.  Blocks of back-to-back calls overlap one another, so the fill hardly counts: there, on 8 B200,
+// cutting a channel's share into eight steps took the 64 MiB broadcast from 511 to 373 GB/s.  A call that other work
+// surrounds pays the fill in full: fenced calls on 4 B200 took 292 us with whole 1 MiB slots and 190 us with 256 KiB
+// steps at 64 MiB (624 -> 551 us at 256 MiB, 99 -> 87 us at 16 MiB with 128 KiB steps), and a step of five mixed
+// collectives on 8 B200 went from 1.42 to 0.95 ms.  The default serves the single call: half a channel's share per
+// step, at least 64 KiB and at most 256 KiB.  MINTCCL_CHAIN_STEP_BYTES overrides it (rounded down to a multiple of
+// 128, at least 4 KiB; 0: whole slots, the best for streams of identical calls).
+static inline uint32_t mt_chain_step_bytes(uint64_t bytes_per_channel, uint64_t slot_bytes) {
   const char* e = getenv("MINTCCL_CHAIN_STEP_BYTES");
-  if (!e) return 0;
-  long long v = atoll(e);
-  if (v <= 0) return 0;
-  if (v < 4096) v = 4096;
-  if (v > (1ll << 30)) v = 1ll << 30;
-  return (uint32_t)(v & ~127ll);
+  if (e) {
+    long long v = atoll(e);
+    if (v <= 0) return 0;
+    if (v < 4096) v = 4096;
+    if (v > (1ll << 30)) v = 1ll << 30;
+    return (uint32_t)(v & ~127ll);
+  }
+  uint64_t step = bytes_per_channel / 2;
+  if (step < (64u << 10)) step = 64u << 10;
+  if (step > (256u << 10)) step = 256u << 10;
+  if (step >= slot_bytes) return 0;
+  return (uint32_t)(step & ~127ull);
 }
 
 enum Role : int {

@@ -840,7 +840,9 @@ class Communicator:
         if n == 1:
             algo = "ring" if not cast else "direct"
         if algo == "auto":
-            if symm and not cast and self._want_nvls(B, ins + outs):
+            # in-switch sums up to 32 MiB in total; above, pulling the shard from every peer measured faster on 4 GPUs
+            # (128 MiB: 535 GB/s against 446) as on 8 (where the tuning table says the same)
+            if symm and not cast and B * n <= (32 << 20) and self._want_nvls(B, ins + outs):
                 algo = "nvls"
             else:
                 algo = "direct" if self._peer_ok(ins) else "ring"
@@ -874,11 +876,14 @@ class Communicator:
             return "ring"
         if nbytes <= self.cfg.ll128_max_bytes or not separate:
             return "ring"
+        if coll == "broadcast" and nbytes >= (8 << 20) and peer_ok:
+            # pull + replicate over the n - 1 other ranks with plain loads and stores: every link carries one message
+            # size.  4 GPUs, one call at a time: 588 GB/s at 64 MiB and 678 at 256 MiB, against 445 / 502 for the
+            # multicast variant (one source of multicast stores per sub-slice) and 478 / 646 for the copy engine.
+            return "direct"
         if self.nvls and symm:
             return "nvls"
-        if peer_ok:
-            return "bulk" if coll == "broadcast" and nbytes >= (8 << 20) else "direct"
-        return "ring"
+        return "direct" if peer_ok else "ring"
 
     def broadcast(self, buff: TensorOrList, root: int = 0, algo: Optional[str] = None, proto: Optional[str] = None,
                   nch: Optional[int] = None) -> None:

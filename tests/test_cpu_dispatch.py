@@ -344,10 +344,13 @@ def test_ordinary_tensors_take_the_one_hop_kernels_once_shared():
     assert l["variant"] == 1 and l["pub_in"][3] == buf.data_ptr() + 3 * 4096 * 4 and l["pub_out"] == [0] * 8
     c.reducescatter(buf, out=torch.zeros(4096, dtype=torch.float32))
     assert c.last()["fn"] == "mt_direct" and c.last()["pub_out"] == [0] * 8    # the shard stays local: not shared
-    large = torch.zeros(8 << 20, dtype=torch.float16)              # automatic, 16 MiB: the copy engine, no multicast
+    large = torch.zeros(8 << 20, dtype=torch.float16)              # automatic, 16 MiB: pull + replicate, plain stores
     c.broadcast(large, root=1)
     l = c.last()
-    assert l["fn"] == "mt_direct" and l["op"] == N.DOP_BROADCAST and l["nvls"] == 0 and l["variant"] == 4
+    assert l["fn"] == "mt_direct" and l["op"] == N.DOP_BROADCAST and l["nvls"] == 0 and l["variant"] == 2
+    hl = c.sym(8 << 20)                                            # the same on the heap: no multicast from 8 MiB on
+    c.broadcast(hl, root=1)
+    assert c.last()["fn"] == "mt_direct" and c.last()["nvls"] == 0 and c.last()["variant"] == 2
     c.broadcast(torch.zeros(1 << 20, dtype=torch.float16), root=1)  # 2 MiB: register-staged pull + replicate
     assert c.last()["fn"] == "mt_direct" and c.last()["nvls"] == 0 and c.last()["variant"] == 2
     c.reduce(large, root=2, out=torch.zeros(8 << 20, dtype=torch.float16))     # the others sum a slice each
