@@ -572,7 +572,8 @@ int mt_ring(MtComm* c, void* stream, int proto, int dtype, int op, const void* c
   a.elem_size = mt::dtype_size(dtype);
   if (nbytes % a.elem_size) return fail("byte count is not a multiple of the element size");
   if (proto == MT_PROTO_SIMPLE && (op == mt::OP_SENDRECV || op == mt::OP_BROADCAST || op == mt::OP_REDUCE))
-    a.step_bytes = mt::mt_chain_step_bytes(nbytes / (uint64_t)nchannels, c->L.fifo_slot_bytes[MT_PROTO_SIMPLE]);
+    a.step_bytes = mt::mt_chain_step_bytes(nbytes / (uint64_t)nchannels, c->L.fifo_slot_bytes[MT_PROTO_SIMPLE],
+                                           op == mt::OP_SENDRECV ? chain_len : c->nranks);
   cudaError_t e = proto == MT_PROTO_LL128
                       ? mt::launch_ring_ll128(dtype, c->d_comms, a, nchannels, c->nlocal, (cudaStream_t)stream)
                       : mt::launch_ring_simple(dtype, c->d_comms, a, nchannels, c->nlocal, (cudaStream_t)stream);

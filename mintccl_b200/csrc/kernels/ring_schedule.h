@@ -57,10 +57,10 @@ struct RingArgs {
 // cutting a channel's share into eight steps took the 64 MiB broadcast from 511 to 373 GB/s.  A call that other work
 // surrounds pays the fill in full: fenced calls on 4 B200 took 292 us with whole 1 MiB slots and 190 us with 256 KiB
 // steps at 64 MiB (624 -> 551 us at 256 MiB, 99 -> 87 us at 16 MiB with 128 KiB steps), and a step of five mixed
-// collectives on 8 B200 went from 1.42 to 0.95 ms.  The default serves the single call: half a channel's share per
-// step, at least 64 KiB and at most 256 KiB.  MINTCCL_CHAIN_STEP_BYTES overrides it (rounded down to a multiple of
+// collectives on 8 B200 went from 1.42 to 0.95 ms.  The default serves the single call: on a chain of more than two
+// ranks half a channel's share per step, at least 64 KiB and at most 256 KiB.  MINTCCL_CHAIN_STEP_BYTES overrides it (rounded down to a multiple of
 // 128, at least 4 KiB; 0: whole slots, the best for streams of identical calls).
-static inline uint32_t mt_chain_step_bytes(uint64_t bytes_per_channel, uint64_t slot_bytes) {
+static inline uint32_t mt_chain_step_bytes(uint64_t bytes_per_channel, uint64_t slot_bytes, int chain_len) {
   const char* e = getenv("MINTCCL_CHAIN_STEP_BYTES");
   if (e) {
     long long v = atoll(e);
@@ -69,6 +69,7 @@ static inline uint32_t mt_chain_step_bytes(uint64_t bytes_per_channel, uint64_t 
     if (v > (1ll << 30)) v = 1ll << 30;
     return (uint32_t)(v & ~127ll);
   }
+  if (chain_len <= 2) return 0;   // one link: nothing to fill, whole slots cost the fewest flag rounds
   uint64_t step = bytes_per_channel / 2;
   if (step < (64u << 10)) step = 64u << 10;
   if (step > (256u << 10)) step = 256u << 10;

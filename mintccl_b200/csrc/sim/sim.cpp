@@ -313,7 +313,7 @@ int mt_sim_run(int nranks, int nchannels, int proto, int op, uint64_t count, int
     a.op = op;
     a.root = root;
     if (proto == MT_PROTO_SIMPLE && (op == OP_SENDRECV || op == OP_BROADCAST || op == OP_REDUCE))
-      a.step_bytes = mt_chain_step_bytes(a.nbytes / (uint64_t)nchannels, slot_bytes);  // the same rule as mt_ring
+      a.step_bytes = mt_chain_step_bytes(a.nbytes / (uint64_t)nchannels, slot_bytes, op == OP_SENDRECV ? chain_len : nranks);  // the same rule as mt_ring
     a.spatial = spatial;
     a.chain_len = chain_len;
     for (int i = 0; i < chain_len; ++i) a.chain[i] = chain[i];
