@@ -874,12 +874,15 @@ class Communicator:
             if nbytes >= (128 << 20) and peer_ok and separate:
                 return "pull" if coll == "broadcast" else "direct"
             return "ring"
-        if nbytes <= self.cfg.ll128_max_bytes or not separate:
+        # one call at a time on 8 GPUs, 256 KiB: broadcast 22.6 us on the LL128 chain as through the switch; reduce 42 us
+        # on the chain (every hop adds its own input) against 21.6 us in the switch
+        small = (256 << 10) if coll == "broadcast" else (64 << 10)
+        if nbytes <= min(small, self.cfg.ll128_max_bytes) or not separate:
             return "ring"
         if coll == "broadcast" and nbytes >= (8 << 20) and peer_ok:
             # pull + replicate over the n - 1 other ranks with plain loads and stores: every link carries one message
-            # size.  4 GPUs, one call at a time: 588 GB/s at 64 MiB and 678 at 256 MiB, against 445 / 502 for the
-            # multicast variant (one source of multicast stores per sub-slice) and 478 / 646 for the copy engine.
+            # size.  One call at a time: 588 GB/s at 64 MiB and 678 at 256 MiB on 4 GPUs (544 / 655 on 8), against
+            # 445 / 502 (425 / 487) for the multicast variant and 478 / 646 (440 / 552) for the copy engine.
             return "direct"
         if self.nvls and symm:
             return "nvls"

@@ -31,6 +31,8 @@ class TuningTable:
             row = {"collective": str(r["collective"]), "nranks": int(r["nranks"]), "max_bytes": int(r["max_bytes"]),
                    "symmetric": bool(r.get("symmetric", True)), "algo": str(r["algo"]),
                    "nch": None if r.get("nch") in (None, 0) else int(r["nch"])}
+            if r.get("min_bytes"):
+                row["min_bytes"] = int(r["min_bytes"])
             self.rows.setdefault((row["collective"], row["nranks"], row["symmetric"]), []).append(row)
         for v in self.rows.values():
             v.sort(key=lambda x: x["max_bytes"])
@@ -38,9 +40,11 @@ class TuningTable:
     # ---------------------------------------------------------------------------------------------- use
     def lookup(self, collective: str, nranks: int, nbytes: int, symmetric: bool = True) -> Optional[Tuple[str, Optional[int]]]:
         """(algo, nch) of the first row whose ``max_bytes`` covers ``nbytes``; None where the table is silent (the
-        built-in policy then decides), including beyond the largest measured size."""
+        built-in policy then decides), including beyond the largest and below the smallest measured size."""
         for row in self.rows.get((collective, nranks, symmetric), ()):
             if nbytes <= row["max_bytes"]:
+                if nbytes < row.get("min_bytes", 0):
+                    return None     # below the smallest size that was measured
                 return row["algo"], row["nch"]
         return None
 
@@ -77,7 +81,7 @@ class TuningTable:
         written where a named algorithm beat it by more than ``margin`` (timing noise must not flip choices), and
         says ``auto`` where nothing did, so that the built-in policy keeps deciding there.  Neighbouring sizes with
         the same choice merge into one row, and a row reaches up to the geometric mean of its last size and the next
-        measured one.  ``symmetric``: None = from each row's ``memory`` field (heap / ordinary)."""
+        measured one; the first row of a group starts at the smallest measured size (``min_bytes``) when that is not small.  ``symmetric``: None = from each row's ``memory`` field (heap / ordinary)."""
         cands: Dict[Tuple[str, int, bool, int], List[dict]] = {}
         for r in rows:
             if r.get("impl") != impl:
@@ -125,6 +129,8 @@ class TuningTable:
                 else:
                     out.append({"collective": coll, "nranks": n, "max_bytes": upto, "symmetric": sym,
                                 "algo": choice[0], "nch": choice[1] or None})
+                    if i == 0 and nbytes > 4096:
+                        out[-1]["min_bytes"] = nbytes    # a sweep that starts at a large size says nothing below it
         return cls(out)
 
 

@@ -138,8 +138,11 @@ def test_broadcast_and_reduce_dispatch():
     c.reduce(x, root=2, out=out)
     l = c.last()
     assert l["fn"] == "mt_direct" and l["op"] == N.DOP_REDUCE and l["nvls"] == 1 and l["variant"] == 2
-    c.reduce(small, root=2, out=c.sym(1 << 17))
-    assert c.last()["fn"] == "mt_ring" and c.last()["op"] == N.OP_REDUCE
+    c.reduce(small, root=2, out=c.sym(1 << 17))             # 256 KiB: a chain hop adds its own input, the switch is faster
+    assert c.last()["fn"] == "mt_direct" and c.last()["nvls"] == 1
+    tiny = c.sym(1 << 14)
+    c.reduce(tiny, root=2, out=c.sym(1 << 14))              # 32 KiB: the LL128 chain
+    assert c.last()["fn"] == "mt_ring" and c.last()["op"] == N.OP_REDUCE and c.last()["proto"] == N.PROTO_LL128
     c.reduce(ordinary, root=2, out=torch.zeros(8 << 20, dtype=torch.float16))
     assert c.last()["fn"] == "mt_ring" and c.last()["op"] == N.OP_REDUCE
     c.reduce(x, root=2, out=out, algo="nvls")
@@ -222,7 +225,7 @@ def test_tuning_table_overrides_the_policy_only_where_it_applies(tmp_path, monke
     assert shipped.lookup("allreduce", 3, 1 << 20, True) is None    # no rows for rank counts that were not measured
 
 
-def test_tuning_table_from_sweep_rows():
+def test_tuning_table_from_sweep_rows(tmp_path):
     from mintccl_b200.tuning import TuningTable
     rows = []
     for nbytes, best in ((1 << 10, ("ll", 0)), (1 << 14, ("ll", 0)), (1 << 20, ("direct", 64)), (1 << 24, ("nvls", 32)), (1 << 28, ("nvls", 32))):
@@ -245,7 +248,12 @@ def test_tuning_table_from_sweep_rows():
               "sync": sync} for a_, us, sync in (("ring", 10.0, False), ("nvls", 20.0, False), ("auto", 20.0, False))]
     assert ("broadcast", 8, True) not in TuningTable.from_sweep(chain).rows
     fenced = [dict(r, sync=True, us={"ring": 60.0, "nvls": 20.0, "auto": 60.0}[r["algo"]]) for r in chain]
-    assert TuningTable.from_sweep(chain + fenced).lookup("broadcast", 8, 1 << 26) == ("nvls", None)
+    t2 = TuningTable.from_sweep(chain + fenced)
+    assert t2.lookup("broadcast", 8, 1 << 26) == ("nvls", None)
+    assert t2.lookup("broadcast", 8, 1 << 20) is None       # a sweep says nothing below its smallest size
+    path2 = str(tmp_path / "t2.json")
+    t2.dump(path2)
+    assert TuningTable.load(path2).lookup("broadcast", 8, 1 << 20) is None and TuningTable.load(path2).lookup("broadcast", 8, 1 << 26)
     two = [dict(r, n=2) for r in chain]
     assert TuningTable.from_sweep(two).lookup("broadcast", 2, 1 << 26) == ("ring", None)   # one link: nothing to fill
 
