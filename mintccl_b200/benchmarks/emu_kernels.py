@@ -24,7 +24,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspa
 
 KERNELS = ("ring_simple_allreduce", "ring_ll128_allreduce", "ring_simple_allgather", "ring_simple_reducescatter",
            "direct_allreduce", "direct_allgather", "direct_reducescatter", "bulk_allgather", "direct_broadcast",
-           "direct_reduce", "ll_oneshot", "mxfp8_allreduce", "p2p_pull", "multihop_ll128")
+           "direct_reduce", "direct2_reduce", "ll_oneshot", "mxfp8_allreduce", "p2p_pull", "multihop_ll128")
 
 
 def main() -> None:
@@ -98,6 +98,10 @@ def main() -> None:
         xs, ys = sym(numel), sym(numel)
         call = lambda: w.reduce(xs, root=0, out=ys, algo="direct", nch=nch)  # noqa: E731
         moved = nbytes / (n - 1) * n + nbytes / (n - 1)
+    elif k == "direct2_reduce":
+        xs, ys = sym(numel), sym(numel)
+        call = lambda: w.reduce(xs, root=0, out=ys, algo="direct2", nch=nch)  # noqa: E731
+        moved = nbytes / (n - 1) * (n - 1) + nbytes / (n - 1) + 3 * nbytes / (n - 1)   # per non-root; the root adds locally
     elif k == "ll_oneshot":
         xs = [torch.randn(8192, device="cuda", dtype=torch.float32).to(dtype) for _ in range(n)]
         ys = [torch.empty_like(x) for x in xs]

@@ -66,7 +66,7 @@ struct MtBarSlot {
   uint64_t pin[MT_MAX_RANKS];
   uint64_t _pad1[8];
   uint64_t pout[MT_MAX_RANKS];
-  uint64_t _pad2[8];
+  uint64_t xflag[MT_MAX_RANKS];   // progress counters inside one call: [p] is written by rank p (reduce with a summing root)
 };
 // Announced buffer addresses: bit 63 set means "offset into the announcing rank's symmetric heap".
 #define MT_PUB_HEAP_TAG 0x8000000000000000ull
@@ -135,3 +135,4 @@ static_assert(sizeof(MtSigSlot) == 128, "MtSigSlot is one 128-byte line");
 #define MT_WHERE_GEMM_FLAG 9
 #define MT_WHERE_TEST 10
 #define MT_WHERE_BULK 11
+#define MT_WHERE_CHUNK_FLAG 12

@@ -602,6 +602,14 @@ int mt_direct(MtComm* c, void* stream, int dtype, int out_dtype, int op, const v
     const bool narrow = dtype == mt::DT_F32 && (out_dtype == mt::DT_F16 || out_dtype == mt::DT_BF16);
     if (!widen && !narrow) return fail("conversions: fp16/bf16 -> fp32 and fp32 -> fp16/bf16");
   }
+  if (op == mt::DOP_REDUCE && variant == 5) {
+    if (dtype != out_dtype || nvls) return fail("reduce with a summing root: one element type, no NVLS");
+    if (c->nranks < 3) return fail("reduce with a summing root needs at least three ranks");
+    if (nbytes & 15) return fail("reduce with a summing root needs a byte count that is a multiple of 16");
+    for (int lr = 0; lr < c->nlocal; ++lr)
+      if ((((uintptr_t)(in ? in[lr] : nullptr)) | ((uintptr_t)(out ? out[lr] : nullptr))) & 15)
+        return fail("reduce with a summing root needs 16-byte aligned buffers");
+  }
   if (!c->emulated && c->nranks > 1 && (!pub_in || !pub_out)) return fail("peer views of the buffers are missing");
   mt::DirectArgs a;
   memset(&a, 0, sizeof(a));

@@ -114,13 +114,14 @@ struct PeerBufs {
 // starts at itself so that the n readers spread over the n memories.
 template <class TI, class TO, int NTHREADS, bool PUSH, bool FIXED_ORDER, int NR>
 __device__ __forceinline__ void pull_reduce_range_n(const MtDevComm& c, const PeerBufs& P, uint8_t* local_out,
-                                                    uint64_t byte_lo, uint64_t byte_hi, uint64_t local_base) {
+                                                    uint64_t byte_lo, uint64_t byte_hi, uint64_t local_base,
+                                                    int nsrc = 0) {
   using CI = CastInfo<TI, TO>;
-  // NR > 0: the rank count is a compile-time constant, so the loop over peers unrolls and all
-  // NR x kU remote loads of a thread are in flight together
-  const int n = NR > 0 ? NR : c.nranks;
+  // NR > 0: the number of sources is a compile-time constant, so the loop over them unrolls and all
+  // NR x kU remote loads of a thread are in flight together.  NR == 0: `nsrc` sources (all ranks if 0).
+  const int n = NR > 0 ? NR : (nsrc > 0 ? nsrc : c.nranks);
   // vectors per thread and pass: bounded so that NR x kU 16-byte registers fit without spilling
-  constexpr int kU = NR >= 8 ? 2 : kDirectUnroll;
+  constexpr int kU = NR >= 6 ? 2 : kDirectUnroll;
   // 16-byte vectors need every address involved to be aligned
   uint64_t mis = (uint64_t)(uintptr_t)(local_out + CI::out_off(byte_lo - local_base)) & CI::kOutAlignMask;
   for (int p = 0; p < n; ++p) {
@@ -207,6 +208,52 @@ __device__ __forceinline__ void pull_reduce_range(const MtDevComm& c, const Peer
     case 4: pull_reduce_range_n<TI, TO, NTHREADS, PUSH, FIXED_ORDER, 4>(c, P, local_out, byte_lo, byte_hi, local_base); break;
     case 8: pull_reduce_range_n<TI, TO, NTHREADS, PUSH, FIXED_ORDER, 8>(c, P, local_out, byte_lo, byte_hi, local_base); break;
     default: pull_reduce_range_n<TI, TO, NTHREADS, PUSH, FIXED_ORDER, 0>(c, P, local_out, byte_lo, byte_hi, local_base); break;
+  }
+}
+
+// Sum of `ns` sources (P.in[0 .. ns), in that order) over message bytes [byte_lo, byte_hi), stored at the same
+// offsets of `dst` (local or a peer's memory).
+// One function per source count (not inlined): each gets its own register allocation.
+template <class TI, class TO, int NTHREADS, int NR>
+__device__ __noinline__ void pull_reduce_sources_n(const MtDevComm& c, const PeerBufs& P, int ns, uint8_t* dst,
+                                                   uint64_t byte_lo, uint64_t byte_hi) {
+  pull_reduce_range_n<TI, TO, NTHREADS, false, true, NR>(c, P, dst, byte_lo, byte_hi, 0, ns);
+}
+template <class TI, class TO, int NTHREADS>
+__device__ __forceinline__ void pull_reduce_sources(const MtDevComm& c, const PeerBufs& P, int ns, uint8_t* dst,
+                                                    uint64_t byte_lo, uint64_t byte_hi) {
+  switch (ns) {
+    case 3: pull_reduce_sources_n<TI, TO, NTHREADS, 3>(c, P, ns, dst, byte_lo, byte_hi); break;
+    case 7: pull_reduce_sources_n<TI, TO, NTHREADS, 7>(c, P, ns, dst, byte_lo, byte_hi); break;
+    default: pull_reduce_sources_n<TI, TO, NTHREADS, 0>(c, P, ns, dst, byte_lo, byte_hi); break;
+  }
+}
+
+// dst[i] = round(dst[i] + src[i]) over nbytes (a multiple of 16; both addresses 16-byte aligned).  dst was
+// written by peers during this kernel, so it is read with system-scope loads.
+template <class T, int NTHREADS>
+__device__ __forceinline__ void add_into_range(uint8_t* dst, const uint8_t* src, uint64_t nbytes) {
+  const uint64_t nvec = nbytes >> 4;
+  for (uint64_t base = 0; base < nvec; base += (uint64_t)NTHREADS * kDirectUnroll) {
+    u128 a[kDirectUnroll], b[kDirectUnroll];
+#pragma unroll
+    for (int u = 0; u < kDirectUnroll; ++u) {
+      const uint64_t i = base + (uint64_t)u * NTHREADS + threadIdx.x;
+      if (i < nvec) {
+        a[u] = load128_relaxed_sys(dst + (i << 4));
+        b[u] = load128_stream(src + (i << 4));
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kDirectUnroll; ++u) {
+      const uint64_t i = base + (uint64_t)u * NTHREADS + threadIdx.x;
+      if (i < nvec) {
+        Acc128<T> acc;
+        acc.set(a[u]);
+        acc.add(b[u]);
+        *reinterpret_cast<u128*>(dst + (i << 4)) = acc.get();
+      }
+    }
   }
 }
 
@@ -433,6 +480,83 @@ __device__ __forceinline__ bool bulk_aligned(const BulkCtl* ctl) {
     for (int d = 0; d < ctl->jobs[j].ndst; ++d) mis |= (uint64_t)(uintptr_t)ctl->jobs[j].dst[d];
   }
   return (mis & 15) == 0;
+}
+
+// The n - 1 other ranks each sum one sub-slice of THEIR OWN inputs (the root's is left out) and store the
+// partial result into the root's output, chunk by chunk, raising a counter in the root's barrier slot
+// after each chunk; the root adds its own input to every chunk as it arrives.  Nobody reads the root's
+// memory.  Measured reason (4 B200, 256 MiB): with the root as one of the read sources (variant 3) the
+// call takes 568 us, without it 433 us, without the stores into the root 414 us.  The stores (write
+// requests carrying data) fill the root's incoming link, and read requests to the root wait behind them.
+// The price is a second rounding (the partial sum is rounded into the output type before the root adds)
+// and the root's own pass over the output: measured 500 us for 256 MiB on 4 B200 (variant 3: 566, in-switch
+// sum: 508) and 169 us for 64 MiB (165, 146).  An option for large messages in memory the switch cannot sum.
+// A function of its own (not inlined): its register allocation stays apart from the rest of the kernel.
+template <class T, int NTHREADS>
+__device__ __noinline__ void reduce_summing_root(const MtDevComm& c, const DirectArgs& a, const PeerBufs& P,
+                                                 const uint8_t* in, uint8_t* out, MtRange r, int cta, int* s_fail) {
+  using TI = T;
+  using TO = T;
+  const int n = c.nranks, me = c.rank;
+  constexpr uint64_t kChunk = 256u << 10;   // 64 KiB chunks cost 10 % (a fence and a counter per chunk), 512 KiB and up lengthen the root's tail
+  __shared__ uint64_t s_tag;
+  const uint64_t len = r.hi - r.lo;
+  MtBarSlot* mine = (MtBarSlot*)(c.heap[me] + c.L.bar_off) + cta;
+  // the slot's epoch moves in step on all ranks (every barrier on a slot includes every rank), so it
+  // tags the counters of this call: older calls left smaller values
+  if (threadIdx.x == 0) s_tag = load64(&mine->epoch) << 24;
+  __syncthreads();
+  const uint64_t tag = s_tag;
+  if (me != a.root) {
+    const int idx = mt_mod(me - a.root - 1, n);
+    const MtRange sm = mt_split(len, n - 1, idx, 128);
+    const uint8_t* src[MT_MAX_RANKS];
+    int ns = 0;
+    for (int d = 0; d < n; ++d) {   // this rank first, then the others in ring order, the root left out
+      const int p = (me + d) % n;
+      if (p != a.root) src[ns++] = P.in[p];
+    }
+    const PeerBufs Q{src, P.out};
+    MtBarSlot* roots = (MtBarSlot*)(c.heap[a.root] + c.L.bar_off) + cta;
+    uint64_t k = 0;
+    for (uint64_t lo = sm.lo; lo < sm.hi; lo += kChunk, ++k) {
+      const uint64_t hi = mt_min64(lo + kChunk, sm.hi);
+      pull_reduce_sources<TI, TO, NTHREADS>(c, Q, ns, P.out[a.root], r.lo + lo, r.lo + hi);
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        fence_acq_rel_sys();   // the CTA's stores into the root have landed before the counter moves
+        store64_release_sys(&roots->xflag[me], tag + k + 1);
+      }
+    }
+  } else {
+    uint64_t nchunks = 0;
+    for (int j = 0; j < n - 1; ++j) {
+      const MtRange sm = mt_split(len, n - 1, j, 128);
+      const uint64_t nc = mt_div_up(sm.hi - sm.lo, kChunk);
+      if (nc > nchunks) nchunks = nc;
+    }
+    bool ok = true;
+    for (uint64_t k = 0; ok && k < nchunks; ++k) {
+      for (int j = 0; ok && j < n - 1; ++j) {
+        const int p = (a.root + 1 + j) % n;   // the rank with sub-slice j
+        const MtRange sm = mt_split(len, n - 1, j, 128);
+        const uint64_t lo = sm.lo + k * kChunk;
+        if (lo >= sm.hi) continue;
+        const uint64_t hi = mt_min64(lo + kChunk, sm.hi);
+        if (threadIdx.x == 0) {
+          const uint64_t want = tag + k + 1;
+          const uint64_t* w = &mine->xflag[p];
+          if (!bounded_wait(
+                  c, [&] { return load64_acquire_sys(w) >= want; }, MT_ERR_TIMEOUT_FLAG, cta,
+                  MT_WHERE_CHUNK_FLAG, want, k, (const volatile uint64_t*)w))
+            atomicExch(s_fail, 1);
+        }
+        __syncthreads();
+        ok = *s_fail == 0;
+        if (ok) add_into_range<TI, NTHREADS>(out + r.lo + lo, in + r.lo + lo, hi - lo);
+      }
+    }
+  }
 }
 
 template <class TI, class TO, int NTHREADS>
@@ -744,6 +868,10 @@ __device__ void direct_body(const MtDevComm& c, const DirectArgs& a, int lr, int
             }
           }
         }
+        break;
+      }
+      if (a.variant == 5) {
+        if constexpr (kSame) reduce_summing_root<TI, NTHREADS>(c, a, P, in, out, r, cta, s_fail);
         break;
       }
       if (a.variant == 3) {

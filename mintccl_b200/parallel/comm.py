@@ -616,7 +616,7 @@ class Communicator:
         "allgather": ("auto", "ring", "direct", "nvls", "pull", "bulk", "bulkpull"),
         "reducescatter": ("auto", "ring", "direct", "nvls"),
         "broadcast": ("auto", "ring", "direct", "nvls", "pull", "push", "nvls1", "bulk"),
-        "reduce": ("auto", "ring", "direct", "nvls", "direct1", "nvls1"),
+        "reduce": ("auto", "ring", "direct", "direct2", "nvls", "direct1", "nvls1"),
     }
 
     def _algo(self, algo: Optional[str], collective: str) -> str:
@@ -965,6 +965,17 @@ class Communicator:
                 algo = self._auto_rooted("reduce", nbytes, symm, self._peer_ok(ins), separate)
         if cast and algo not in ("direct", "direct1"):
             raise ValueError(f"reduce into another element type runs on the one-hop paths (direct, direct1), not {algo}")
+        if algo == "direct2":
+            # The other ranks sum their own inputs slice by slice into the root's output and the root adds its own
+            # input as the chunks arrive: nobody reads the root's memory, whose incoming link is full of the partial
+            # sums.  Two roundings into the element type (partial sum, then the root's addition).
+            if cast or not separate or self.world_size < 3 or nbytes % 16 or \
+                    any(t.data_ptr() % 16 for t in ins + outs) or not (self._peer_ok(ins) and self._peer_ok(outs)):
+                raise ValueError("algo=direct2 needs three or more ranks, a separate output of the same element type that "
+                                 "the peers can address, 16-byte aligned buffers and a byte count that is a multiple of 16")
+            self._launch_direct(N.DOP_REDUCE, ins, outs, nbytes, dt, root=root, variant=5, nctas=nch,
+                                peers_read_in=True, peers_write_out=True, out_dtype=odt)
+            return
         if algo in ("direct", "nvls", "direct1", "nvls1"):
             if algo.startswith("nvls") and not (self.nvls and symm):
                 raise ValueError(f"algo={algo} needs the multicast mapping and a symmetric buffer")

@@ -366,6 +366,13 @@ def test_ordinary_tensors_take_the_one_hop_kernels_once_shared():
     assert l["fn"] == "mt_direct" and l["op"] == N.DOP_REDUCE and l["nvls"] == 0 and l["variant"] == 3
     c.reduce(large, root=2)                                        # in place: the chain
     assert c.last()["fn"] == "mt_ring"
+    c.reduce(large, root=2, out=torch.zeros(8 << 20, dtype=torch.float16), algo="direct2")   # the root sums its own input
+    l = c.last()
+    assert l["fn"] == "mt_direct" and l["op"] == N.DOP_REDUCE and l["variant"] == 5 and l["nvls"] == 0
+    with pytest.raises(ValueError):
+        c.reduce(large, root=2, algo="direct2")                    # needs a separate output
+    with pytest.raises(ValueError):
+        c.reduce(large[:1001], root=2, out=torch.zeros(1001, dtype=torch.float16), algo="direct2")   # 2002 bytes
     big = torch.zeros(1 << 20, dtype=torch.float16)
     c.broadcast(big, root=2, algo="direct")
     assert c.last()["fn"] == "mt_direct" and c.last()["variant"] == 2 and c.last()["nvls"] == 0

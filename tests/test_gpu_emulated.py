@@ -599,3 +599,28 @@ def test_algorithm_names_are_checked_per_collective():
             assert_sum_close(bufs[r][r], ref[r], torch.float16, 2)
     finally:
         w.cfg.algo = old
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n", [3, 4, 8])
+@pytest.mark.parametrize("numel", [8, 1000, 65536 + 24, 1_500_000])
+def test_reduce_with_a_summing_root(n, numel):
+    """`algo="direct2"`: the other ranks sum their own inputs slice by slice into the root's output, chunk by chunk
+    with a progress counter per chunk, and the root adds its own input as the chunks arrive.  Two roundings into the
+    element type; every root; several chunks per CTA at the largest size; two calls in a row (the counters of the
+    first call must not satisfy the waits of the second)."""
+    w = world(n)
+    for dtype in (torch.float16, torch.bfloat16, torch.float32):
+        per16 = 16 // torch.empty((), dtype=dtype).element_size()
+        ne = max(per16, numel // per16 * per16)                 # the byte count is a multiple of 16
+        for root in sorted({0, 1, n - 1}):
+            src = rand(n, ne, dtype, seed0=300 + root)
+            outs = [torch.full((ne,), -7.0, device="cuda", dtype=dtype) for _ in range(n)]
+            for rep in range(2):
+                w.reduce(src, root=root, out=outs, algo="direct2", nch=2 if numel > 1_000_000 else None)
+                w.check()
+                assert_sum_close(outs[root], oracle_sum(src), dtype, hops=2, nranks=n)
+                src = [s_ * 0.5 for s_ in src]                    # other values for the second call
+            for r in range(n):
+                if r != root:
+                    assert bool((outs[r] == -7.0).all())         # only the root's output is written
