@@ -933,7 +933,10 @@ class Communicator:
     def reduce(self, buff: TensorOrList, root: int = 0, out: Optional[TensorOrList] = None, algo: Optional[str] = None,
                proto: Optional[str] = None, nch: Optional[int] = None) -> None:
         """Sum of ``buff`` over all ranks, stored in ``buff`` (or ``out``) of ``root`` (5_reduce.py:99-121).  ``out``
-        may be the fp32 / 16-bit counterpart of ``buff``'s element type (one-hop paths)."""
+        may be the fp32 / 16-bit counterpart of ``buff``'s element type (one-hop paths).  ``algo``: ``ring`` (chain
+        over the FIFOs, any memory, in place or not), ``direct`` (the other ranks sum a slice each into the root's
+        ``out``), ``direct2`` (the same without any read of the root's memory: the root adds its own input; two
+        roundings), ``nvls`` (sums in the switch; heap tensors), ``direct1`` / ``nvls1`` (the root sums everything)."""
         if not self.emulated and type(buff) is torch.Tensor:
             if self._replay(self._key("reduce", buff, out, root, algo, proto, nch)):
                 return

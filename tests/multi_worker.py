@@ -209,6 +209,14 @@ def main():
                 c.check()
                 if rank == 0:
                     close(o, srcs, dtype, n if algo == "ring" else (2 if algo.startswith("nvls") else 1), f"reduce {algo}")
+                if algo == "direct" and n >= 3 and (numel * srcs[0].element_size()) % 16 == 0:
+                    o2 = torch.zeros(numel, device="cuda", dtype=dtype)   # the root sums its own input: two roundings
+                    torch.cuda.synchronize()
+                    c.control.barrier()
+                    c.reduce(b, root=1, out=o2, algo="direct2")
+                    c.check()
+                    if rank == 1:
+                        close(o2, srcs, dtype, 2, "reduce direct2")
                 if algo in ("direct", "nvls"):  # symmetric output: summing spread over all ranks
                     so = c.symm_zeros(numel, dtype)
                     torch.cuda.synchronize()
