@@ -1,4 +1,5 @@
 // One-hop / NVLS collectives, point-to-point copy, one-shot all-reduce: instantiations and launchers.
+#include <type_traits>
 #include "launch.h"
 #include "direct_engine.cuh"
 #include "p2p_engine.cuh"
@@ -8,6 +9,12 @@ template <class TI, class TO>
 static cudaError_t go_direct(const MtDevComm* comms, const DirectArgs& a, int nctas, int nlocal, cudaStream_t s) {
   DirectArgs args = a;
   void* p[] = {(void*)&comms, (void*)&args};
+  if (a.op == DOP_REDUCE && a.variant == 5) {   // counters per chunk: a kernel of its own
+    if constexpr (std::is_same<TI, TO>::value)
+      return launch_any((const void*)rooted_reduce_kernel<TI, kDirectThreads>, dim3(nctas, nlocal), dim3(kDirectThreads), p, s,
+                        nlocal > 1, 0);
+    return cudaErrorInvalidValue;
+  }
   const void* fn = (const void*)direct_kernel<TI, TO, kDirectThreads>;
   size_t smem = 0;
   if (a.variant >= 4) {  // the copy-engine variants stage their pieces in dynamic shared memory

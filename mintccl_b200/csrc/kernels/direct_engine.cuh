@@ -112,7 +112,7 @@ struct PeerBufs {
 // at local_out + out_off(o - local_base).  FIXED_ORDER sums ranks 0..n-1 in that order on every rank (bitwise
 // identical results everywhere, needed when several ranks reduce the same element); otherwise each rank
 // starts at itself so that the n readers spread over the n memories.
-template <class TI, class TO, int NTHREADS, bool PUSH, bool FIXED_ORDER, int NR>
+template <class TI, class TO, int NTHREADS, bool PUSH, bool FIXED_ORDER, int NR, bool SLIM = false>
 __device__ __forceinline__ void pull_reduce_range_n(const MtDevComm& c, const PeerBufs& P, uint8_t* local_out,
                                                     uint64_t byte_lo, uint64_t byte_hi, uint64_t local_base,
                                                     int nsrc = 0) {
@@ -121,7 +121,9 @@ __device__ __forceinline__ void pull_reduce_range_n(const MtDevComm& c, const Pe
   // NR x kU remote loads of a thread are in flight together.  NR == 0: `nsrc` sources (all ranks if 0).
   const int n = NR > 0 ? NR : (nsrc > 0 ? nsrc : c.nranks);
   // vectors per thread and pass: bounded so that NR x kU 16-byte registers fit without spilling
-  constexpr int kU = NR >= 6 ? 2 : kDirectUnroll;
+  // SLIM: half of that, for callers that keep more state alive around the call (chunk loops with counters);
+  // with n - 1 remote sources a CTA still has tens of KiB in flight
+  constexpr int kU = SLIM ? (NR >= 6 ? 1 : 2) : (NR >= 6 ? 2 : kDirectUnroll);
   // 16-byte vectors need every address involved to be aligned
   uint64_t mis = (uint64_t)(uintptr_t)(local_out + CI::out_off(byte_lo - local_base)) & CI::kOutAlignMask;
   for (int p = 0; p < n; ++p) {
@@ -200,24 +202,23 @@ __device__ __forceinline__ void pull_reduce_range_n(const MtDevComm& c, const Pe
   }
 }
 
-template <class TI, class TO, int NTHREADS, bool PUSH, bool FIXED_ORDER>
+template <class TI, class TO, int NTHREADS, bool PUSH, bool FIXED_ORDER, bool SLIM = false>
 __device__ __forceinline__ void pull_reduce_range(const MtDevComm& c, const PeerBufs& P, uint8_t* local_out,
                                                   uint64_t byte_lo, uint64_t byte_hi, uint64_t local_base) {
   switch (c.nranks) {
-    case 2: pull_reduce_range_n<TI, TO, NTHREADS, PUSH, FIXED_ORDER, 2>(c, P, local_out, byte_lo, byte_hi, local_base); break;
-    case 4: pull_reduce_range_n<TI, TO, NTHREADS, PUSH, FIXED_ORDER, 4>(c, P, local_out, byte_lo, byte_hi, local_base); break;
-    case 8: pull_reduce_range_n<TI, TO, NTHREADS, PUSH, FIXED_ORDER, 8>(c, P, local_out, byte_lo, byte_hi, local_base); break;
-    default: pull_reduce_range_n<TI, TO, NTHREADS, PUSH, FIXED_ORDER, 0>(c, P, local_out, byte_lo, byte_hi, local_base); break;
+    case 2: pull_reduce_range_n<TI, TO, NTHREADS, PUSH, FIXED_ORDER, 2, SLIM>(c, P, local_out, byte_lo, byte_hi, local_base); break;
+    case 4: pull_reduce_range_n<TI, TO, NTHREADS, PUSH, FIXED_ORDER, 4, SLIM>(c, P, local_out, byte_lo, byte_hi, local_base); break;
+    case 8: pull_reduce_range_n<TI, TO, NTHREADS, PUSH, FIXED_ORDER, 8, SLIM>(c, P, local_out, byte_lo, byte_hi, local_base); break;
+    default: pull_reduce_range_n<TI, TO, NTHREADS, PUSH, FIXED_ORDER, 0, SLIM>(c, P, local_out, byte_lo, byte_hi, local_base); break;
   }
 }
 
 // Sum of `ns` sources (P.in[0 .. ns), in that order) over message bytes [byte_lo, byte_hi), stored at the same
 // offsets of `dst` (local or a peer's memory).
-// One function per source count (not inlined): each gets its own register allocation.
 template <class TI, class TO, int NTHREADS, int NR>
-__device__ __noinline__ void pull_reduce_sources_n(const MtDevComm& c, const PeerBufs& P, int ns, uint8_t* dst,
-                                                   uint64_t byte_lo, uint64_t byte_hi) {
-  pull_reduce_range_n<TI, TO, NTHREADS, false, true, NR>(c, P, dst, byte_lo, byte_hi, 0, ns);
+__device__ __forceinline__ void pull_reduce_sources_n(const MtDevComm& c, const PeerBufs& P, int ns, uint8_t* dst,
+                                                      uint64_t byte_lo, uint64_t byte_hi) {
+  pull_reduce_range_n<TI, TO, NTHREADS, false, true, NR, true>(c, P, dst, byte_lo, byte_hi, 0, ns);
 }
 template <class TI, class TO, int NTHREADS>
 __device__ __forceinline__ void pull_reduce_sources(const MtDevComm& c, const PeerBufs& P, int ns, uint8_t* dst,
@@ -490,10 +491,12 @@ __device__ __forceinline__ bool bulk_aligned(const BulkCtl* ctl) {
 // requests carrying data) fill the root's incoming link, and read requests to the root wait behind them.
 // The price is a second rounding (the partial sum is rounded into the output type before the root adds)
 // and the root's own pass over the output: measured 500 us for 256 MiB on 4 B200 (variant 3: 566, in-switch
-// sum: 508) and 169 us for 64 MiB (165, 146).  An option for large messages in memory the switch cannot sum.
-// A function of its own (not inlined): its register allocation stays apart from the rest of the kernel.
+// sum: 508) and 169 us for 64 MiB (165, 146); 482 / 159 us once the chunk loop stopped spilling registers.  The
+// choice for large messages in memory the switch cannot sum.  (Tried and dropped: the others sum into staging
+// slots of their own and the root pulls them, so that all bulk data travels as read responses.  730 us: a root
+// CTA that pulls 64 KiB chunks from n - 1 producers in turn is bound by the latency of each chunk.)
 template <class T, int NTHREADS>
-__device__ __noinline__ void reduce_summing_root(const MtDevComm& c, const DirectArgs& a, const PeerBufs& P,
+__device__ __forceinline__ void reduce_summing_root(const MtDevComm& c, const DirectArgs& a, const PeerBufs& P,
                                                  const uint8_t* in, uint8_t* out, MtRange r, int cta, int* s_fail) {
   using TI = T;
   using TO = T;
@@ -870,10 +873,6 @@ __device__ void direct_body(const MtDevComm& c, const DirectArgs& a, int lr, int
         }
         break;
       }
-      if (a.variant == 5) {
-        if constexpr (kSame) reduce_summing_root<TI, NTHREADS>(c, a, P, in, out, r, cta, s_fail);
-        break;
-      }
       if (a.variant == 3) {
         // the root only receives: the other n - 1 ranks each sum one sub-slice (pulling it from everybody,
         // the root included) and store the result into the root's output.  Every link then carries about
@@ -916,6 +915,29 @@ __global__ void __launch_bounds__(NTHREADS, 1) direct_kernel(const MtDevComm* co
   const int lr = blockIdx.y;
   uint8_t* ring = (uint8_t*)(((uintptr_t)dyn_smem + 1023) & ~(uintptr_t)1023);
   direct_body<TI, TO, NTHREADS>(comms[lr], a, lr, blockIdx.x, gridDim.x, &s_fail, s_in, s_out, &ctl, ring);
+}
+
+// The reduce variant with per-chunk counters between the other ranks and the root (variant 5: summing root), as a
+// kernel of its own: its registers are allocated apart from direct_kernel's.
+template <class T, int NTHREADS>
+__global__ void __launch_bounds__(NTHREADS, 1) rooted_reduce_kernel(const MtDevComm* comms, DirectArgs a) {
+  __shared__ int s_fail;
+  __shared__ const uint8_t* s_in[MT_MAX_RANKS];
+  __shared__ uint8_t* s_out[MT_MAX_RANKS];
+  const int lr = blockIdx.y, cta = blockIdx.x;
+  const MtDevComm& c = comms[lr];
+  const uint8_t* in = (const uint8_t*)a.in[lr];
+  uint8_t* out = (uint8_t*)a.out[lr];
+  {
+    const int t = threadIdx.x & (MT_MAX_RANKS - 1);
+    const uint64_t vin = a.pub_local ? (uint64_t)(uintptr_t)in : a.pub_in[t];
+    const uint64_t vout = a.pub_local ? (uint64_t)(uintptr_t)out : a.pub_out[t];
+    if (!rank_barrier_xchg(c, cta, &s_fail, vin, vout, in, out, s_in, s_out)) return;
+  }
+  const PeerBufs P{s_in, s_out};
+  const MtRange r = mt_split(a.nbytes, gridDim.x, cta, kSplitAlignDirect);
+  reduce_summing_root<T, NTHREADS>(c, a, P, in, out, r, cta, &s_fail);
+  rank_barrier(c, cta, &s_fail);
 }
 
 }  // namespace mt

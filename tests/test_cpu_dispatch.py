@@ -364,6 +364,9 @@ def test_ordinary_tensors_take_the_one_hop_kernels_once_shared():
     c.reduce(large, root=2, out=torch.zeros(8 << 20, dtype=torch.float16))     # the others sum a slice each
     l = c.last()
     assert l["fn"] == "mt_direct" and l["op"] == N.DOP_REDUCE and l["nvls"] == 0 and l["variant"] == 3
+    huge = torch.zeros(32 << 20, dtype=torch.float16)              # 64 MiB: nobody reads the root, which adds its own input
+    c.reduce(huge, root=2, out=torch.zeros(32 << 20, dtype=torch.float16))
+    assert c.last()["fn"] == "mt_direct" and c.last()["variant"] == 5
     c.reduce(large, root=2)                                        # in place: the chain
     assert c.last()["fn"] == "mt_ring"
     c.reduce(large, root=2, out=torch.zeros(8 << 20, dtype=torch.float16), algo="direct2")   # the root sums its own input

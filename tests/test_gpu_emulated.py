@@ -604,7 +604,7 @@ def test_algorithm_names_are_checked_per_collective():
 @pytest.mark.gpu
 @pytest.mark.parametrize("n", [3, 4, 8])
 @pytest.mark.parametrize("numel", [8, 1000, 65536 + 24, 1_500_000])
-def test_reduce_with_a_summing_root(n, numel):
+def test_reduce_with_a_summing_root(n, numel, algo="direct2"):
     """`algo="direct2"`: the other ranks sum their own inputs slice by slice into the root's output, chunk by chunk
     with a progress counter per chunk, and the root adds its own input as the chunks arrive.  Two roundings into the
     element type; every root; several chunks per CTA at the largest size; two calls in a row (the counters of the
@@ -617,9 +617,9 @@ def test_reduce_with_a_summing_root(n, numel):
             src = rand(n, ne, dtype, seed0=300 + root)
             outs = [torch.full((ne,), -7.0, device="cuda", dtype=dtype) for _ in range(n)]
             for rep in range(2):
-                w.reduce(src, root=root, out=outs, algo="direct2", nch=2 if numel > 1_000_000 else None)
+                w.reduce(src, root=root, out=outs, algo=algo, nch=2 if numel > 1_000_000 else None)
                 w.check()
-                assert_sum_close(outs[root], oracle_sum(src), dtype, hops=2, nranks=n)
+                assert_sum_close(outs[root], oracle_sum(src), dtype, hops=2 if algo == "direct2" else 1, nranks=n)
                 src = [s_ * 0.5 for s_ in src]                    # other values for the second call
             for r in range(n):
                 if r != root:
