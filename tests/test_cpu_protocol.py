@@ -72,6 +72,37 @@ def test_split_covers_message_without_gaps():
             assert prev == total
 
 
+def test_rooted_one_hop_split_covers_every_byte_once():
+    """The index arithmetic of the rooted one-hop kernels (broadcast pull + replicate, reduce with the other ranks
+    summing): the message is split over the CTAs (128-byte boundaries), each CTA's range over the n - 1 ranks that are
+    not the root (128-byte boundaries), each sub-slice into 256 KiB chunks.  Every byte belongs to exactly one
+    (CTA, rank, chunk), every chunk starts on a 16-byte boundary for a byte count that is a multiple of 16, and the root
+    and each producer count the same number of chunks per sub-slice."""
+    def split(total, parts, i, align):
+        lo, hi = C.c_uint64(), C.c_uint64()
+        lib.mt_sched_split(total, parts, i, align, C.byref(lo), C.byref(hi))
+        return lo.value, hi.value
+    chunk = 256 << 10
+    for n in (3, 4, 8):
+        for total in (16, 2000, 65536 + 48, 3_000_000 - 3_000_000 % 16, 64 << 20):
+            for ncta in (1, 2, 37, 128):
+                covered = 0
+                for cta in range(ncta):
+                    rlo, rhi = split(total, ncta, cta, 128)
+                    prev = 0
+                    for idx in range(n - 1):
+                        lo, hi = split(rhi - rlo, n - 1, idx, 128)
+                        assert lo == prev and hi >= lo
+                        prev = hi
+                        nchunks = -(-(hi - lo) // chunk)
+                        for k in range(nchunks):
+                            clo, chi = lo + k * chunk, min(lo + (k + 1) * chunk, hi)
+                            assert (rlo + clo) % 16 == 0 and (chi - clo) % 16 == 0 and chi > clo
+                            covered += chi - clo
+                    assert prev == rhi - rlo
+                assert covered == total
+
+
 def test_ring_schedule_visits_every_shard_once():
     lib.mt_sched_ag_shard.restype = C.c_int
     lib.mt_sched_rs_shard.restype = C.c_int
