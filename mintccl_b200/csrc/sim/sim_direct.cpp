@@ -8,6 +8,11 @@
 //                of its own) BEFORE touching peer memory and again AFTER its last access; between the two it
 //                reads and writes slices of the peers' symmetric buffers.  Calls follow each other back to
 //                back on the same buffers, in place, and the "user" rewrites its input between calls.
+//   rooted sum   reduce with a summing root (rooted_reduce_kernel): between the two barriers every rank but the root sums
+//                its own slice over the ranks that are not the root, stores the partial sum into the root's output,
+//                chunk by chunk, and raises a counter in the root's barrier slot; the root waits for each counter and
+//                adds its own input to that chunk.  The counters are tagged with the slot's barrier epoch, so they
+//                are never cleared and an older call's value cannot satisfy a wait.  The root changes from call to call.
 //   one-shot     no barrier: every rank stores its lines, tagged with the call number, into the peers' staging
 //                area of that call's parity and polls its own area until the tag matches.
 //
@@ -43,7 +48,8 @@ struct Datum {
 };
 #endif
 
-enum Op { AR_TWO_SHOT = 0, ALLGATHER = 1, REDUCESCATTER = 2, ALLTOALL = 3, LL_ONESHOT = 4, NUM_OPS = 5 };
+enum Op { AR_TWO_SHOT = 0, ALLGATHER = 1, REDUCESCATTER = 2, ALLTOALL = 3, LL_ONESHOT = 4, REDUCE_SUMMING_ROOT = 5, NUM_OPS = 6 };
+constexpr int kChunks = 3;   // chunks per sub-slice in the rooted sum
 
 struct Params {
   int n, nctas, iters, slow_rank, dead_rank, exit_barrier;
@@ -59,6 +65,8 @@ struct Rank {
   std::vector<Datum> out;                       // second symmetric buffer (all-gather / all-to-all output)
   std::vector<std::atomic<uint64_t>> arrive;    // barrier slots [nctas][n]
   std::vector<uint64_t> bar_epoch;              // [nctas], private to the CTA that owns the slot
+  std::vector<std::atomic<uint64_t>> xflag;     // chunk counters of the rooted sum [nctas][n]: [.][q] is written by rank q
+  std::vector<Datum> rout;                      // the root's output of the rooted sum [n slices][nctas parts][kChunks]
   std::vector<std::atomic<uint64_t>> ll;        // one-shot area [2 parities][n sources][nctas]: the stamp is the flag
   std::vector<uint64_t> ll_epoch;               // [nctas]
   std::atomic<int> done_in_call{0};
@@ -149,6 +157,33 @@ bool direct_cta(Ctx& c, int me, int cta, int op, uint64_t e) {
       // slice q of my buffer goes to slice `me` of rank q's output
       for (int q = 0; q < n; ++q) c.w->ranks[q].out[at(me)].store(c.w->ranks[me].buf[at(q)].load());
       break;
+    case REDUCE_SUMMING_ROOT: {
+      const int root = (int)(e % (uint64_t)n);
+      const uint64_t tag = c.w->ranks[me].bar_epoch[cta] << 24;   // the same on every rank after the entry barrier
+      auto ro = [&](int slice, int k) { return ((size_t)slice * nc + cta) * kChunks + k; };
+      if (n == 1) break;
+      if (me != root) {
+        for (int k = 0; k < kChunks; ++k) {
+          // sum my slice over the ranks that are not the root (the root's memory is never read)
+          for (int q = 0; q < n; ++q)
+            if (q != root && c.w->ranks[q].buf[at(me)].load() != stamp(e, q, me, cta)) return c.bad();
+          c.w->ranks[root].rout[ro(me, k)].store(stamp(e, n + me, me, cta) + (uint64_t)k * 7);   // the partial sum
+          c.jitter();
+          c.w->ranks[root].xflag[(size_t)cta * n + me].store(tag + k + 1, std::memory_order_release);
+        }
+      } else {
+        for (int k = 0; k < kChunks; ++k)
+          for (int q = 0; q < n; ++q) {
+            if (q == root) continue;
+            const std::atomic<uint64_t>& f = c.w->ranks[root].xflag[(size_t)cta * n + q];
+            if (!c.wait([&] { return f.load(std::memory_order_acquire) >= tag + k + 1; })) return false;
+            if (c.w->ranks[root].rout[ro(q, k)].load() != stamp(e, n + q, q, cta) + (uint64_t)k * 7) return c.bad();
+            if (c.w->ranks[root].buf[at(q)].load() != stamp(e, root, q, cta)) return c.bad();   // my own input
+            c.w->ranks[root].rout[ro(q, k)].store(stamp(e, 2 * n + q, q, cta) + (uint64_t)k * 7);   // the sum
+          }
+      }
+      break;
+    }
     default: break;
   }
   c.jitter();
@@ -171,6 +206,15 @@ bool direct_cta(Ctx& c, int me, int cta, int op, uint64_t e) {
       for (int s = 0; s < n; ++s)
         if (c.w->ranks[me].out[at(s)].load() != stamp(e, s, me, cta)) return c.bad();
       break;
+    case REDUCE_SUMMING_ROOT: {
+      const int root = (int)(e % (uint64_t)n);
+      if (me != root) break;
+      for (int q = 0; q < n; ++q)
+        for (int k = 0; q != root && k < kChunks; ++k)
+          if (c.w->ranks[me].rout[(((size_t)q * nc + cta) * kChunks) + k].load() != stamp(e, 2 * n + q, q, cta) + (uint64_t)k * 7)
+            return c.bad();
+      break;
+    }
     default: break;
   }
   return true;
@@ -223,7 +267,8 @@ void cta_thread(World* w, int me, int cta, uint32_t seed) {
 extern "C" {
 
 // Runs `iters` back-to-back calls (a seeded random mix of two-shot all-reduce, all-gather, reduce-scatter,
-// all-to-all and one-shot all-reduce; `only_op` >= 0 fixes the operation) on a simulated world.
+// all-to-all, one-shot all-reduce and the reduce with a summing root; `only_op` >= 0 fixes the operation) on a
+// simulated world.
 // Returns 0 ok, 1 a value of another call / rank was read, 2 a wait gave up, -1 bad argument.
 int mt_sim_direct(int nranks, int nctas, int iters, uint32_t seed, int only_op, int slow_rank, int dead_rank,
                   int exit_barrier, uint64_t timeout_ms) {
@@ -238,6 +283,9 @@ int mt_sim_direct(int nranks, int nctas, int iters, uint32_t seed, int only_op, 
     r.out = std::vector<Datum>((size_t)nranks * nctas);
     r.arrive = std::vector<std::atomic<uint64_t>>((size_t)nctas * nranks);
     r.ll = std::vector<std::atomic<uint64_t>>((size_t)2 * nranks * nctas);
+    r.xflag = std::vector<std::atomic<uint64_t>>((size_t)nctas * nranks);
+    for (auto& x : r.xflag) x.store(0);
+    r.rout = std::vector<Datum>((size_t)nranks * nctas * kChunks);
     for (auto& x : r.arrive) x.store(0);
     for (auto& x : r.ll) x.store(0);
     r.bar_epoch.assign(nctas, 0);

@@ -355,12 +355,12 @@ def _direct(n, nctas, iters, seed=1, only_op=-1, slow=-1, dead=-1, exit_barrier=
 
 @pytest.mark.parametrize("n", [2, 4, 8])
 def test_direct_protocols_random_mix_back_to_back(n):
-    """Two-shot all-reduce (in place), all-gather, reduce-scatter, all-to-all and the one-shot all-reduce in a
-    random order on the same buffers, which the 'user' rewrites between calls: every value read carries the
+    """Two-shot all-reduce (in place), all-gather, reduce-scatter, all-to-all, the one-shot all-reduce and the reduce
+    with a summing root in a random order on the same buffers, which the 'user' rewrites between calls: every value read carries the
     stamp of the expected call and rank; also with one rank far behind."""
     assert _direct(n, 3, 300, seed=n) == 0
     assert _direct(n, 2, 60, seed=10 + n, slow=0) == 0
-    for op in range(5):
+    for op in range(6):   # 5: reduce with a summing root (chunk counters tagged with the barrier epoch, a new root per call)
         assert _direct(n, 2, 40, seed=20 + op, only_op=op) == 0
 
 
@@ -393,7 +393,7 @@ def test_direct_protocols_under_thread_sanitizer(tmp_path):
 
     # ranks, CTAs, calls, seed, operation (-1 mix), slow rank, dead rank, exit barrier, ms
     for a in [(8, 3, 60, 1, -1, -1, -1, 1, 8000), (4, 2, 60, 2, -1, 0, -1, 1, 8000), (4, 2, 60, 3, 0, 1, -1, 1, 8000),
-              (4, 4, 100, 4, 4, 2, -1, 1, 8000)]:
+              (4, 4, 100, 4, 4, 2, -1, 1, 8000), (8, 2, 60, 7, 5, -1, -1, 1, 8000), (4, 3, 80, 8, 5, 1, -1, 1, 8000)]:
         rc, err = run(*a)
         assert rc == 0, (a, err[-1500:])
     rc, err = run(4, 2, 30, 5, 0, 0, -1, 0, 8000)
